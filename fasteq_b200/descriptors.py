@@ -1,0 +1,158 @@
+"""Path tables ("descriptors") for the three operators of the message-passing hot path.
+
+The reference receives these tables from cuEquivariance descriptors
+(``cue.descriptors.channelwise_tensor_product`` etc., called at
+test/bench_tensor_product_uniform1d.py:127-130); that package is not part of
+the reference tree, so the tables are generated here from e3nn's published
+``TensorProduct`` semantics (e3nn/o3/_tensor_product/_tensor_product.py:277-323
+for the path normalisation, _codegen.py:166-187 for the uvu contraction).
+
+A Uniform1D table is the flat list ``(i, j, k, v, coeff)`` of the reference's
+``meta`` dict (fasteq/ops/uniform1d_jit.py:3216-3235):
+``out[v, u] += coeff * w[i, u] * x[j, u] * y[k, (u|0)]``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from math import sqrt
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from .irreps import Irreps, Irrep
+from .wigner import wigner_3j
+
+
+@dataclass(frozen=True)
+class Instruction:
+    """One (l1, l2, l3) coupling: rows of x, y, out it touches and its weight segment."""
+    w_seg: int
+    x_off: int
+    y_off: int
+    out_off: int
+    l1: int
+    l2: int
+    l3: int
+    path_weight: float  # e3nn's sqrt(alpha)
+
+
+@dataclass
+class Uniform1DDescriptor:
+    i_list: np.ndarray
+    j_list: np.ndarray
+    k_list: np.ndarray
+    v_list: np.ndarray
+    coeff_list: np.ndarray  # float64
+    w_seg_num: int
+    x_seg_num: int
+    y_seg_num: int
+    out_seg_num: int
+    u_dim: int
+    y_u_dim: int = 1  # 1 = "u,u,,u" (scalar y per segment), u_dim = "u,u,u,u"
+    instructions: Tuple[Instruction, ...] = ()
+    irreps_in1: Optional[Irreps] = None
+    irreps_in2: Optional[Irreps] = None
+    irreps_out: Optional[Irreps] = None
+
+    @property
+    def num_paths(self) -> int:
+        return int(self.i_list.shape[0])
+
+    def meta(self, dtype=None, device=None) -> Dict:
+        """The ``meta`` dict ``fast_uniform1d_jit`` takes (same keys as the reference)."""
+        import torch
+        dtype = dtype or torch.float32
+        t = lambda a: torch.as_tensor(np.ascontiguousarray(a), dtype=torch.int32, device=device)
+        return dict(
+            i_list=t(self.i_list), j_list=t(self.j_list), k_list=t(self.k_list), v_list=t(self.v_list),
+            coeff_list=torch.as_tensor(self.coeff_list, dtype=dtype, device=device),
+            w_seg_num=self.w_seg_num, x_seg_num=self.x_seg_num, y_seg_num=self.y_seg_num,
+            out_seg_num=self.out_seg_num, u_dim=self.u_dim,
+            size_list=[self.w_seg_num * self.u_dim, self.x_seg_num * self.u_dim,
+                       self.y_seg_num * self.y_u_dim, self.out_seg_num * self.u_dim],
+        )
+
+
+def full_channelwise_instructions(irreps_in1, irreps_in2, lmax_out: int, sort: bool = False,
+                                  parity_filter: Optional[str] = None):
+    """All allowed uvu couplings of ``irreps_in1 x irreps_in2`` up to ``lmax_out``.
+
+    Returns ``(irreps_out, instructions)`` with one output block per coupling
+    (the MACE / NequIP convolution construction).  ``parity_filter='natural'``
+    keeps only outputs with parity ``(-1)^l`` (MACE's default).  ``sort=True``
+    orders the output blocks by (l, parity) the way e3nn's ``Irreps.sort`` does
+    and remaps the instructions.
+    """
+    irreps_in1, irreps_in2 = Irreps(irreps_in1), Irreps(irreps_in2)
+    out_blocks, instr = [], []
+    for i1, b1 in enumerate(irreps_in1):
+        for i2, b2 in enumerate(irreps_in2):
+            for ir in b1.ir * b2.ir:
+                if ir.l > lmax_out:
+                    continue
+                if parity_filter == "natural" and ir.p != (-1) ** ir.l:
+                    continue
+                k = len(out_blocks)
+                out_blocks.append((b1.mul, ir))
+                instr.append((i1, i2, k, "uvu", True))
+    if sort:
+        # e3nn orders irreps by (l, then even before odd for even l / odd before even for odd l);
+        # a stable sort on (l, -p*(-1)^l) reproduces Irrep.__lt__.
+        order = sorted(range(len(out_blocks)), key=lambda n: (out_blocks[n][1].l, -out_blocks[n][1].p * (-1) ** out_blocks[n][1].l))
+        inv = {old: new for new, old in enumerate(order)}
+        out_blocks = [out_blocks[o] for o in order]
+        instr = sorted([(a, b, inv[c], m, h) for a, b, c, m, h in instr], key=lambda t: t[2])
+    return Irreps(out_blocks), instr
+
+
+def channelwise_tensor_product(irreps_in1, irreps_in2, irreps_out, instructions,
+                               irrep_normalization: str = "component",
+                               path_normalization: str = "element") -> Uniform1DDescriptor:
+    """Flatten an e3nn ``TensorProduct`` with ``uvu`` instructions into a Uniform1D table.
+
+    ``instructions`` are e3nn tuples ``(i_in1, i_in2, i_out, "uvu", has_weight[, path_weight])``.
+    Every ``irreps_in2`` block must have multiplicity 1 (edge attributes / spherical
+    harmonics) and ``irreps_in1`` / ``irreps_out`` a uniform multiplicity ``u``.
+    """
+    irreps_in1, irreps_in2, irreps_out = Irreps(irreps_in1), Irreps(irreps_in2), Irreps(irreps_out)
+    u = irreps_in1.uniform_mul()
+    if any(b.mul != 1 for b in irreps_in2):
+        raise ValueError("channelwise tensor product needs multiplicity 1 on irreps_in2")
+    if any(b.mul != u for b in irreps_out):
+        raise ValueError("irreps_out must carry the multiplicity of irreps_in1")
+    norm = []
+    for ins in instructions:
+        ins = tuple(ins) + ((1.0,) if len(ins) == 5 else ())
+        if ins[3] != "uvu" or not ins[4]:
+            raise NotImplementedError("only weighted 'uvu' instructions are supported")
+        norm.append(ins)
+    x_offs, y_offs, o_offs = irreps_in1.segment_offsets(), irreps_in2.segment_offsets(), irreps_out.segment_offsets()
+
+    il, jl, kl, vl, cl, table = [], [], [], [], [], []
+    for n, (i1, i2, io, _, _, pw_user) in enumerate(norm):
+        ir1, ir2, iro = irreps_in1[i1].ir, irreps_in2[i2].ir, irreps_out[io].ir
+        if ir1.p * ir2.p != iro.p or not (abs(ir1.l - ir2.l) <= iro.l <= ir1.l + ir2.l):
+            raise ValueError(f"instruction {n} violates the selection rules")
+        alpha = {"component": float(iro.dim), "norm": float(ir1.dim * ir2.dim), "none": 1.0}[irrep_normalization]
+        if path_normalization == "element":
+            fan = sum(irreps_in2[t[1]].mul for t in norm if t[2] == io)
+        elif path_normalization == "path":
+            fan = irreps_in2[i2].mul * len([t for t in norm if t[2] == io])
+        else:
+            fan = 1
+        if fan > 0:
+            alpha /= fan
+        alpha *= pw_user
+        pw = sqrt(alpha)
+        c3 = wigner_3j(ir1.l, ir2.l, iro.l)
+        table.append(Instruction(n, x_offs[i1], y_offs[i2], o_offs[io], ir1.l, ir2.l, iro.l, pw))
+        for m1, m2, m3 in zip(*np.nonzero(c3)):
+            il.append(n); jl.append(x_offs[i1] + m1); kl.append(y_offs[i2] + m2); vl.append(o_offs[io] + m3)
+            cl.append(pw * c3[m1, m2, m3])
+    i32 = lambda a: np.asarray(a, dtype=np.int32)
+    return Uniform1DDescriptor(
+        i32(il), i32(jl), i32(kl), i32(vl), np.asarray(cl, dtype=np.float64),
+        w_seg_num=len(norm), x_seg_num=irreps_in1.num_segments, y_seg_num=irreps_in2.num_segments,
+        out_seg_num=irreps_out.num_segments, u_dim=u, y_u_dim=1, instructions=tuple(table),
+        irreps_in1=irreps_in1, irreps_in2=irreps_in2, irreps_out=irreps_out,
+    )

@@ -1,0 +1,102 @@
+"""Generate golden vectors from the e3nn 0.5.6 sources vendored in the reference tree.
+
+Run where the reference is mounted:  python tests/golden/make_golden.py
+Writes tests/golden/e3nn_golden.npz (float64).  The e3nn sources are imported in
+place from the reference's model bundle; the one missing dependency
+(opt_einsum_fx, an einsum-order optimiser) is replaced by an identity stub.
+"""
+import glob
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+REF = os.environ.get("FASTEQ_REFERENCE", "/root/reference")
+bundle = glob.glob(os.path.join(REF, "test/nequip_allegro_test/NequIP_OAM_R_4.5*nequip"))[0]
+sys.path.insert(0, bundle)
+stub = types.ModuleType("opt_einsum_fx")
+stub.optimize_einsums_full = lambda model, example_inputs=None, *a, **k: model
+stub.jitable = lambda x: x
+sys.modules["opt_einsum_fx"] = stub
+
+from e3nn.o3._wigner import wigner_3j  # noqa: E402
+from e3nn.o3._irreps import Irreps  # noqa: E402
+from e3nn.o3._spherical_harmonics import spherical_harmonics  # noqa: E402
+from e3nn.o3._tensor_product._tensor_product import TensorProduct  # noqa: E402
+from e3nn.o3._linear import Linear  # noqa: E402
+
+torch.set_default_dtype(torch.float64)
+out = {}
+
+# 1. Wigner 3j
+for l1 in range(4):
+    for l2 in range(5):
+        for l3 in range(abs(l1 - l2), min(l1 + l2, 4) + 1):
+            out[f"w3j_{l1}_{l2}_{l3}"] = wigner_3j(l1, l2, l3).numpy()
+
+# 2. spherical harmonics + gradient
+g = torch.Generator().manual_seed(11)
+vec = torch.randn(24, 3, generator=g) * 2.0
+vec.requires_grad_(True)
+for normalize in (True, False):
+    sh = spherical_harmonics([0, 1, 2, 3, 4], vec, normalize=normalize, normalization="component")
+    r = torch.randn(sh.shape, generator=g)
+    (gv,) = torch.autograd.grad((sh * r).sum(), vec)
+    tag = "n" if normalize else "u"
+    out[f"sh_{tag}_val"], out[f"sh_{tag}_r"], out[f"sh_{tag}_grad"] = sh.detach().numpy(), r.numpy(), gv.numpy()
+out["sh_vec"] = vec.detach().numpy()
+
+
+def all_paths(in1, in2, lmax, natural=False):
+    in1, in2 = Irreps(in1), Irreps(in2)
+    blocks, ins = [], []
+    for i1, (mul, ir1) in enumerate(in1):
+        for i2, (_, ir2) in enumerate(in2):
+            for ir in ir1 * ir2:
+                if ir.l <= lmax and (not natural or ir.p == (-1) ** ir.l):
+                    ins.append((i1, i2, len(blocks), "uvu", True))
+                    blocks.append((mul, ir))
+    return Irreps(blocks), ins
+
+
+def tp_case(name, in1, in2, irreps_out, ins, z, seed):
+    tp = TensorProduct(in1, in2, irreps_out, ins, shared_weights=False, internal_weights=False)
+    g = torch.Generator().manual_seed(seed)
+    x1 = torch.randn(z, tp.irreps_in1.dim, generator=g, requires_grad=True)
+    v = torch.randn(z, 3, generator=g)
+    x2 = spherical_harmonics(list(range(Irreps(in2).lmax + 1)), v, normalize=True, normalization="component").requires_grad_(True)
+    w = torch.randn(z, tp.weight_numel, generator=g, requires_grad=True)
+    o = tp(x1, x2, w)
+    r = torch.randn(o.shape, generator=g)
+    g1, g2, gw = torch.autograd.grad((o * r).sum(), (x1, x2, w))
+    out[f"tp_{name}_irreps"] = np.array([str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out)])
+    out[f"tp_{name}_ins"] = np.array([(a, b, c) for a, b, c, *_ in ins], dtype=np.int64)
+    for k, t in dict(x1=x1, x2=x2, w=w, out=o, r=r, g1=g1, g2=g2, gw=gw).items():
+        out[f"tp_{name}_{k}"] = t.detach().numpy()
+
+
+# 3a. one output block per path (MACE-style), all parities, l <= 3
+io, ins = all_paths("4x0e+4x1o+4x2e", "1x0e+1x1o+1x2e+1x3o", 3)
+tp_case("full", "4x0e+4x1o+4x2e", "1x0e+1x1o+1x2e+1x3o", io, ins, z=7, seed=3)
+# 3b. shared output blocks (NequIP-style): several instructions feed one irreps_out block
+in1, in2, o3 = Irreps("3x0e+3x1o+3x1e"), Irreps("1x0e+1x1o+1x2e"), Irreps("3x0e+3x1o+3x1e+3x2e")
+ins = [(i1, i2, io_, "uvu", True) for i1, (_, a) in enumerate(in1) for i2, (_, b) in enumerate(in2)
+       for io_, (_, c) in enumerate(o3) if c in a * b]
+tp_case("shared", in1, in2, o3, ins, z=5, seed=4)
+
+# 4. e3nn Linear
+for name, a, b in (("simple", "4x0e+4x1o+4x2e", "6x0e+6x1o+6x2e"), ("multi", "4x0e+4x0e+4x1o", "5x0e+5x1o+5x1o")):
+    lin = Linear(a, b, internal_weights=False, shared_weights=True)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(9, lin.irreps_in.dim, generator=g)
+    w = torch.randn(lin.weight_numel, generator=g)
+    out[f"lin_{name}_irreps"] = np.array([str(lin.irreps_in), str(lin.irreps_out)])
+    out[f"lin_{name}_x"], out[f"lin_{name}_w"], out[f"lin_{name}_out"] = x.numpy(), w.numpy(), lin(x, w).numpy()
+    out[f"lin_{name}_ins"] = np.array([(i.i_in, i.i_out) for i in lin.instructions], dtype=np.int64)
+    out[f"lin_{name}_pw"] = np.array([i.path_weight for i in lin.instructions])
+
+dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "e3nn_golden.npz")
+np.savez_compressed(dst, **out)
+print("wrote", dst, os.path.getsize(dst), "bytes,", len(out), "arrays")
