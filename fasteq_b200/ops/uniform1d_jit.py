@@ -1,0 +1,285 @@
+"""``fast_uniform1d_jit``: drop-in for fasteq/ops/uniform1d_jit.py:3328-3349.
+
+Same call: ``fast_uniform1d_jit(w, x, y, input_indices, output_indices, meta)`` with
+``input_indices = {1: src}`` (gather x), ``{2: src}`` (gather y), ``output_indices =
+{0: dst}`` (scatter-sum the result), ``meta`` the reference's dict
+(``i_list, j_list, k_list, v_list, coeff_list, w_seg_num, x_seg_num, y_seg_num,
+out_seg_num, u_dim, size_list``).  Tensors are 2-D ``[rows, segments * u]`` in
+ir_mul layout, CUDA, contiguous (a non-contiguous operand raises ``RuntimeError``
+as in the reference; there is no CPU path).
+
+Underneath, the path table is compiled into an sm_100a module (one per
+signature, cached in-tree) and called through the C ABI of
+include/fasteq_b200.h.  Scattered outputs use a receiver-sorted CSR plan that is
+built once per index tensor and cached.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+import torch
+
+from .. import _build, _cabi
+from ..codegen import u1d as _emit
+from ..codegen.u1d_common import U1DSpec, make_spec
+
+_EMITTER_VERSION = "u1d-v1"
+_MODULES: Dict[Tuple, _cabi.U1DModule] = {}
+_TUNING_OVERRIDE: Dict[str, _emit.Tuning] = {}
+_lock = threading.Lock()
+
+
+def _dtype_str(t: torch.Tensor) -> str:
+    if t.dtype == torch.float32:
+        return "f32"
+    if t.dtype == torch.float64:
+        return "f64"
+    raise ValueError(f"fast_uniform1d_jit supports float32 and float64, got {t.dtype}")
+
+
+def get_module(spec: U1DSpec, direction: str, needs=(False, False, False), tuning: Optional[_emit.Tuning] = None) -> _cabi.U1DModule:
+    """Build (or load from the in-tree cache) the module of one signature."""
+    tun = tuning or _TUNING_OVERRIDE.get(direction) or _emit.default_tuning(spec, direction)
+    key = (spec, direction, tuple(needs), tun)
+    with _lock:
+        mod = _MODULES.get(key)
+        if mod is None:
+            tag = spec.key(f"{_EMITTER_VERSION}|{direction}|{tuple(needs)}|{tun}")
+            if direction == "fwd":
+                source = _emit.emit_forward(spec, tun)
+            else:
+                source = _emit.emit_backward(spec, tun, *needs)
+            so = _build.build_generated(f"u1d_{direction}_{tag}", source)
+            mod = _cabi.U1DModule(so)
+            _MODULES[key] = mod
+    return mod
+
+
+# ----------------------------------------------------------------------------- graph plan
+
+class GraphPlan:
+    """Receiver-sorted CSR view of a scatter index: sortedness, permutation, segment offsets
+    and per-grid partitions.  Built once per index tensor (one host sync) and cached."""
+
+    def __init__(self, dst: torch.Tensor, n_rows: int):
+        if dst.dim() != 1:
+            raise ValueError("scatter index must be 1-D")
+        core = _cabi.core()
+        self.n_rows = int(n_rows)
+        self.n_edges = int(dst.numel())
+        dev = dst.device
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        dst32 = dst.to(torch.int32).contiguous()
+        flag = torch.empty(1, dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            _cabi.check(core.fasteq_graph_check_sorted(dst32.data_ptr(), self.n_edges, flag.data_ptr(), stream), core,
+                        "fasteq_graph_check_sorted")
+            self.sorted = bool(flag.item())
+            if self.sorted:
+                self.perm = None
+                sorted_dst = dst32
+            else:
+                sorted_dst64, perm = torch.sort(dst32.to(torch.int64), stable=True)
+                self.perm = perm.to(torch.int32).contiguous()
+                sorted_dst = sorted_dst64.to(torch.int32).contiguous()
+            self.seg_ptr = torch.empty(self.n_rows + 1, dtype=torch.int32, device=dev)
+            _cabi.check(core.fasteq_graph_build_csr(sorted_dst.data_ptr(), self.n_edges, self.n_rows,
+                                                    self.seg_ptr.data_ptr(), stream), core, "fasteq_graph_build_csr")
+        self._parts: Dict[int, torch.Tensor] = {}
+        self.device = dev
+
+    def partition(self, n_parts: int) -> torch.Tensor:
+        p = self._parts.get(n_parts)
+        if p is None:
+            core = _cabi.core()
+            p = torch.empty(n_parts + 1, dtype=torch.int32, device=self.device)
+            with torch.cuda.device(self.device):
+                stream = torch.cuda.current_stream(self.device).cuda_stream
+                _cabi.check(core.fasteq_graph_partition(self.seg_ptr.data_ptr(), self.n_rows, self.n_edges, n_parts,
+                                                        p.data_ptr(), stream), core, "fasteq_graph_partition")
+            self._parts[n_parts] = p
+        return p
+
+
+_PLANS: Dict[Tuple, GraphPlan] = {}
+_PLAN_LIMIT = 64
+
+
+def graph_plan(dst: torch.Tensor, n_rows: int) -> GraphPlan:
+    key = (dst.data_ptr(), dst.numel(), dst._version, str(dst.device), dst.dtype, int(n_rows))
+    plan = _PLANS.get(key)
+    if plan is None:
+        if len(_PLANS) >= _PLAN_LIMIT:
+            _PLANS.pop(next(iter(_PLANS)))
+        plan = GraphPlan(dst, n_rows)
+        plan._keepalive = dst  # the key is the storage address: keep it from being recycled
+        _PLANS[key] = plan
+    return plan
+
+
+_SM_COUNT: Dict[int, int] = {}
+
+
+def _sm_count(dev: torch.device) -> int:
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SM_COUNT[idx]
+
+
+# ----------------------------------------------------------------------------- helpers
+
+def _validate(w, x, y):
+    for name, t in (("w", w), ("x", x), ("y", y)):
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"{name} must be a tensor")
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor: fasteq_b200 has no CPU path")
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+    if not (w.dtype == x.dtype == y.dtype):
+        raise ValueError("w, x, y must share one dtype")
+
+
+def _index32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    if t is None:
+        return None
+    if t.dtype != torch.int32:
+        t = t.to(torch.int32)
+    return t.contiguous()
+
+
+class _Call:
+    """Resolved shapes / indices / plan of one operator call, shared by forward and backward."""
+
+    def __init__(self, w, x, y, input_indices, output_indices, meta):
+        input_indices = {} if input_indices is None else input_indices
+        output_indices = {} if output_indices is None else output_indices
+        self.u = int(meta["u_dim"])
+        self.w_segs, self.x_segs = int(meta["w_seg_num"]), int(meta["x_seg_num"])
+        self.y_segs, self.out_segs = int(meta["y_seg_num"]), int(meta["out_seg_num"])
+        size_list = meta["size_list"]
+        y_cols = int(size_list[2]) // self.y_segs
+        if y_cols not in (1, self.u):
+            raise ValueError("y must carry 1 or u_dim values per segment")
+        self.y_vec = y_cols != 1
+        for name, t, cols in (("w", w, self.w_segs * self.u), ("x", x, self.x_segs * self.u), ("y", y, self.y_segs * y_cols)):
+            if t.dim() < 2 or t.numel() % cols != 0:
+                raise ValueError(f"{name} has {t.numel()} elements, not a multiple of {cols}")
+        self.w_rows, self.x_rows, self.y_rows = w.numel() // (self.w_segs * self.u), x.numel() // (self.x_segs * self.u), y.numel() // (self.y_segs * y_cols)
+        self.x_indexed, self.y_indexed = 1 in input_indices, 2 in input_indices
+        self.scattered = 0 in output_indices
+        src = input_indices.get(1, input_indices.get(2))
+        self.src = _index32(src)
+        dst = output_indices.get(0)
+        # row count of the per-edge operands: dst, else src, else x (uniform1d_forward.py:163-168)
+        if dst is not None:
+            self.n_edges = int(dst.numel())
+        elif src is not None:
+            self.n_edges = int(src.numel())
+        else:
+            self.n_edges = self.x_rows
+        self.w_shared = self.w_rows == 1 and self.n_edges != 1
+        if not self.w_shared and self.w_rows != self.n_edges:
+            raise ValueError(f"w has {self.w_rows} rows for {self.n_edges} edges")
+        if not self.x_indexed and self.x_rows != self.n_edges:
+            raise ValueError("x rows must equal the edge count when x is not gathered")
+        if not self.y_indexed and self.y_rows != self.n_edges:
+            raise ValueError("y rows must equal the edge count when y is not gathered")
+        # scattered output has as many rows as x (uniform1d_forward.py:109)
+        self.n_out_rows = self.x_rows if self.scattered else self.n_edges
+        self.plan = graph_plan(dst, self.n_out_rows) if self.scattered else None
+        self.dtype = _dtype_str(w)
+        self.spec = make_spec(
+            _np(meta["i_list"]), _np(meta["j_list"]), _np(meta["k_list"]), _np(meta["v_list"]), _np(meta["coeff_list"], True),
+            w_segs=self.w_segs, x_segs=self.x_segs, y_segs=self.y_segs, out_segs=self.out_segs, u=self.u,
+            dtype=self.dtype, y_vec=self.y_vec, w_shared=self.w_shared, x_indexed=self.x_indexed,
+            y_indexed=self.y_indexed, scattered=self.scattered)
+
+    def graph(self, mod: _cabi.U1DModule, dev) -> _cabi.U1DGraph:
+        g = _cabi.U1DGraph()
+        g.n_edges, g.n_out_rows, g.x_rows, g.y_rows = self.n_edges, self.n_out_rows, self.x_rows, self.y_rows
+        g.x_index = self.src.data_ptr() if self.x_indexed else None
+        g.y_index = self.src.data_ptr() if self.y_indexed else None
+        if self.plan is not None:
+            g.seg_ptr = self.plan.seg_ptr.data_ptr()
+            g.perm = self.plan.perm.data_ptr() if self.plan.perm is not None else None
+            n_parts = max(1, min(_sm_count(dev) * int(mod.desc.ctas_per_sm), self.n_out_rows))
+            g.part_ptr = self.plan.partition(n_parts).data_ptr()
+            g.n_parts = n_parts
+        return g
+
+
+_META_CACHE: Dict[Tuple, np.ndarray] = {}
+
+
+def _np(t, is_float=False) -> np.ndarray:
+    """Host copy of a meta tensor (cached by storage identity: the tables are small and static)."""
+    if isinstance(t, torch.Tensor):
+        key = (t.data_ptr(), t.numel(), t._version, t.dtype, str(t.device))
+        a = _META_CACHE.get(key)
+        if a is None:
+            a = t.detach().cpu().numpy().astype(np.float64 if is_float else np.int64)
+            if len(_META_CACHE) > 512:
+                _META_CACHE.clear()
+            _META_CACHE[key] = a
+        return a
+    return np.asarray(t, dtype=np.float64 if is_float else np.int64)
+
+
+_CALL_CACHE: Dict[Tuple, U1DSpec] = {}
+
+
+def _run_fwd(call: _Call, w, x, y) -> torch.Tensor:
+    mod = get_module(call.spec, "fwd")
+    dev = x.device
+    out = torch.empty((call.n_out_rows, call.out_segs * call.u), dtype=x.dtype, device=dev)
+    with torch.cuda.device(dev):
+        g = call.graph(mod, dev)
+        mod.forward(g, w.data_ptr(), x.data_ptr(), y.data_ptr(), out.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+    return out
+
+
+def _run_bwd(call: _Call, grad_out, w, x, y, needs):
+    mod = get_module(call.spec, "bwd", needs)
+    dev = x.device
+    gw = torch.empty_like(w) if needs[0] else None
+    gx = torch.empty_like(x) if needs[1] else None
+    gy = torch.empty_like(y) if needs[2] else None
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    with torch.cuda.device(dev):
+        g = call.graph(mod, dev)
+        mod.backward(g, grad_out.data_ptr(), w.data_ptr(), x.data_ptr(), y.data_ptr(), ptr(gw), ptr(gx), ptr(gy),
+                     torch.cuda.current_stream(dev).cuda_stream)
+    return gw, gx, gy
+
+
+class FastUniform1dJITFunction(torch.autograd.Function):
+    """Autograd wrapper (reference: fasteq/ops/uniform1d_jit.py:3194-3326).  The backward
+    produces exactly the gradients autograd asks for; it is not itself differentiable."""
+
+    @staticmethod
+    def forward(ctx, w, x, y, input_indices, output_indices, meta):
+        _validate(w, x, y)
+        call = _Call(w, x, y, input_indices, output_indices, meta)
+        ctx.call = call
+        ctx.save_for_backward(w, x, y)
+        return _run_fwd(call, w, x, y)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        w, x, y = ctx.saved_tensors
+        needs = tuple(bool(n) for n in ctx.needs_input_grad[:3])
+        if not any(needs):
+            return None, None, None, None, None, None
+        grad_out = grad_out.contiguous()
+        gw, gx, gy = _run_bwd(ctx.call, grad_out, w, x, y, needs)
+        return gw, gx, gy, None, None, None
+
+
+def fast_uniform1d_jit(w, x, y, input_indices, output_indices, meta, use_multiwarp_candidates: Optional[bool] = None):
+    """See module docstring.  ``use_multiwarp_candidates`` is accepted and ignored, as in the reference."""
+    return FastUniform1dJITFunction.apply(w, x, y, input_indices, output_indices, meta)

@@ -1,0 +1,40 @@
+"""Compile the generated modules of the standard signatures ahead of time (no GPU needed)."""
+from __future__ import annotations
+
+import time
+from concurrent.futures import ThreadPoolExecutor
+
+from .codegen.u1d_common import make_spec
+from .descriptors import channelwise_tensor_product, full_channelwise_instructions
+from .irreps import Irreps
+
+# (irreps_in1, SH lmax, lmax_out, dtypes): BASELINE configs and the test / smoke signatures
+STANDARD_CWTP = [
+    ("128x0e+128x1o+128x2e", 3, 3, ("f32", "f64")),   # config 0
+    ("128x0e+128x1o", 3, 3, ("f32",)),                # config 1 interaction
+    ("64x0e+64x1o", 3, 3, ("f32", "f64")),
+    ("32x0e+32x1o", 2, 2, ("f32", "f64")),
+]
+
+
+def cwtp_spec(in1: str, lmax_sh: int, lmax_out: int, dtype: str):
+    sh = Irreps.spherical_harmonics(lmax_sh)
+    io, ins = full_channelwise_instructions(in1, sh, lmax_out)
+    d = channelwise_tensor_product(in1, sh, io, ins)
+    return make_spec(d.i_list, d.j_list, d.k_list, d.v_list, d.coeff_list, w_segs=d.w_seg_num, x_segs=d.x_seg_num,
+                     y_segs=d.y_seg_num, out_segs=d.out_seg_num, u=d.u_dim, dtype=dtype)
+
+
+def build_standard_modules(verbose: bool = False) -> None:
+    from .ops.uniform1d_jit import get_module
+    jobs = []
+    for in1, lsh, lout, dtypes in STANDARD_CWTP:
+        for dt in dtypes:
+            spec = cwtp_spec(in1, lsh, lout, dt)
+            jobs.append((spec, "fwd", (False, False, False)))
+            jobs.append((spec, "bwd", (True, True, True)))
+    t0 = time.time()
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        list(ex.map(lambda j: get_module(*j), jobs))
+    if verbose:
+        print(f"built {len(jobs)} Uniform1D modules in {time.time() - t0:.1f} s")

@@ -1,0 +1,121 @@
+/*
+ * fasteq_b200 -- C ABI of the B200 (sm_100a) kernels for the equivariant
+ * message-passing hot path.  Plain pointers and sizes only; every pointer is a
+ * DEVICE pointer unless its comment says "host".  All launches are asynchronous
+ * on the stream that is passed (a cudaStream_t cast to void*; NULL = default
+ * stream) of the CURRENT device.  Functions return a fasteq_status; no C++
+ * exception crosses this boundary (same contract as the reference's
+ * EqLinearBackendApi, fasteq/cuda/src/eqlinear/common/eqlinear_common.h:16-22).
+ *
+ * Two kinds of shared library export these symbols:
+ *   - libfasteq_b200_core.so : graph utilities, spherical harmonics, SO3Linear.
+ *   - one generated module per operator signature (fasteq_u1d_* / fasteq_stc_*):
+ *     the Clebsch-Gordan path table is compiled into the kernel, so each
+ *     signature is its own .so exporting the same symbol names.
+ */
+#ifndef FASTEQ_B200_H_
+#define FASTEQ_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FASTEQ_ABI_VERSION 1
+
+typedef enum fasteq_status {
+  FASTEQ_OK = 0,
+  FASTEQ_UNSUPPORTED = 1,   /* shape / mode this build does not implement */
+  FASTEQ_INVALID = 2,       /* bad argument (null pointer, negative size, misalignment) */
+  FASTEQ_CUDA_ERROR = 3,    /* a CUDA runtime call failed; see fasteq_last_cuda_error() */
+  FASTEQ_INTERNAL = 4,
+  FASTEQ_DEVICE_FAULT = 5   /* a kernel reported a bounded-wait timeout or an out-of-range index */
+} fasteq_status;
+
+typedef enum fasteq_dtype { FASTEQ_F32 = 0, FASTEQ_F64 = 1 } fasteq_dtype;
+
+typedef void* fasteq_stream_t;
+
+/* ------------------------------------------------------------------------- *
+ * Uniform1D (ChannelwiseTensorProduct) generated modules.
+ *
+ * Replaces the pybind `run(w, x, y, [src_idx], [dst_idx], V)` entry point of the
+ * reference's JIT modules (fasteq/ops/auto_schedule/uniform1d_forward.py:78-92,
+ * 172-245) and the backward `run(w, x, y, grad_out, [src], [dst], V)`
+ * (test/nequip_allegro_test/generated_uniform1d_bwd_lars.cu:246-324).
+ *
+ *   out[r_out, v, u] += c_p * w[r_w, i_p, u] * x[r_x, j_p, u] * y[r_y, k_p, u or 0]
+ *
+ * Tensors are contiguous [rows, segments, u].  Differences from the reference
+ * entry point, all on the caller's side of the boundary: outputs are allocated
+ * by the caller; the receiver index arrives as CSR segment offsets over
+ * receiver-sorted edges (seg_ptr, see fasteq_graph_build_csr) plus an optional
+ * permutation for unsorted input, instead of a raw dst index.
+ * ------------------------------------------------------------------------- */
+typedef struct fasteq_u1d_desc {
+  int32_t abi_version;
+  int32_t dtype;            /* fasteq_dtype */
+  int32_t u, w_segs, x_segs, y_segs, out_segs, num_paths;
+  int32_t y_vec;            /* 1: y is [rows, y_segs, u]; 0: y is [rows, y_segs, 1] */
+  int32_t w_shared;         /* 1: w has a single row */
+  int32_t x_indexed, y_indexed, scattered;
+  int32_t direction;        /* 0 forward module, 1 backward module */
+  int32_t need_gw, need_gx, need_gy;   /* backward modules: which gradients are produced */
+  int32_t ctas_per_sm;      /* resident CTAs per SM the kernel was built for (grid = SMs * ctas_per_sm) */
+  int32_t threads, smem_bytes;
+} fasteq_u1d_desc;
+
+typedef struct fasteq_u1d_graph {
+  int64_t n_edges;          /* rows of the per-edge operands */
+  int64_t n_out_rows;       /* rows of out (scattered: receivers; else == n_edges) */
+  int64_t x_rows, y_rows;   /* rows of x and y (bounds for the gather indices) */
+  const int32_t* x_index;   /* [n_edges] row of x per edge, or NULL (row = edge) */
+  const int32_t* y_index;   /* [n_edges] row of y per edge, or NULL */
+  const int32_t* seg_ptr;   /* [n_out_rows+1] CSR offsets into the receiver-sorted edge order (scattered only) */
+  const int32_t* perm;      /* [n_edges] edge id at each sorted position, or NULL when edges are already sorted */
+  const int32_t* part_ptr;  /* [n_parts+1] first segment (scattered) or first edge (else) of each CTA, or NULL = even split */
+  int32_t n_parts;
+} fasteq_u1d_graph;
+
+int fasteq_u1d_describe(fasteq_u1d_desc* out /* host */);
+
+/* out is fully overwritten (rows without edges become zero); no zero-fill needed. */
+int fasteq_u1d_forward(const fasteq_u1d_graph* g /* host */, const void* w, const void* x, const void* y,
+                       void* out, fasteq_stream_t stream);
+
+/* grad_w / grad_x / grad_y may be NULL when the module was built without that gradient.
+ * Gradients that are accumulated through an index (grad_x, grad_y when gathered, grad_w when
+ * shared, grad_y when u is tiled) are zero-filled by this call on `stream` before the kernel. */
+int fasteq_u1d_backward(const fasteq_u1d_graph* g /* host */, const void* grad_out, const void* w, const void* x,
+                        const void* y, void* grad_w, void* grad_x, void* grad_y, fasteq_stream_t stream);
+
+/* Reads and clears the device-side status word of this module (synchronises the device).
+ * 0 = no fault; otherwise the code of the first fault (1 wait timeout, 2 index out of range). */
+int fasteq_u1d_device_status(int32_t* code /* host */);
+
+/* ------------------------------------------------------------------------- *
+ * Core library.
+ * ------------------------------------------------------------------------- */
+const char* fasteq_status_string(int status);
+const char* fasteq_last_cuda_error(void);
+int fasteq_core_abi_version(void);
+
+/* sorted_flag[0] (device int32) <- 1 if dst is non-decreasing else 0. */
+int fasteq_graph_check_sorted(const int32_t* dst, int64_t n_edges, int32_t* sorted_flag, fasteq_stream_t stream);
+
+/* CSR offsets of a non-decreasing receiver index: seg_ptr[r] = first position with dst >= r,
+ * seg_ptr[n_rows] = n_edges.  The reference scatters with atomicAdd on the raw dst index
+ * (fasteq/ops/auto_schedule/uniform1d_forward.py:351-356) and has no counterpart. */
+int fasteq_graph_build_csr(const int32_t* dst_sorted, int64_t n_edges, int64_t n_rows, int32_t* seg_ptr,
+                           fasteq_stream_t stream);
+
+/* Split segments into n_parts contiguous ranges of about equal edge count:
+ * part_ptr[p] = first segment whose start is >= p * n_edges / n_parts. */
+int fasteq_graph_partition(const int32_t* seg_ptr, int64_t n_rows, int64_t n_edges, int32_t n_parts,
+                           int32_t* part_ptr, fasteq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FASTEQ_B200_H_ */
