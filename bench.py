@@ -1,0 +1,332 @@
+#!/usr/bin/env python
+"""Benchmark of the ChannelwiseTensorProduct hot path (forward + force backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One step = one forward + one backward (grad_w, grad_x, grad_y) of the fused
+gather / tensor-product / scatter operator over one synthetic batch.  Default
+workload: the interaction of BASELINE config 1 -- 64 periodic boxes x 192 atoms
+(cutoff 5 A, ~52 neighbours), hidden 128x0e+128x1o (x) SH l<=3 -> all paths l<=3,
+FP32, per-edge weights materialised.  With N > 1 every rank processes its own
+batch of whole structures (no data-path collective): weak scaling.
+
+Prints ONE JSON line (rank 0).  ``value`` is edges/s with inputs resident in HBM,
+``e2e`` the same through the public operator with pinned-host inputs copied in
+and a scalar result copied out every step, ``roofline`` the dominant kernel's
+algorithmic bytes / CUDA-event time against the measured copy bandwidth,
+``cpu_baseline`` the CPU oracle (e3nn algorithm, torch CPU, all host threads)
+on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+import torch
+
+WORKLOADS = {
+    # name: (irreps_in1, SH lmax, lmax_out, boxes per GPU, dtype)
+    "config1_cwtp": ("128x0e+128x1o", 3, 3, 64, torch.float32),
+    "config0_layout_cwtp": ("128x0e+128x1o+128x2e", 3, 3, 64, torch.float32),
+}
+METRIC = "ChannelwiseTP edges/s (fwd+force bwd)"
+
+
+def algorithmic_bytes(N, E, d, s):
+    """Each logical tensor once (unique node rows, per-edge tensors, outputs, indices)."""
+    U = d.u_dim
+    fwd = s * (N * d.x_seg_num * U + E * d.w_seg_num * U + E * d.y_seg_num + N * d.out_seg_num * U) + 8 * E
+    bwd = s * (2 * E * d.w_seg_num * U + 2 * N * d.x_seg_num * U + 2 * E * d.y_seg_num + N * d.out_seg_num * U) + 8 * E
+    return fwd, bwd
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_inputs(workload: str, seed: int, n_boxes=None):
+    from fasteq_b200.descriptors import channelwise_tensor_product, full_channelwise_instructions
+    from fasteq_b200.graph import config1_batch
+    from fasteq_b200.irreps import Irreps
+    in1, lsh, lout, boxes, dtype = WORKLOADS[workload]
+    sh = Irreps.spherical_harmonics(lsh)
+    io, ins = full_channelwise_instructions(in1, sh, lout)
+    d = channelwise_tensor_product(in1, sh, io, ins)
+    batch = config1_batch(n_boxes or boxes, seed=seed)
+    g = torch.Generator().manual_seed(seed)
+    N, E, U = batch.n_nodes, batch.n_edges, d.u_dim
+    vec = torch.from_numpy(batch.edge_vec)
+    return dict(d=d, ins=ins, irreps=(in1, str(sh), str(io)), batch=batch, N=N, E=E, dtype=dtype, vec=vec,
+                x=torch.randn(N, d.x_seg_num * U, generator=g, dtype=dtype),
+                w=torch.randn(E, d.w_seg_num * U, generator=g, dtype=dtype),
+                r=torch.randn(N, d.out_seg_num * U, generator=g, dtype=dtype),
+                src=torch.from_numpy(batch.edge_src).int(), dst=torch.from_numpy(batch.edge_dst).int())
+
+
+def cpu_reference_run(inp, steps: int, warmup: int, threads: int):
+    """e3nn-algorithm CPU oracle: scatter(tp(x[src], sh, w), dst) forward + autograd backward (mul_ir layout)."""
+    from fasteq_b200.irreps import Irreps, ir_mul_to_mul_ir
+    from oracle import e3nn_uvu_ref, sh_ref
+    torch.set_num_threads(threads)
+    d = inp["d"]
+    in1, in2, io = inp["irreps"]
+    dt = inp["dtype"]
+    tp = e3nn_uvu_ref.TensorProductUVU(in1, in2, io, inp["ins"], dtype=dt)
+    x = ir_mul_to_mul_ir(inp["x"], Irreps(in1)).requires_grad_(True)
+    y = sh_ref.spherical_harmonics(Irreps(in2).lmax, inp["vec"].to(dt), normalize=True).requires_grad_(True)
+    w = inp["w"].clone().requires_grad_(True)
+    r = ir_mul_to_mul_ir(inp["r"], Irreps(io))
+    src, dst = inp["src"].long(), inp["dst"].long()
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        out = e3nn_uvu_ref.tp_scatter(tp, x, y, w, dst, src, inp["N"])
+        torch.autograd.grad((out * r).sum(), (w, x, y))
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    return inp["E"] * len(times) / sum(times), float(np.mean(times))
+
+
+def reference_arm(args):
+    """The reference's CPU path (e3nn algorithm, restated in oracle/) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = len(os.sched_getaffinity(0))
+    inp = build_inputs(args.workload, seed=0, n_boxes=1)
+    eps, sec = cpu_reference_run(inp, max(1, args.steps), max(0, args.warmup), threads)
+    in1, lsh, lout, boxes, dtype = WORKLOADS[args.workload]
+    sample = f"1 of {boxes} boxes per step ({inp['N']} atoms, {inp['E']} edges), forward + autograd backward"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": eps, "unit": "edges/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32" if dtype == torch.float32 else "f64", "data": "synthetic",
+        "config": config_dict(args.workload, inp, args.gpus),
+        "cpu_baseline": {"value": eps, "unit": "edges/s", "cores": threads, "kind": "port", "sample": sample,
+                         "torch_threads": torch.get_num_threads(), "os_cpu_count": os.cpu_count()},
+        "e2e": {"value": eps, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(workload, inp, n_gpus):
+    in1, lsh, lout, boxes, dtype = WORKLOADS[workload]
+    d = inp["d"]
+    return {"workload": workload, "irreps_in1": in1, "sh_lmax": lsh, "lmax_out": lout, "u": d.u_dim,
+            "w_segs": d.w_seg_num, "out_segs": d.out_seg_num, "cg_paths": d.num_paths,
+            "boxes_per_gpu": boxes, "atoms_per_box": 192, "box_side_A": 12.4, "cutoff_A": 5.0,
+            "parallelism": f"whole-structure split, {n_gpus} rank(s), no data-path collective",
+            "l2_policy": "inputs larger than L2 (per-edge weights alone are several GB)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="config1_cwtp", choices=sorted(WORKLOADS))
+    ap.add_argument("--boxes", type=int, default=None, help="boxes per GPU (default: the workload's)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    from fasteq_b200.ops import fast_uniform1d_jit
+    from fasteq_b200.ops import uniform1d_jit as u1d
+    from fasteq_b200.sh import spherical_harmonics_host
+
+    inp = build_inputs(args.workload, seed=rank, n_boxes=args.boxes)
+    d, N, E, dtype = inp["d"], inp["N"], inp["E"], inp["dtype"]
+    s = 4 if dtype == torch.float32 else 8
+    y_host = torch.from_numpy(spherical_harmonics_host(3, inp["vec"].numpy(), normalize=True)).to(dtype).contiguous()
+    meta = d.meta(dtype, dev)
+    host = {k: inp[k].contiguous().pin_memory() for k in ("w", "x", "r", "src", "dst")}
+    host["y"] = y_host.pin_memory()
+    devt = {k: v.to(dev) for k, v in host.items()}
+    w, x, y = (devt[k].requires_grad_(True) for k in ("w", "x", "y"))
+    inp_idx, out_idx = {1: devt["src"]}, {0: devt["dst"]}
+
+    def step():
+        out = fast_uniform1d_jit(w, x, y, inp_idx, out_idx, meta)
+        return torch.autograd.grad(out, (w, x, y), devt["r"])
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        ev0.record()
+        for _ in range(args.steps):
+            step()
+        ev1.record()
+        barrier()
+    ms = ev0.elapsed_time(ev1)
+    t = torch.tensor([ms, float(E)], dtype=torch.float64, device=dev)
+    if dist is not None:
+        tmax = t.clone(); dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone(); dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        ms, total_edges = float(tmax[0]), float(tsum[1])
+    else:
+        total_edges = float(E)
+    value = total_edges * args.steps / (ms * 1e-3)
+
+    # ---- per-kernel timing for the roofline (rank 0's kernels, CUDA events on the launch stream)
+    call = u1d._Call(w, x, y, inp_idx, out_idx, meta)
+    k = max(3, args.steps)
+    def timed(fn):
+        fn(); torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(k):
+            fn()
+        b.record(); torch.cuda.synchronize()
+        return a.elapsed_time(b) / k * 1e-3
+    with torch.no_grad():
+        t_fwd = timed(lambda: u1d._run_fwd(call, w, x, y))
+        t_bwd = timed(lambda: u1d._run_bwd(call, devt["r"], w, x, y, (True, True, True)))
+    bytes_fwd, bytes_bwd = algorithmic_bytes(N, E, d, s)
+    peak, peak_kind = measured_peak()
+    roof = {"bound": "hbm", "kernel": "fasteq_u1d_bwd_kernel", "achieved": bytes_bwd / t_bwd / 1e9, "peak": peak,
+            "unit": "GB/s", "frac": bytes_bwd / t_bwd / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
+            "algorithmic_bytes_per_launch": bytes_bwd, "launch_ms": t_bwd * 1e3}
+    roof_fwd = {"bound": "hbm", "kernel": "fasteq_u1d_fwd_kernel", "achieved": bytes_fwd / t_fwd / 1e9, "peak": peak,
+                "unit": "GB/s", "frac": bytes_fwd / t_fwd / 1e9 / peak, "algorithmic_bytes_per_launch": bytes_fwd,
+                "launch_ms": t_fwd * 1e3}
+    roof_both = {"achieved": (bytes_fwd + bytes_bwd) / (t_fwd + t_bwd) / 1e9,
+                 "frac": (bytes_fwd + bytes_bwd) / (t_fwd + t_bwd) / 1e9 / peak,
+                 "edges_per_s_kernels_only": E / (t_fwd + t_bwd)}
+
+    # ---- end to end: pinned host inputs in, scalar out, through the public operator
+    e2e = None
+    if not args.no_e2e:
+        ke = max(2, min(args.steps, 5))
+        h2d = sum(host[n].numel() * host[n].element_size() for n in ("w", "x", "y", "r", "src", "dst"))
+        def e2e_step():
+            dv = {n: host[n].to(dev, non_blocking=True) for n in ("w", "x", "y", "r", "src", "dst")}
+            ww, xx, yy = (dv[n].requires_grad_(True) for n in ("w", "x", "y"))
+            out = fast_uniform1d_jit(ww, xx, yy, {1: dv["src"]}, {0: dv["dst"]}, meta)
+            gw, gx, gy = torch.autograd.grad(out, (ww, xx, yy), dv["r"])
+            return float((out.sum() + gw.sum() + gx.sum() + gy.sum()).item())
+        e2e_step(); barrier()
+        t0 = time.perf_counter()
+        for _ in range(ke):
+            e2e_step()
+        barrier()
+        te = time.perf_counter() - t0
+        tt = torch.tensor([te], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e = {"value": total_edges * ke / float(tt[0]), "unit": "edges/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": 8, "steps": ke,
+               "note": "pinned host w/x/y/grad_out/indices copied in each step (PCIe-bound: per-edge weights dominate)"}
+
+    status = {name: m.device_status() for name, m in (("fwd", u1d.get_module(call.spec, "fwd")),
+                                                      ("bwd", u1d.get_module(call.spec, "bwd", (True, True, True))))}
+
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline:
+        threads = len(os.sched_getaffinity(0))
+        small = build_inputs(args.workload, seed=0, n_boxes=1)
+        eps, sec = cpu_reference_run(small, steps=2, warmup=1, threads=threads)
+        cpu = {"value": eps, "unit": "edges/s", "cores": threads, "kind": "port",
+               "sample": f"1 box ({small['N']} atoms, {small['E']} edges), 2 timed forward+backward passes of the e3nn-algorithm oracle",
+               "torch_threads": torch.get_num_threads(), "os_cpu_count": os.cpu_count()}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32" if dtype == torch.float32 else "f64", "data": "synthetic",
+            "config": dict(config_dict(args.workload, inp, world), atoms_per_gpu=N, edges_per_gpu=E),
+            "roofline": roof, "roofline_fwd": roof_fwd, "roofline_fwd_bwd": roof_both, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": 2 * args.steps, "clocks": clocks.summary(), "device_status": status,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

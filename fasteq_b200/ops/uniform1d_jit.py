@@ -193,11 +193,22 @@ class _Call:
         self.n_out_rows = self.x_rows if self.scattered else self.n_edges
         self.plan = graph_plan(dst, self.n_out_rows) if self.scattered else None
         self.dtype = _dtype_str(w)
-        self.spec = make_spec(
-            _np(meta["i_list"]), _np(meta["j_list"]), _np(meta["k_list"]), _np(meta["v_list"]), _np(meta["coeff_list"], True),
-            w_segs=self.w_segs, x_segs=self.x_segs, y_segs=self.y_segs, out_segs=self.out_segs, u=self.u,
-            dtype=self.dtype, y_vec=self.y_vec, w_shared=self.w_shared, x_indexed=self.x_indexed,
-            y_indexed=self.y_indexed, scattered=self.scattered)
+        skey = tuple((id(meta[k]), getattr(meta[k], "_version", 0)) for k in ("i_list", "j_list", "k_list", "v_list", "coeff_list")) + (
+            self.w_segs, self.x_segs, self.y_segs, self.out_segs, self.u, self.dtype, self.y_vec, self.w_shared,
+            self.x_indexed, self.y_indexed, self.scattered)
+        hit = _SPEC_CACHE.get(skey)
+        if hit is None:
+            spec = make_spec(
+                _np(meta["i_list"]), _np(meta["j_list"]), _np(meta["k_list"]), _np(meta["v_list"]), _np(meta["coeff_list"], True),
+                w_segs=self.w_segs, x_segs=self.x_segs, y_segs=self.y_segs, out_segs=self.out_segs, u=self.u,
+                dtype=self.dtype, y_vec=self.y_vec, w_shared=self.w_shared, x_indexed=self.x_indexed,
+                y_indexed=self.y_indexed, scattered=self.scattered)
+            if len(_SPEC_CACHE) > 256:
+                _SPEC_CACHE.clear()
+            # the entry holds the table objects so their ids stay unique while it exists
+            hit = (spec, [meta[k] for k in ("i_list", "j_list", "k_list", "v_list", "coeff_list")])
+            _SPEC_CACHE[skey] = hit
+        self.spec = hit[0]
 
     def graph(self, mod: _cabi.U1DModule, dev) -> _cabi.U1DGraph:
         g = _cabi.U1DGraph()
@@ -213,24 +224,26 @@ class _Call:
         return g
 
 
-_META_CACHE: Dict[Tuple, np.ndarray] = {}
+_META_CACHE: Dict[Tuple, Tuple[torch.Tensor, np.ndarray]] = {}
 
 
 def _np(t, is_float=False) -> np.ndarray:
-    """Host copy of a meta tensor (cached by storage identity: the tables are small and static)."""
+    """Host copy of a meta tensor.  Cached by storage identity; the cache keeps the tensor alive,
+    so its address cannot be handed to another tensor while the entry exists."""
     if isinstance(t, torch.Tensor):
         key = (t.data_ptr(), t.numel(), t._version, t.dtype, str(t.device))
-        a = _META_CACHE.get(key)
-        if a is None:
+        hit = _META_CACHE.get(key)
+        if hit is None:
             a = t.detach().cpu().numpy().astype(np.float64 if is_float else np.int64)
             if len(_META_CACHE) > 512:
                 _META_CACHE.clear()
-            _META_CACHE[key] = a
-        return a
+            _META_CACHE[key] = (t, a)
+            return a
+        return hit[1]
     return np.asarray(t, dtype=np.float64 if is_float else np.int64)
 
 
-_CALL_CACHE: Dict[Tuple, U1DSpec] = {}
+_SPEC_CACHE: Dict[Tuple, U1DSpec] = {}
 
 
 def _run_fwd(call: _Call, w, x, y) -> torch.Tensor:
