@@ -250,8 +250,8 @@ extern "C" int fasteq_u1d_forward(const fasteq_u1d_graph* gh, const void* w, con
   Graph g; int grid = 1;
   int rc = fill_graph(gh, &g, &grid, {tun.min_blocks});
   if (rc != FASTEQ_OK) return rc;
-  if (!w || !x || !y || !out) return (gh->n_edges == 0 && gh->n_out_rows == 0) ? FASTEQ_OK : FASTEQ_INVALID;
   if (gh->n_out_rows == 0 && gh->n_edges == 0) return FASTEQ_OK;
+  if (!out || (gh->n_edges > 0 && (!w || !x || !y))) return FASTEQ_INVALID;
   g.bulk_ok = aligned16(w) && aligned16(x) && aligned16(y) && ((U * sizeof(T)) % 16 == 0) && ((CT * sizeof(T)) % 16 == 0);
   cudaError_t e = cudaFuncSetAttribute(fasteq_u1d_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return cuda_fail(e);
