@@ -26,33 +26,50 @@ from .u1d_common import U1DSpec, Block, build_blocks, lit, split_out_segments
 
 @dataclass(frozen=True)
 class Tuning:
-    ct: int            # channels per tile (= consumer threads per group), multiple of 32
+    ct: int            # channels per tile, multiple of 32 * vec
     groups: int        # thread groups that split the output segments (forward only)
     stages: int
     min_blocks: int    # CTAs per SM targeted by __launch_bounds__
+    vec: int = 1       # channels per thread: 2 = packed f32x2 arithmetic (FP32, even u)
+    two_pass: bool = False  # backward: evaluate a block once for grad_w and once for grad_x / grad_y
+    pipes: int = 1     # independent producer/consumer pipelines per CTA (keeps all four SM sub-partitions busy)
 
 
 def default_tuning(spec: U1DSpec, direction: str) -> Tuning:
-    ct = min((spec.u + 31) // 32 * 32, 128 if spec.dtype == "f32" else 64)
-    if spec.u % ct != 0 and spec.u > ct:
-        # keep tiles uniform when possible
+    """Defaults from sweeps on B200 (128-channel FP32 signatures with 55 and 106 output segments).
+
+    Forward: one channel per thread, the receiver row in registers; two thread groups split the
+    output segments when there are too many for one thread.  Backward: packed two-channel
+    arithmetic with two pipelines per CTA when the channel count allows, else one channel per thread."""
+    f32 = spec.dtype == "f32"
+    cap = 128 if f32 else 64
+    ct = min((spec.u + 31) // 32 * 32, cap)
+    if spec.u > ct and spec.u % ct != 0:
         for cand in (128, 96, 64, 32):
             if cand <= ct and spec.u % cand == 0:
                 ct = cand
                 break
+    big = spec.out_segs > 64
     if direction == "fwd":
-        groups = 2 if spec.out_segs >= 32 else 1
-        return Tuning(ct=ct, groups=groups, stages=4, min_blocks=2)
+        if f32:
+            return Tuning(ct=ct, groups=2 if big else 1, stages=8, min_blocks=1 if big else 3)
+        return Tuning(ct=ct, groups=1, stages=4, min_blocks=2)
+    if f32 and spec.u % 128 == 0:
+        return Tuning(ct=128, groups=1, stages=3, min_blocks=1 if big else 2, vec=2, pipes=2)
+    if f32:
+        return Tuning(ct=ct, groups=1, stages=3, min_blocks=2 if big else 3)
     return Tuning(ct=ct, groups=1, stages=3, min_blocks=2)
 
 
 def _cfg(spec: U1DSpec, tun: Tuning, extra_bytes: int, ncons_warps: int, emit_empty: bool = True) -> str:
     b = lambda v: "true" if v else "false"
+    vtype = "float2" if tun.vec == 2 else spec.ctype
     return f"""namespace cfg {{
 using T = {spec.ctype};
+using V = {vtype};   // what one thread carries per segment: one channel, or two packed FP32 channels
 constexpr int U = {spec.u}, CT = {tun.ct}, WSEG = {spec.w_segs}, XSEG = {spec.x_segs}, YSEG = {spec.y_segs}, OSEG = {spec.out_segs};
-constexpr int STAGES = {tun.stages}, GROUPS = {tun.groups}, NCONS_WARPS = {ncons_warps}, STAGE_EXTRA_BYTES = {extra_bytes};
-constexpr bool EMIT_EMPTY_ROWS = {b(emit_empty)};
+constexpr int STAGES = {tun.stages}, GROUPS = {tun.groups}, PIPES = {tun.pipes}, NCONS_WARPS = {ncons_warps}, STAGE_EXTRA_BYTES = {extra_bytes};
+constexpr bool EMIT_EMPTY_ROWS = {b(emit_empty)}, BEGIN_PER_SEGMENT = {b(not emit_empty)};
 constexpr bool Y_VEC = {b(spec.y_vec)}, W_SHARED = {b(spec.w_shared)}, X_INDEXED = {b(spec.x_indexed)}, Y_INDEXED = {b(spec.y_indexed)}, SCATTERED = {b(spec.scattered)};
 }}  // namespace cfg
 """
@@ -90,11 +107,12 @@ static int fill_graph(const fasteq_u1d_graph* g, fasteq::u1d::Graph* o, int* gri
   e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) return cuda_fail(e);
   const long long units = cfg::SCATTERED ? g->n_out_rows : g->n_edges;
-  long long want = (long long)sms * ctas_per_sm;
+  long long want = (long long)sms * ctas_per_sm * cfg::PIPES;   // pipelines
   if (g->part_ptr) want = g->n_parts;
   else if (want > units) want = units;
   if (want < 1) want = 1;
-  *grid = (int)want;
+  o->n_vblocks = (int)want;
+  *grid = (int)((want + cfg::PIPES - 1) / cfg::PIPES);
   return FASTEQ_OK;
 }
 
@@ -117,7 +135,8 @@ def _prelude(spec: U1DSpec, tun: Tuning, extra_bytes: int, ncons_warps: int, emi
     return ("// Generated by fasteq_b200.codegen.u1d -- do not edit.\n"
             "#include <cstdio>\n#include <cstdint>\n#include <cuda_runtime.h>\n"
             '#include "fasteq_b200.h"\n' + _cfg(spec, tun, extra_bytes, ncons_warps, emit_empty) +
-            '#include "u1d_pipeline.cuh"\nusing namespace fasteq;\nusing namespace fasteq::u1d;\n')
+            '#include "u1d_pipeline.cuh"\nusing namespace fasteq;\nusing namespace fasteq::u1d;\n'
+            "using V = cfg::V;\nusing VS = VT<V>;\nconstexpr int VEC = VS::N;\nconstexpr int TPG = CT / VEC;  // threads per group\n")
 
 
 def _describe(spec: U1DSpec, tun: Tuning, direction: int, needs=(0, 0, 0), threads=0) -> str:
@@ -129,60 +148,132 @@ extern "C" int fasteq_u1d_describe(fasteq_u1d_desc* d) {{
   d->num_paths = {len(spec.paths)}; d->y_vec = {int(spec.y_vec)}; d->w_shared = {int(spec.w_shared)};
   d->x_indexed = {int(spec.x_indexed)}; d->y_indexed = {int(spec.y_indexed)}; d->scattered = {int(spec.scattered)};
   d->direction = {direction}; d->need_gw = {needs[0]}; d->need_gx = {needs[1]}; d->need_gy = {needs[2]};
-  d->ctas_per_sm = {tun.min_blocks}; d->threads = {threads}; d->smem_bytes = SMEM_BYTES;
+  d->ctas_per_sm = {tun.min_blocks * tun.pipes}; d->threads = {threads}; d->smem_bytes = SMEM_BYTES;
   return FASTEQ_OK;
 }}
 """
 
 
+def _check_tuning(spec: U1DSpec, tun: Tuning) -> None:
+    if tun.vec not in (1, 2):
+        raise ValueError("vec must be 1 or 2")
+    if tun.vec == 2 and (spec.dtype != "f32" or spec.u % 2):
+        raise ValueError("packed arithmetic needs FP32 and an even channel count")
+    if tun.ct % (32 * tun.vec):
+        raise ValueError("ct must be a multiple of 32 * vec")
+
+
+def _vlit(c: float, dtype: str) -> str:
+    return f"VS::bc({lit(c, dtype)})"
+
+
+def _sum_expr(items, dtype: str) -> List[str]:
+    """Statements computing ``t = sum c * p_j_k`` with fused multiply-adds."""
+    out = []
+    for n, (j, k, c) in enumerate(items):
+        if n == 0:
+            out.append(f"V t = p_{j}_{k};" if c == 1.0 else f"V t = vmul({_vlit(c, dtype)}, p_{j}_{k});")
+        else:
+            out.append(f"t = vfma({_vlit(c, dtype)}, p_{j}_{k}, t);")
+    return out
+
+
+def _load_xy(spec: U1DSpec, ind: str) -> List[str]:
+    L = [f"{ind}const V x{j} = VS::ld(sx + {j} * CT);" for j in range(spec.x_segs)]
+    if spec.y_vec:
+        L += [f"{ind}const V y{k} = VS::ld(sy + {k} * CT);" for k in range(spec.y_segs)]
+    else:
+        L += [f"{ind}const V y{k} = VS::bc(sy[{k}]);" for k in range(spec.y_segs)]
+    return L
+
+
 # --------------------------------------------------------------------------- forward
+
+def _diagonal_runs(terms) -> Dict[Tuple[int, int, float], List[Tuple[int, int]]]:
+    """For a block whose terms all have one product: (i, j, c) -> [(k, v), ...].  Such a block (an
+    l1 = 0 or l2 = 0 coupling) needs one multiply ``c * w[i] * x[j]`` per run and one FMA per output."""
+    runs: Dict[Tuple[int, int, float], List[Tuple[int, int]]] = {}
+    for t in terms:
+        (j, k, c), = t.items
+        runs.setdefault((t.i, j, c), []).append((k, t.v))
+    return runs
+
+
+def _is_diagonal(terms) -> bool:
+    return bool(terms) and all(len(t.items) == 1 for t in terms)
+
 
 def _emit_block_fwd(spec: U1DSpec, b: Block, owned: set, slot_of: Dict[int, int], ind: str) -> List[str]:
     terms = [t for t in b.terms if t.v in owned]
     if not terms:
         return []
+    if _is_diagonal(terms):
+        L = [ind + "{"]
+        for (i, j, c), kv in _diagonal_runs(terms).items():
+            sexpr = f"vmul(W({i}), x{j})" if c == 1.0 else f"vmul(vmul({_vlit(c, spec.dtype)}, W({i})), x{j})"
+            L.append(f"{ind}  {{ const V s = {sexpr};")
+            for k, v in kv:
+                L.append(f"{ind}    acc{slot_of[v]} = vfma(s, y{k}, acc{slot_of[v]});")
+            L.append(f"{ind}  }}")
+        L.append(ind + "}")
+        return L
     used = sorted({(j, k) for t in terms for j, k, _ in t.items})
     L = [ind + "{"]
     for (j, k) in used:
-        L.append(f"{ind}  const T p_{j}_{k} = x{j} * y{k};")
+        L.append(f"{ind}  const V p_{j}_{k} = vmul(x{j}, y{k});")
     for t in terms:
-        expr = " + ".join(f"{lit(c, spec.dtype)} * p_{j}_{k}" for j, k, c in t.items)
-        L.append(f"{ind}  acc[{slot_of[t.v]}] += W({t.i}) * ({expr});")
+        L.append(f"{ind}  {{ " + " ".join(_sum_expr(t.items, spec.dtype)) + f" acc{slot_of[t.v]} = vfma(W({t.i}), t, acc{slot_of[t.v]}); }}")
     L.append(ind + "}")
     return L
 
 
 def emit_forward(spec: U1DSpec, tun: Tuning) -> str:
+    _check_tuning(spec, tun)
     blocks = build_blocks(spec)
     G = tun.groups
     owners = split_out_segments(blocks, spec.out_segs, G)
     max_slots = max(1, max(len(o) for o in owners))
-    ncons_warps = G * tun.ct // 32
-    threads = G * tun.ct + 32
+    tpg = tun.ct // tun.vec
+    ncons_warps = G * tpg // 32
+    threads = tun.pipes * (G * tpg + 32)
     src = [_prelude(spec, tun, 0, ncons_warps)]
+    acc_decl = " ".join(f"V acc{s_} = VS::zero();" for s_ in range(max_slots))
+    wdef = ("#define W(i) VS::ld(w + (size_t)(i) * U + m.ct * CT + ch)" if spec.w_shared
+            else "#define W(i) VS::ld(sw + (i) * CT)")
     src.append(f"""
 constexpr int NTHREADS = {threads};
-constexpr int W_SHARED_BYTES = cfg::W_SHARED ? WSEG * CT * (int)sizeof(T) : 0;
-constexpr int SMEM_BYTES = BAR_BYTES + STAGES * STAGE_BYTES + W_SHARED_BYTES;
+constexpr int PIPE_BYTES = BAR_BYTES + STAGES * STAGE_BYTES;
+constexpr int SMEM_BYTES = cfg::PIPES * PIPE_BYTES;
 
 __global__ void __launch_bounds__(NTHREADS, {tun.min_blocks})
 fasteq_u1d_fwd_kernel(const Graph g, const T* __restrict__ w, const T* __restrict__ x, const T* __restrict__ y,
                       T* __restrict__ out) {{
-  extern __shared__ __align__(128) unsigned char smem[];
+  extern __shared__ __align__(128) unsigned char smem_all[];
+  if (threadIdx.x == 0) {{
+    for (int p = 0; p < cfg::PIPES; ++p) {{
+      uint64_t* f = reinterpret_cast<uint64_t*>(smem_all + (size_t)p * PIPE_BYTES);
+      init_barriers(f, f + STAGES, g.bulk_ok);
+    }}
+    mbar_fence_init();
+  }}
+  __syncthreads();
+  // warps [0, PIPES * NCONS_WARPS) consume, the last PIPES warps produce; pipeline p owns consumer
+  // warps [p * NCONS_WARPS, (p + 1) * NCONS_WARPS) and producer warp PIPES * NCONS_WARPS + p
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool is_producer = warp >= cfg::PIPES * cfg::NCONS_WARPS;
+  const int pipe = is_producer ? warp - cfg::PIPES * cfg::NCONS_WARPS : warp / cfg::NCONS_WARPS;
+  unsigned char* smem = smem_all + (size_t)pipe * PIPE_BYTES;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + STAGES;
   unsigned char* stages = smem + BAR_BYTES;
-  init_barriers(full, empty);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (warp == cfg::NCONS_WARPS) {{
-    Producer p{{g, w, x, y, stages, full, empty, lane, 0u}};
-    p.run([](unsigned char*, int) {{}}, [](int, int, int) {{}});
+  if (is_producer) {{
+    Producer p{{g, w, x, y, stages, full, empty, lane, 0u, (int)blockIdx.x * cfg::PIPES + pipe}};
+    p.run([](unsigned char*) {{}}, [](int, int, int) {{}});
     return;
   }}
-  const int grp = threadIdx.x / CT, ch = threadIdx.x % CT;
-  T acc[{max_slots}];
-#pragma unroll
-  for (int s = 0; s < {max_slots}; ++s) acc[s] = T(0);
+  const int ptid = threadIdx.x - pipe * cfg::NCONS_WARPS * 32;   // thread index inside the pipeline
+  const int grp = ptid / TPG, ch = (ptid % TPG) * VEC;
+  {acc_decl}
   uint32_t it = 0;
   for (;;) {{
     const int stage = it % STAGES;
@@ -190,50 +281,34 @@ fasteq_u1d_fwd_kernel(const Graph g, const T* __restrict__ w, const T* __restric
     mbar_wait(&full[stage], ph, g.status);
     const unsigned char* st = stages + (size_t)stage * STAGE_BYTES;
     const Meta m = *reinterpret_cast<const Meta*>(st + OFF_META);
-    const int valid = (U - m.ct * CT) < CT ? (U - m.ct * CT) : CT;
+    const int valid = (U % CT == 0) ? CT : ((U - m.ct * CT) < CT ? (U - m.ct * CT) : CT);
     const bool live = ch < valid;
     if ((m.flags & F_DATA) && live) {{
-      const T* sw = reinterpret_cast<const T*>(st + OFF_W) + ch;
+      const T* sw = reinterpret_cast<const T*>(st + OFF_W) + ch; (void)sw;
       const T* sx = reinterpret_cast<const T*>(st + OFF_X) + ch;
       const T* sy = reinterpret_cast<const T*>(st + OFF_Y){' + ch' if spec.y_vec else ''};
-#define W(i) sw[(i) * CT]
+{wdef}
 """)
-    # shared weights are read straight from global memory (one row for the whole launch, L1/L2 resident)
-    if spec.w_shared:
-        src[-1] = src[-1].replace("#define W(i) sw[(i) * CT]", "#define W(i) __ldg(w + (size_t)(i) * U + m.ct * CT + ch)")
-        src[-1] = src[-1].replace("      const T* sw = reinterpret_cast<const T*>(st + OFF_W) + ch;\n", "")
-    body = []
-    for j in range(spec.x_segs):
-        body.append(f"      const T x{j} = sx[{j} * CT];")
-    if spec.y_vec:
-        for k in range(spec.y_segs):
-            body.append(f"      const T y{k} = sy[{k} * CT];")
-    else:
-        for k in range(spec.y_segs):
-            body.append(f"      const T y{k} = sy[{k}];")
+    body = _load_xy(spec, "      ")
     for gi in range(G):
         owned = set(owners[gi])
         slot_of = {v: s for s, v in enumerate(owners[gi])}
-        cond = f"      if (grp == {gi}) {{" if G > 1 else "      {"
-        body.append(cond)
+        body.append(f"      if (grp == {gi}) {{" if G > 1 else "      {")
         for b in blocks:
             body += _emit_block_fwd(spec, b, owned, slot_of, "        ")
         body.append("      }")
     body.append("#undef W")
     body.append("    }")
-    # store on the last edge of a segment
     body.append("    if (m.flags & F_LAST) {")
     body.append("      if (live) {")
     body.append("        T* o = out + (size_t)m.row * OSEG * U + (size_t)m.ct * CT + ch;")
     for gi in range(G):
-        cond = f"        if (grp == {gi}) {{" if G > 1 else "        {"
-        body.append(cond)
+        body.append(f"        if (grp == {gi}) {{" if G > 1 else "        {")
         for s, v in enumerate(owners[gi]):
-            body.append(f"          o[{v} * U] = acc[{s}];")
+            body.append(f"          VS::st(o + {v} * U, acc{s});")
         body.append("        }")
     body.append("      }")
-    body.append("#pragma unroll")
-    body.append(f"      for (int s = 0; s < {max_slots}; ++s) acc[s] = T(0);")
+    body.append("      " + " ".join(f"acc{s_} = VS::zero();" for s_ in range(max_slots)))
     body.append("    }")
     body.append("    __syncwarp();")
     body.append("    if (lane == 0) mbar_arrive(&empty[stage]);")
@@ -253,6 +328,7 @@ extern "C" int fasteq_u1d_forward(const fasteq_u1d_graph* gh, const void* w, con
   if (gh->n_out_rows == 0 && gh->n_edges == 0) return FASTEQ_OK;
   if (!out || (gh->n_edges > 0 && (!w || !x || !y))) return FASTEQ_INVALID;
   g.bulk_ok = aligned16(w) && aligned16(x) && aligned16(y) && ((U * sizeof(T)) % 16 == 0) && ((CT * sizeof(T)) % 16 == 0);
+  if (VEC == 2 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(w)) & 7u)) return FASTEQ_INVALID;
   cudaError_t e = cudaFuncSetAttribute(fasteq_u1d_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return cuda_fail(e);
   fasteq_u1d_fwd_kernel<<<grid, NTHREADS, SMEM_BYTES, (cudaStream_t)stream>>>(
@@ -272,6 +348,39 @@ extern "C" int fasteq_u1d_backward(const fasteq_u1d_graph*, const void*, const v
 
 # --------------------------------------------------------------------------- backward
 
+def _emit_warp_reduce_scatter(exprs: List[str], ind: str) -> List[str]:
+    """Sum each of n per-lane values over the 32 lanes with a halving butterfly: at every step a
+    lane keeps half of its values and hands the other half to its partner, so n values cost about
+    n + log2(32) shuffles instead of 5 n.  Ends with ``part[k] = total_k`` from one lane per k."""
+    n = len(exprs)
+    P = 1
+    while P < n:
+        P *= 2
+    P = min(P, 32)
+    if n > 32:
+        raise ValueError("more than 32 scalar y segments are not supported by the warp reduction")
+    L = [f"{ind}T r{i} = {exprs[i]};" if i < n else f"{ind}T r{i} = T(0);" for i in range(P)]
+    half, off = P // 2, 16
+    kterms = []
+    while half >= 1:
+        L.append(f"{ind}{{ const bool up = (lane & {off}) != 0;")
+        for i in range(half):
+            L.append(f"{ind}  {{ const T send = up ? r{i} : r{i + half}; const T keep = up ? r{i + half} : r{i}; "
+                     f"r{i} = keep + __shfl_xor_sync(0xffffffffu, send, {off}); }}")
+        L.append(f"{ind}}}")
+        kterms.append(f"((lane & {off}) ? {half} : 0)")
+        half //= 2
+        off //= 2
+    rest_mask = 0
+    while off >= 1:
+        L.append(f"{ind}r0 += __shfl_xor_sync(0xffffffffu, r0, {off});")
+        rest_mask |= off
+        off //= 2
+    k = " + ".join(kterms) if kterms else "0"
+    L.append(f"{ind}{{ const int k = {k}; if ((lane & {rest_mask}) == 0 && k < {n}) part[k] = r0; }}")
+    return L
+
+
 def emit_backward(spec: U1DSpec, tun: Tuning, need_gw: bool, need_gx: bool, need_gy: bool) -> str:
     """Backward module: grad_w, grad_x, grad_y of ``sum(out * grad_out)`` (any subset).
 
@@ -282,40 +391,54 @@ def emit_backward(spec: U1DSpec, tun: Tuning, need_gw: bool, need_gx: bool, need
     ``red.global.add`` when x is gathered; a scalar-y gradient is summed over channels
     with warp shuffles, then across warps by the producer warp when the stage is recycled.
     """
-    assert tun.groups == 1
+    _check_tuning(spec, tun)
+    if tun.groups != 1:
+        raise ValueError("the backward kernel uses one thread group")
     blocks = build_blocks(spec)
-    ncons_warps = tun.ct // 32
-    threads = tun.ct + 32
+    tpg = tun.ct // tun.vec
+    ncons_warps = tpg // 32
+    threads = tun.pipes * (tpg + 32)
     scalar_gy = need_gy and not spec.y_vec
     extra = ncons_warps * spec.y_segs * spec.elem_bytes if scalar_gy else 0
     extra = (extra + 15) // 16 * 16
-    T = spec.ctype
+    dt = spec.dtype
     src = [_prelude(spec, tun, extra, ncons_warps, emit_empty=False)]
     src.append(f"""
 constexpr int NTHREADS = {threads};
-constexpr int NGO = {tun.min_blocks and 1};            // grad_out row buffers
+constexpr int NGO = 1;                                 // grad_out row buffers
 constexpr int GO_BYTES = round_up(OSEG * CT * (int)sizeof(T), 128);
-constexpr int SMEM_BYTES = BAR_BYTES + STAGES * STAGE_BYTES + NGO * GO_BYTES;
+constexpr int PIPE_BYTES = BAR_BYTES + STAGES * STAGE_BYTES + NGO * GO_BYTES;
+constexpr int SMEM_BYTES = cfg::PIPES * PIPE_BYTES;
 constexpr bool NEED_GW = {str(need_gw).lower()}, NEED_GX = {str(need_gx).lower()}, NEED_GY = {str(need_gy).lower()};
 constexpr bool GY_ATOMIC = cfg::Y_INDEXED || (!cfg::Y_VEC && NCT > 1);
 
 __global__ void __launch_bounds__(NTHREADS, {tun.min_blocks})
 fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restrict__ w, const T* __restrict__ x,
                       const T* __restrict__ y, T* __restrict__ gw, T* __restrict__ gx, T* __restrict__ gy) {{
-  extern __shared__ __align__(128) unsigned char smem[];
+  extern __shared__ __align__(128) unsigned char smem_all[];
+  if (threadIdx.x == 0) {{
+    for (int p = 0; p < cfg::PIPES; ++p) {{
+      uint64_t* f = reinterpret_cast<uint64_t*>(smem_all + (size_t)p * PIPE_BYTES);
+      init_barriers(f, f + STAGES, g.bulk_ok);
+      uint64_t* gf = f + 2 * STAGES;
+      for (int b = 0; b < NGO; ++b) {{ mbar_init(&gf[b], 33); mbar_init(&gf[NGO + b], cfg::NCONS_WARPS); }}
+    }}
+    mbar_fence_init();
+  }}
+  __syncthreads();
+  const int warp_all = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool is_producer = warp_all >= cfg::PIPES * cfg::NCONS_WARPS;
+  const int pipe = is_producer ? warp_all - cfg::PIPES * cfg::NCONS_WARPS : warp_all / cfg::NCONS_WARPS;
+  const int warp = warp_all - pipe * cfg::NCONS_WARPS;           // consumer warp index inside the pipeline
+  unsigned char* smem = smem_all + (size_t)pipe * PIPE_BYTES;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + STAGES;
   uint64_t* go_full = empty + STAGES;
   uint64_t* go_empty = go_full + NGO;
   unsigned char* stages = smem + BAR_BYTES;
   unsigned char* gobuf = stages + STAGES * STAGE_BYTES;
-  if (threadIdx.x == 0) {{
-    for (int b = 0; b < NGO; ++b) {{ mbar_init(&go_full[b], 33); mbar_init(&go_empty[b], cfg::NCONS_WARPS); }}
-  }}
-  init_barriers(full, empty);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (warp == cfg::NCONS_WARPS) {{
-    Producer p{{g, w, x, y, stages, full, empty, lane, 0u}};
+  if (is_producer) {{
+    Producer p{{g, w, x, y, stages, full, empty, lane, 0u, (int)blockIdx.x * cfg::PIPES + pipe}};
     uint32_t nseg = 0;
     auto begin = [&](int row, int ct, int ln) {{
       // stage the receiver's grad_out tile once per segment
@@ -329,17 +452,20 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
       cp_async_arrive_noinc(&go_full[b]);
       ++nseg;
     }};
-    auto flush = [&](unsigned char* st, int ln) {{
+    auto flush = [&](unsigned char* st) {{
+      // one lane finishes the y gradient of the edge that occupied this stage: sum the consumer
+      // warps' partial sums and write the row
       if ({'true' if scalar_gy else 'false'}) {{
         const Meta pm = *reinterpret_cast<const Meta*>(st + OFF_META);
         if (pm.flags & F_DATA) {{
           const T* part = reinterpret_cast<const T*>(st + OFF_EXTRA);
-          for (int k = ln; k < YSEG; k += 32) {{
+          T* dst = gy + (size_t)pm.yr * YSEG;
+#pragma unroll
+          for (int k = 0; k < YSEG; ++k) {{
             T s = T(0);
 #pragma unroll
             for (int wp = 0; wp < cfg::NCONS_WARPS; ++wp) s += part[wp * YSEG + k];
-            T* dst = gy + (size_t)pm.yr * YSEG + k;
-            if (GY_ATOMIC) red_add(dst, s); else *dst = s;
+            if (GY_ATOMIC) red_add(dst + k, s); else dst[k] = s;
           }}
         }}
       }}
@@ -347,14 +473,14 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
     p.run(flush, begin);
     return;
   }}
-  const int ch = threadIdx.x;
+  const int ch = (threadIdx.x - pipe * cfg::NCONS_WARPS * 32) * VEC;
   uint32_t it = 0, nseg = 0;
 """)
     L: List[str] = []
     if spec.w_shared and need_gw:
-        L.append(f"  T gws[{spec.w_segs}];")
+        L.append(f"  V gws[{spec.w_segs}];")
         L.append("#pragma unroll")
-        L.append(f"  for (int i = 0; i < {spec.w_segs}; ++i) gws[i] = T(0);")
+        L.append(f"  for (int i = 0; i < {spec.w_segs}; ++i) gws[i] = VS::zero();")
         L.append("  int gws_ct = 0;")
     L.append("""  for (;;) {
     const int stage = it % STAGES;
@@ -362,7 +488,7 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
     mbar_wait(&full[stage], ph, g.status);
     unsigned char* st = stages + (size_t)stage * STAGE_BYTES;
     const Meta m = *reinterpret_cast<const Meta*>(st + OFF_META);
-    const int valid = (U - m.ct * CT) < CT ? (U - m.ct * CT) : CT;
+    const int valid = (U % CT == 0) ? CT : ((U - m.ct * CT) < CT ? (U - m.ct * CT) : CT);
     const bool live = ch < valid;
     const int gb = nseg % NGO;
     if (m.flags & F_FIRST) mbar_wait(&go_full[gb], (nseg / NGO) & 1u, g.status);""")
@@ -370,106 +496,142 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
         L.append("    if ((m.flags & (F_DATA | F_DONE)) && (m.ct != gws_ct || (m.flags & F_DONE))) {")
         L.append("      if (ch < ((U - gws_ct * CT) < CT ? (U - gws_ct * CT) : CT)) {")
         for i in range(spec.w_segs):
-            L.append(f"        red_add(gw + (size_t){i} * U + gws_ct * CT + ch, gws[{i}]); gws[{i}] = T(0);")
+            L.append(f"        VS::red(gw + (size_t){i} * U + gws_ct * CT + ch, gws[{i}]); gws[{i}] = VS::zero();")
         L.append("      }")
         L.append("      gws_ct = m.ct;")
         L.append("    }")
     if scalar_gy:
         for k in range(spec.y_segs):
-            L.append(f"    T gy{k} = T(0);")
+            L.append(f"    V gy{k} = VS::zero();")
     L.append("    if ((m.flags & F_DATA) && live) {")
     L.append("      const T* sx = reinterpret_cast<const T*>(st + OFF_X) + ch;")
     L.append(f"      const T* sy = reinterpret_cast<const T*>(st + OFF_Y){' + ch' if spec.y_vec else ''};")
     L.append("      const T* sgo = reinterpret_cast<const T*>(gobuf + (size_t)gb * GO_BYTES) + ch;")
     if spec.w_shared:
-        L.append("#define W(i) __ldg(w + (size_t)(i) * U + m.ct * CT + ch)")
+        L.append("#define W(i) VS::ld(w + (size_t)(i) * U + m.ct * CT + ch)")
     else:
         L.append("      const T* sw = reinterpret_cast<const T*>(st + OFF_W) + ch;")
-        L.append("#define W(i) sw[(i) * CT]")
-    L.append("#define GO(v) sgo[(v) * CT]")
-    for j in range(spec.x_segs):
-        L.append(f"      const T x{j} = sx[{j} * CT];")
-    for k in range(spec.y_segs):
-        L.append(f"      const T y{k} = sy[{k}{' * CT' if spec.y_vec else ''}];")
+        L.append("#define W(i) VS::ld(sw + (i) * CT)")
+    L.append("#define GO(v) VS::ld(sgo + (v) * CT)")
+    L += _load_xy(spec, "      ")
     if need_gx:
-        for j in range(spec.x_segs):
-            L.append(f"      T gx{j} = T(0);")
+        L += [f"      V gx{j} = VS::zero();" for j in range(spec.x_segs)]
     if need_gy and spec.y_vec:
-        for k in range(spec.y_segs):
-            L.append(f"      T gy{k} = T(0);")
-    # which block is the last to touch weight segment i
+        L += [f"      V gy{k} = VS::zero();" for k in range(spec.y_segs)]
     last_block_of_i: Dict[int, int] = {}
     for bi, b in enumerate(blocks):
         for t in b.terms:
             last_block_of_i[t.i] = bi
     if need_gw:
-        for i in sorted(last_block_of_i):
-            L.append(f"      T gw{i} = T(0);")
+        L += [f"      V gw{i} = VS::zero();" for i in sorted(last_block_of_i)]
         if not spec.w_shared:
             L.append("      T* gwp = gw + (size_t)m.e * WSEG * U + (size_t)m.ct * CT + ch;")
     need_q = need_gx or need_gy
-    for bi, b in enumerate(blocks):
-        L.append("      {")
-        if need_gw:
-            for (j, k) in b.products:
-                L.append(f"        const T p_{j}_{k} = x{j} * y{k};")
-        if need_q:
-            for (j, k) in b.products:
-                L.append(f"        T q_{j}_{k} = T(0);")
+
+    def gw_part(b: Block, ind: str) -> List[str]:
+        out = [f"{ind}const V p_{j}_{k} = vmul(x{j}, y{k});" for (j, k) in b.products]
         for t in b.terms:
-            L.append(f"        {{ const T gv = GO({t.v});")
-            if need_gw:
-                expr = " + ".join(f"{lit(c, spec.dtype)} * p_{j}_{k}" for j, k, c in t.items)
-                L.append(f"          gw{t.i} += gv * ({expr});")
-            if need_q:
-                L.append(f"          const T gp = W({t.i}) * gv;")
-                for j, k, c in t.items:
-                    L.append(f"          q_{j}_{k} += {lit(c, spec.dtype)} * gp;")
-            L.append("        }")
+            out.append(f"{ind}{{ " + " ".join(_sum_expr(t.items, dt)) + f" gw{t.i} = vfma(GO({t.v}), t, gw{t.i}); }}")
+        return out
+
+    def q_part(b: Block, ind: str) -> List[str]:
+        out = []
+        first_use = set()
+        for t in b.terms:
+            out.append(f"{ind}{{ const V gp = vmul(W({t.i}), GO({t.v}));")
+            for j, k, c in t.items:
+                if (j, k) in first_use:
+                    out.append(f"{ind}  q_{j}_{k} = vfma({_vlit(c, dt)}, gp, q_{j}_{k});")
+                else:
+                    first_use.add((j, k))
+                    out.append(f"{ind}  q_{j}_{k} = vmul({_vlit(c, dt)}, gp);")
+            out.append(f"{ind}}}")
+        decl = [f"{ind}V q_{j}_{k};" for (j, k) in b.products]
+        tail = []
         if need_gx:
-            for (j, k) in b.products:
-                L.append(f"        gx{j} += q_{j}_{k} * y{k};")
+            tail += [f"{ind}gx{j} = vfma(q_{j}_{k}, y{k}, gx{j});" for (j, k) in b.products]
         if need_gy:
-            for (j, k) in b.products:
-                L.append(f"        gy{k} += q_{j}_{k} * x{j};")
+            tail += [f"{ind}gy{k} = vfma(q_{j}_{k}, x{j}, gy{k});" for (j, k) in b.products]
+        return decl + out + tail
+
+    def diag_part(b: Block, ind: str) -> List[str]:
+        out = []
+        for (i, j, c), kv in _diagonal_runs(b.terms).items():
+            out.append(f"{ind}{{")
+            if need_gw or need_gx:
+                k0, v0 = kv[0]
+                out.append(f"{ind}  V d = vmul(GO({v0}), y{k0});")
+                for k, v in kv[1:]:
+                    out.append(f"{ind}  d = vfma(GO({v}), y{k}, d);")
+            cw = f"W({i})" if c == 1.0 else f"vmul({_vlit(c, dt)}, W({i}))"
+            out.append(f"{ind}  const V cw = {cw};")
+            if need_gw:
+                cx = f"x{j}" if c == 1.0 else f"vmul({_vlit(c, dt)}, x{j})"
+                out.append(f"{ind}  gw{i} = vfma({cx}, d, gw{i});")
+            if need_gx:
+                out.append(f"{ind}  gx{j} = vfma(cw, d, gx{j});")
+            if need_gy:
+                out.append(f"{ind}  const V s = vmul(cw, x{j});")
+                for k, v in kv:
+                    out.append(f"{ind}  gy{k} = vfma(s, GO({v}), gy{k});")
+            out.append(f"{ind}}}")
+        return out
+
+    for bi, b in enumerate(blocks):
+        if _is_diagonal(b.terms):
+            L.append("      {"); L += diag_part(b, "        "); L.append("      }")
+        elif tun.two_pass or not (need_gw and need_q):
+            if need_gw:
+                L.append("      {"); L += gw_part(b, "        "); L.append("      }")
+            if need_q:
+                L.append("      {"); L += q_part(b, "        "); L.append("      }")
+        else:
+            # single pass: products and their gradients live together, grad_out / weight read once
+            L.append("      {")
+            L += [f"        const V p_{j}_{k} = vmul(x{j}, y{k});" for (j, k) in b.products]
+            L += [f"        V q_{j}_{k};" for (j, k) in b.products]
+            first_use = set()
+            for t in b.terms:
+                L.append(f"        {{ const V gv = GO({t.v});")
+                L.append("          " + " ".join(_sum_expr(t.items, dt)) + f" gw{t.i} = vfma(gv, t, gw{t.i});")
+                L.append(f"          const V gp = vmul(W({t.i}), gv);")
+                for j, k, c in t.items:
+                    if (j, k) in first_use:
+                        L.append(f"          q_{j}_{k} = vfma({_vlit(c, dt)}, gp, q_{j}_{k});")
+                    else:
+                        first_use.add((j, k))
+                        L.append(f"          q_{j}_{k} = vmul({_vlit(c, dt)}, gp);")
+                L.append("        }")
+            if need_gx:
+                L += [f"        gx{j} = vfma(q_{j}_{k}, y{k}, gx{j});" for (j, k) in b.products]
+            if need_gy:
+                L += [f"        gy{k} = vfma(q_{j}_{k}, x{j}, gy{k});" for (j, k) in b.products]
+            L.append("      }")
         if need_gw:
             for i in sorted(i for i, last in last_block_of_i.items() if last == bi):
                 if spec.w_shared:
-                    L.append(f"        gws[{i}] += gw{i};")
+                    L.append(f"      gws[{i}] = vadd(gws[{i}], gw{i});")
                 else:
-                    L.append(f"        gwp[{i} * U] = gw{i};")
-        L.append("      }")
+                    L.append(f"      VS::st(gwp + {i} * U, gw{i});")
     if need_gw and not spec.w_shared:
-        # weight segments no path touches still need a defined gradient
         for i in range(spec.w_segs):
             if i not in last_block_of_i:
-                L.append(f"      gwp[{i} * U] = T(0);")
+                L.append(f"      VS::st(gwp + {i} * U, VS::zero());")
     if need_gx:
         L.append("      T* gxp = gx + (size_t)m.xr * XSEG * U + (size_t)m.ct * CT + ch;")
         for j in range(spec.x_segs):
-            if spec.x_indexed:
-                L.append(f"      red_add(gxp + {j} * U, gx{j});")
-            else:
-                L.append(f"      gxp[{j} * U] = gx{j};")
+            L.append(f"      VS::{'red' if spec.x_indexed else 'st'}(gxp + {j} * U, gx{j});")
     if need_gy and spec.y_vec:
         L.append("      T* gyp = gy + (size_t)m.yr * YSEG * U + (size_t)m.ct * CT + ch;")
         for k in range(spec.y_segs):
-            if spec.y_indexed:
-                L.append(f"      red_add(gyp + {k} * U, gy{k});")
-            else:
-                L.append(f"      gyp[{k} * U] = gy{k};")
+            L.append(f"      VS::{'red' if spec.y_indexed else 'st'}(gyp + {k} * U, gy{k});")
     L.append("#undef W")
     L.append("#undef GO")
     L.append("    }")
     if scalar_gy:
         L.append("    if (m.flags & F_DATA) {")
         L.append("      T* part = reinterpret_cast<T*>(st + OFF_EXTRA) + warp * YSEG;")
-        for k in range(spec.y_segs):
-            L.append(f"      gy{k} = warp_sum(gy{k});")
-        L.append("      if (lane == 0) {")
-        for k in range(spec.y_segs):
-            L.append(f"        part[{k}] = gy{k};")
-        L.append("      }")
+        L += _emit_warp_reduce_scatter([f"VS::hsum(gy{k})" for k in range(spec.y_segs)], "      ")
         L.append("    }")
     L.append("""    __syncwarp();
     if (lane == 0) {
@@ -513,6 +675,8 @@ extern "C" int fasteq_u1d_backward(const fasteq_u1d_graph* gh, const void* go, c
   if (!go || !w || !x || !y) return FASTEQ_INVALID;
   g.bulk_ok = aligned16(w) && aligned16(x) && aligned16(y) && aligned16(go) && ((U * sizeof(T)) % 16 == 0) &&
               ((CT * sizeof(T)) % 16 == 0);
+  if (VEC == 2 && ((reinterpret_cast<uintptr_t>(gw) | reinterpret_cast<uintptr_t>(gx) | reinterpret_cast<uintptr_t>(gy)) & 7u))
+    return FASTEQ_INVALID;
   e = cudaFuncSetAttribute(fasteq_u1d_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return cuda_fail(e);
   fasteq_u1d_bwd_kernel<<<grid, NTHREADS, SMEM_BYTES, s>>>(g, (const T*)go, (const T*)w, (const T*)x, (const T*)y,

@@ -102,6 +102,67 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 __device__ __forceinline__ void red_add(float* p, float v) { asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory"); }
 __device__ __forceinline__ void red_add(double* p, double v) { asm volatile("red.global.add.f64 [%0], %1;" ::"l"(p), "d"(v) : "memory"); }
 
+// red.global.add of two adjacent floats in one instruction (8-byte aligned address)
+__device__ __forceinline__ void red_add2(float* p, float2 v) {
+  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(v.x), "f"(v.y) : "memory");
+}
+
+// ---- value abstraction used by the generated arithmetic: a "value" is one channel (float or
+// double) or two adjacent FP32 channels packed in a float2 and processed with the sm_100
+// f32x2 instructions (one issue slot for two FMAs; literal multipliers become packed
+// constant-bank operands).
+__device__ __forceinline__ float vmul(float a, float b) { return a * b; }
+__device__ __forceinline__ float vfma(float a, float b, float c) { return fmaf(a, b, c); }
+__device__ __forceinline__ float vadd(float a, float b) { return a + b; }
+__device__ __forceinline__ double vmul(double a, double b) { return a * b; }
+__device__ __forceinline__ double vfma(double a, double b, double c) { return fma(a, b, c); }
+__device__ __forceinline__ double vadd(double a, double b) { return a + b; }
+__device__ __forceinline__ unsigned long long f2_bits(float2 a) { return *reinterpret_cast<unsigned long long*>(&a); }
+__device__ __forceinline__ float2 vmul(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(*reinterpret_cast<unsigned long long*>(&d)) : "l"(f2_bits(a)), "l"(f2_bits(b)));
+  return d;
+}
+__device__ __forceinline__ float2 vfma(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(f2_bits(a)), "l"(f2_bits(b)), "l"(f2_bits(c)));
+  return d;
+}
+__device__ __forceinline__ float2 vadd(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(*reinterpret_cast<unsigned long long*>(&d)) : "l"(f2_bits(a)), "l"(f2_bits(b)));
+  return d;
+}
+template <typename V> struct VT;
+template <> struct VT<float> {
+  using S = float; static constexpr int N = 1;
+  static __device__ __forceinline__ float bc(float s) { return s; }
+  static __device__ __forceinline__ float zero() { return 0.f; }
+  static __device__ __forceinline__ float hsum(float v) { return v; }
+  static __device__ __forceinline__ float ld(const float* p) { return *p; }
+  static __device__ __forceinline__ void st(float* p, float v) { *p = v; }
+  static __device__ __forceinline__ void red(float* p, float v) { red_add(p, v); }
+};
+template <> struct VT<double> {
+  using S = double; static constexpr int N = 1;
+  static __device__ __forceinline__ double bc(double s) { return s; }
+  static __device__ __forceinline__ double zero() { return 0.0; }
+  static __device__ __forceinline__ double hsum(double v) { return v; }
+  static __device__ __forceinline__ double ld(const double* p) { return *p; }
+  static __device__ __forceinline__ void st(double* p, double v) { *p = v; }
+  static __device__ __forceinline__ void red(double* p, double v) { red_add(p, v); }
+};
+template <> struct VT<float2> {
+  using S = float; static constexpr int N = 2;
+  static __device__ __forceinline__ float2 bc(float s) { return make_float2(s, s); }
+  static __device__ __forceinline__ float2 zero() { return make_float2(0.f, 0.f); }
+  static __device__ __forceinline__ float hsum(float2 v) { return v.x + v.y; }
+  static __device__ __forceinline__ float2 ld(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ void st(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+  static __device__ __forceinline__ void red(float* p, float2 v) { red_add2(p, v); }
+};
+
 template <typename T>
 __device__ __forceinline__ T warp_sum(T v) {
 #pragma unroll

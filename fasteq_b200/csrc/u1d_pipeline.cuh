@@ -8,8 +8,8 @@
 // shared memory.
 //
 // The including file must define namespace cfg { T, U, CT, WSEG, XSEG, YSEG,
-// OSEG, STAGES, Y_VEC, W_SHARED, X_INDEXED, Y_INDEXED, SCATTERED, NCONS_WARPS,
-// STAGE_EXTRA_BYTES, EMIT_EMPTY_ROWS }.
+// OSEG, STAGES, PIPES, Y_VEC, W_SHARED, X_INDEXED, Y_INDEXED, SCATTERED, NCONS_WARPS,
+// STAGE_EXTRA_BYTES, EMIT_EMPTY_ROWS, BEGIN_PER_SEGMENT }.
 #pragma once
 #include "fasteq_device.cuh"
 
@@ -43,6 +43,7 @@ struct Graph {
   long long n_edges, n_out_rows, x_rows, y_rows;
   const int* x_index; const int* y_index; const int* seg_ptr; const int* perm; const int* part_ptr;
   int bulk_ok;      // rows may travel as bulk copies
+  int n_vblocks;    // pipelines that have work (grid * pipelines per CTA may exceed it)
   int* status;
 };
 
@@ -75,47 +76,132 @@ __device__ __forceinline__ void copy_tile(unsigned char* sdst, const T* grow, in
 
 struct Producer {
   const Graph& g; const T* w; const T* x; const T* y;
-  unsigned char* stages; uint64_t* full; uint64_t* empty; int lane; uint32_t it;
+  unsigned char* stages; uint64_t* full; uint64_t* empty; int lane; uint32_t it; int vblock;
 
-  // Called when a stage is about to be reused (and once per stage at the end): `prev` is the
-  // record of the edge that occupied it.  The backward kernels finish per-edge reductions here.
-  template <typename Flush, typename Begin>
-  __device__ __forceinline__ void emit(int flags, int row, int ct, int e, int xr, int yr, Flush&& flush, Begin&& begin) {
-    const int stage = it % STAGES;
-    const uint32_t ph = (it / STAGES) & 1u;
-    if (flags & F_FIRST) begin(row, ct, lane);
+  static __device__ __forceinline__ int valid_of(int ct) { return (U - ct * CT) < CT ? (U - ct * CT) : CT; }
+  static __device__ __forceinline__ uint32_t tx_bytes(int valid) {
+    return (uint32_t)((cfg::W_SHARED ? 0 : WSEG) + XSEG + (cfg::Y_VEC ? YSEG : 0)) * (uint32_t)(valid * sizeof(T));
+  }
+  __device__ __forceinline__ int checked(int r, long long n) {
+    if (r < 0 || (long long)r >= n) { atomicExch(g.status, (int)kDevBadIndex); return 0; }
+    return r;
+  }
+
+  // Bulk path: ONE lane fills one stage (record, expected bytes, bulk copies of its edge's rows,
+  // 4/8-byte cp.async for a scalar y row).  Up to STAGES lanes do this side by side, so the
+  // producer spends about (instructions of one fill) / STAGES per edge.
+  // `flush(st)` runs on the same lane before a stage is reused; the backward finishes the
+  // per-edge y-gradient there.
+  template <typename Flush>
+  __device__ __forceinline__ void fill_one(uint32_t myit, int flags, int row, int ct, int e, int xr, int yr, Flush&& flush) {
+    const int stage = myit % STAGES;
+    const uint32_t ph = (myit / STAGES) & 1u;
     mbar_wait(&empty[stage], ph ^ 1u, g.status);
     unsigned char* st = stages + (size_t)stage * STAGE_BYTES;
-    if (it >= (uint32_t)STAGES) flush(st, lane);
-    const int valid = (U - ct * CT) < CT ? (U - ct * CT) : CT;
+    if (myit >= (uint32_t)STAGES) flush(st);
+    const int valid = valid_of(ct);
+    Meta m; m.row = row; m.flags = flags; m.ct = ct; m.e = e; m.xr = xr; m.yr = yr; m.pad0 = 0; m.pad1 = 0;
+    *reinterpret_cast<Meta*>(st + OFF_META) = m;
     const bool data = (flags & F_DATA) != 0;
-    const bool bulk = g.bulk_ok != 0;
+    mbar_arrive_expect_tx(&full[stage], data ? tx_bytes(valid) : 0u);
+    if (data) {
+      const uint32_t piece = (uint32_t)(valid * sizeof(T));
+      if (!cfg::W_SHARED) {
+        const T* src = w + (size_t)e * WSEG * U;
+        if (FULL_ROW) bulk_g2s(st + OFF_W, src, (uint32_t)(WSEG * U * sizeof(T)), &full[stage]);
+        else for (int s = 0; s < WSEG; ++s) bulk_g2s(st + OFF_W + (size_t)s * CT * sizeof(T), src + (size_t)s * U + ct * CT, piece, &full[stage]);
+      }
+      {
+        const T* src = x + (size_t)xr * XSEG * U;
+        if (FULL_ROW) bulk_g2s(st + OFF_X, src, (uint32_t)(XSEG * U * sizeof(T)), &full[stage]);
+        else for (int s = 0; s < XSEG; ++s) bulk_g2s(st + OFF_X + (size_t)s * CT * sizeof(T), src + (size_t)s * U + ct * CT, piece, &full[stage]);
+      }
+      if (cfg::Y_VEC) {
+        const T* src = y + (size_t)yr * YSEG * U;
+        if (FULL_ROW) bulk_g2s(st + OFF_Y, src, (uint32_t)(YSEG * U * sizeof(T)), &full[stage]);
+        else for (int s = 0; s < YSEG; ++s) bulk_g2s(st + OFF_Y + (size_t)s * CT * sizeof(T), src + (size_t)s * U + ct * CT, piece, &full[stage]);
+      } else {
+        const T* src = y + (size_t)yr * YSEG;
+#pragma unroll
+        for (int k = 0; k < YSEG; ++k) cp_async_elem(st + OFF_Y + k * sizeof(T), src + k);
+      }
+    }
+    cp_async_arrive_noinc(&full[stage]);
+  }
+
+  // Fallback path (operands not 16-byte aligned): the whole warp copies one edge with 4/8-byte cp.async.
+  template <typename Flush>
+  __device__ __forceinline__ void fill_coop(int flags, int row, int ct, int e, int xr, int yr, Flush&& flush) {
+    const int stage = it % STAGES;
+    const uint32_t ph = (it / STAGES) & 1u;
+    mbar_wait(&empty[stage], ph ^ 1u, g.status);
+    unsigned char* st = stages + (size_t)stage * STAGE_BYTES;
     if (lane == 0) {
+      if (it >= (uint32_t)STAGES) flush(st);
       Meta m; m.row = row; m.flags = flags; m.ct = ct; m.e = e; m.xr = xr; m.yr = yr; m.pad0 = 0; m.pad1 = 0;
       *reinterpret_cast<Meta*>(st + OFF_META) = m;
-      uint32_t tx = 0;
-      if (data && bulk) {
-        tx = (uint32_t)((cfg::W_SHARED ? 0 : WSEG) + XSEG + (cfg::Y_VEC ? YSEG : 0)) * (uint32_t)(valid * sizeof(T));
-      }
-      mbar_arrive_expect_tx(&full[stage], tx);
+      mbar_arrive_expect_tx(&full[stage], 0u);
     }
     __syncwarp();
-    if (data) {
-      if (!cfg::W_SHARED) copy_tile(st + OFF_W, w + (size_t)e * WSEG * U, WSEG, ct, valid, bulk, &full[stage], lane);
-      copy_tile(st + OFF_X, x + (size_t)xr * XSEG * U, XSEG, ct, valid, bulk, &full[stage], lane);
-      if (cfg::Y_VEC) {
-        copy_tile(st + OFF_Y, y + (size_t)yr * YSEG * U, YSEG, ct, valid, bulk, &full[stage], lane);
-      } else {
-        for (int k = lane; k < YSEG; k += 32) cp_async_elem(st + OFF_Y + k * sizeof(T), y + (size_t)yr * YSEG + k);
-      }
+    if (flags & F_DATA) {
+      const int valid = valid_of(ct);
+      if (!cfg::W_SHARED) copy_tile(st + OFF_W, w + (size_t)e * WSEG * U, WSEG, ct, valid, false, &full[stage], lane);
+      copy_tile(st + OFF_X, x + (size_t)xr * XSEG * U, XSEG, ct, valid, false, &full[stage], lane);
+      if (cfg::Y_VEC) copy_tile(st + OFF_Y, y + (size_t)yr * YSEG * U, YSEG, ct, valid, false, &full[stage], lane);
+      else for (int k = lane; k < YSEG; k += 32) cp_async_elem(st + OFF_Y + k * sizeof(T), y + (size_t)yr * YSEG + k);
     }
     cp_async_arrive_noinc(&full[stage]);
     ++it;
   }
 
-  __device__ __forceinline__ int checked(int r, long long n) {
-    if (r < 0 || (long long)r >= n) { atomicExch(g.status, (int)kDevBadIndex); return 0; }
-    return r;
+  // A stage without rows (an empty receiver, or the end marker).
+  template <typename Flush>
+  __device__ __forceinline__ void fill_special(int flags, int row, int ct, Flush&& flush) {
+    if (g.bulk_ok) {
+      if (lane == 0) fill_one(it, flags, row, ct, 0, 0, 0, flush);
+      __syncwarp();
+      ++it;
+    } else {
+      fill_coop(flags, row, ct, 0, 0, 0, flush);
+    }
+  }
+
+  // m <= 32 consecutive edges of one segment (lane l holds edge l: id, x row, y row);
+  // first / last tell whether the batch starts / ends the segment.
+  template <typename Flush, typename Begin>
+  __device__ __forceinline__ void fill_batch(int m, int me, int mx, int my, int row, int ct, bool first, bool last,
+                                             bool each_is_segment, Flush&& flush, Begin&& begin) {
+    if (g.bulk_ok && !(each_is_segment && cfg::BEGIN_PER_SEGMENT)) {
+      for (int base = 0; base < m; base += STAGES) {
+        const int n = (m - base) < STAGES ? (m - base) : STAGES;
+        const int l = lane - base;
+        if (l >= 0 && l < n) {
+          int flags = F_DATA;
+          if (each_is_segment || (first && lane == 0)) flags |= F_FIRST;
+          if (each_is_segment || (last && lane == m - 1)) flags |= F_LAST;
+          fill_one(it + (uint32_t)l, flags, each_is_segment ? me : row, ct, me, mx, my, flush);
+        }
+        __syncwarp();
+        it += (uint32_t)n;
+      }
+    } else {
+      for (int j = 0; j < m; ++j) {
+        const int e = __shfl_sync(0xffffffffu, me, j);
+        const int xr = __shfl_sync(0xffffffffu, mx, j), yr = __shfl_sync(0xffffffffu, my, j);
+        int flags = F_DATA;
+        if (each_is_segment || (first && j == 0)) flags |= F_FIRST;
+        if (each_is_segment || (last && j == m - 1)) flags |= F_LAST;
+        const int r = each_is_segment ? e : row;
+        if (each_is_segment) begin(r, ct, lane);
+        if (g.bulk_ok) {
+          if (lane == 0) fill_one(it, flags, r, ct, e, xr, yr, flush);
+          __syncwarp();
+          ++it;
+        } else {
+          fill_coop(flags, r, ct, e, xr, yr, flush);
+        }
+      }
+    }
   }
 
   template <typename Flush, typename Begin>
@@ -123,8 +209,10 @@ struct Producer {
     it = 0;
     const long long n_units = cfg::SCATTERED ? g.n_out_rows : g.n_edges;
     long long s0, s1;
-    if (g.part_ptr) { s0 = g.part_ptr[blockIdx.x]; s1 = g.part_ptr[blockIdx.x + 1]; }
-    else { s0 = n_units * blockIdx.x / gridDim.x; s1 = n_units * (blockIdx.x + 1) / gridDim.x; }
+    // vblock: this pipeline's index among all pipelines of the launch (a CTA may hold several)
+    if (vblock >= g.n_vblocks) { s0 = 0; s1 = 0; }
+    else if (g.part_ptr) { s0 = g.part_ptr[vblock]; s1 = g.part_ptr[vblock + 1]; }
+    else { s0 = n_units * vblock / g.n_vblocks; s1 = n_units * (vblock + 1) / g.n_vblocks; }
     for (int ct = 0; ct < NCT; ++ct) {
       if (cfg::SCATTERED) {
         for (long long sb = s0; sb < s1; sb += 32) {
@@ -134,7 +222,8 @@ struct Producer {
           for (int i = 0; i < n; ++i) {
             const int e0 = __shfl_sync(0xffffffffu, rp0, i), e1 = __shfl_sync(0xffffffffu, rp1, i);
             const int row = (int)(sb + i);
-            if (e0 >= e1) { if (cfg::EMIT_EMPTY_ROWS) emit(F_LAST, row, ct, 0, 0, 0, flush, begin); continue; }
+            if (e0 >= e1) { if (cfg::EMIT_EMPTY_ROWS) fill_special(F_LAST, row, ct, flush); continue; }
+            begin(row, ct, lane);
             for (int pb = e0; pb < e1; pb += 32) {
               const int m = (e1 - pb) < 32 ? (e1 - pb) : 32;
               int me = 0, mx = 0, my = 0;
@@ -144,11 +233,7 @@ struct Producer {
                 mx = cfg::X_INDEXED ? checked(g.x_index[me], g.x_rows) : me;
                 my = cfg::Y_INDEXED ? checked(g.y_index[me], g.y_rows) : me;
               }
-              for (int j = 0; j < m; ++j) {
-                const int e = __shfl_sync(0xffffffffu, me, j);
-                const int xr = __shfl_sync(0xffffffffu, mx, j), yr = __shfl_sync(0xffffffffu, my, j);
-                emit(F_DATA | ((pb + j == e1 - 1) ? F_LAST : 0) | ((pb + j == e0) ? F_FIRST : 0), row, ct, e, xr, yr, flush, begin);
-              }
+              fill_batch(m, me, mx, my, row, ct, pb == e0, pb + m == e1, false, flush, begin);
             }
           }
         }
@@ -161,36 +246,32 @@ struct Producer {
             mx = cfg::X_INDEXED ? checked(g.x_index[me], g.x_rows) : me;
             my = cfg::Y_INDEXED ? checked(g.y_index[me], g.y_rows) : me;
           }
-          for (int j = 0; j < m; ++j) {
-            const int e = __shfl_sync(0xffffffffu, me, j);
-            const int xr = __shfl_sync(0xffffffffu, mx, j), yr = __shfl_sync(0xffffffffu, my, j);
-            emit(F_DATA | F_LAST | F_FIRST, e, ct, e, xr, yr, flush, begin);
-          }
+          fill_batch(m, me, mx, my, 0, ct, true, true, true, flush, begin);
         }
       }
     }
-    emit(F_DONE, 0, 0, 0, 0, 0, flush, begin);
-    // drain: every stage still holding a finished edge gets its flush, in order
+    fill_special(F_DONE, 0, 0, flush);
+    // drain: every stage still holding a finished edge gets its flush
     const uint32_t total = it;
     const uint32_t first = total > (uint32_t)STAGES ? total - STAGES : 0;
-    for (uint32_t k = first; k < total; ++k) {
+    const uint32_t k = first + (uint32_t)lane;
+    if (k < total) {
       const int stage = k % STAGES;
       const uint32_t ph = (k / STAGES) & 1u;
       mbar_wait(&empty[stage], ph, g.status);
-      flush(stages + (size_t)stage * STAGE_BYTES, lane);
+      flush(stages + (size_t)stage * STAGE_BYTES);
     }
+    __syncwarp();
   }
 };
 
-__device__ __forceinline__ void init_barriers(uint64_t* full, uint64_t* empty) {
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], 33);                 // lane 0's expect_tx arrive + 32 cp.async completion arrives
-      mbar_init(&empty[s], cfg::NCONS_WARPS);  // one arrive per consumer warp
-    }
-    mbar_fence_init();
+// full[s] expects: bulk path = the filling lane's expect_tx arrive + its cp.async completion arrive;
+// fallback path = lane 0's arrive + one cp.async completion arrive per lane.
+__device__ __forceinline__ void init_barriers(uint64_t* full, uint64_t* empty, int bulk_ok) {
+  for (int s = 0; s < STAGES; ++s) {
+    mbar_init(&full[s], bulk_ok ? 2 : 33);
+    mbar_init(&empty[s], cfg::NCONS_WARPS);  // one arrive per consumer warp of the pipeline
   }
-  __syncthreads();
 }
 
 }  // namespace u1d

@@ -246,10 +246,20 @@ def _np(t, is_float=False) -> np.ndarray:
 _SPEC_CACHE: Dict[Tuple, U1DSpec] = {}
 
 
+def _tuning_for(spec: U1DSpec, direction: str, tensors) -> Optional[_emit.Tuning]:
+    """Packed two-channel modules read and write 8-byte pairs; operands at an odd 4-byte offset
+    (a contiguous view into a larger buffer) get the one-channel-per-thread module instead."""
+    tun = _TUNING_OVERRIDE.get(direction) or _emit.default_tuning(spec, direction)
+    if tun.vec == 2 and any(t is not None and t.data_ptr() % 8 for t in tensors):
+        import dataclasses
+        return dataclasses.replace(tun, vec=1, pipes=1, min_blocks=min(tun.min_blocks + 1, 3))
+    return tun
+
+
 def _run_fwd(call: _Call, w, x, y) -> torch.Tensor:
-    mod = get_module(call.spec, "fwd")
     dev = x.device
     out = torch.empty((call.n_out_rows, call.out_segs * call.u), dtype=x.dtype, device=dev)
+    mod = get_module(call.spec, "fwd", tuning=_tuning_for(call.spec, "fwd", (w, x, y, out)))
     with torch.cuda.device(dev):
         g = call.graph(mod, dev)
         mod.forward(g, w.data_ptr(), x.data_ptr(), y.data_ptr(), out.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
@@ -257,11 +267,11 @@ def _run_fwd(call: _Call, w, x, y) -> torch.Tensor:
 
 
 def _run_bwd(call: _Call, grad_out, w, x, y, needs):
-    mod = get_module(call.spec, "bwd", needs)
     dev = x.device
     gw = torch.empty_like(w) if needs[0] else None
     gx = torch.empty_like(x) if needs[1] else None
     gy = torch.empty_like(y) if needs[2] else None
+    mod = get_module(call.spec, "bwd", needs, tuning=_tuning_for(call.spec, "bwd", (grad_out, w, x, y, gw, gx, gy)))
     ptr = lambda t: t.data_ptr() if t is not None else None
     with torch.cuda.device(dev):
         g = call.graph(mod, dev)
