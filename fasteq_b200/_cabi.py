@@ -68,6 +68,8 @@ class U1DModule:
         lib.fasteq_u1d_backward.argtypes = [C.POINTER(U1DGraph)] + [C.c_void_p] * 8
         lib.fasteq_u1d_device_status.argtypes = [C.POINTER(C.c_int32)]
         lib.fasteq_last_cuda_error.restype = C.c_char_p
+        if hasattr(lib, "fasteq_u1d_forward_noalloc"):   # forward modules only
+            lib.fasteq_u1d_forward_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64] + [C.c_void_p] * 5
         self.lib = lib
         self.desc = U1DDesc()
         check(lib.fasteq_u1d_describe(C.byref(self.desc)), lib, "fasteq_u1d_describe")
@@ -76,6 +78,14 @@ class U1DModule:
 
     def forward(self, graph: U1DGraph, w: int, x: int, y: int, out: int, stream: int) -> None:
         check(self.lib.fasteq_u1d_forward(C.byref(graph), w, x, y, out, stream), self.lib, "fasteq_u1d_forward")
+
+    def forward_noalloc(self, dst_sorted: int, x_index, n_edges: int, n_out_rows: int, x_rows: int,
+                        w: int, x: int, y: int, out: int, stream: int) -> int:
+        """Raw status of fasteq_u1d_forward_noalloc (the caller decides how to treat a refusal)."""
+        return int(self.lib.fasteq_u1d_forward_noalloc(dst_sorted, x_index, n_edges, n_out_rows, x_rows, w, x, y, out, stream))
+
+    def last_error(self) -> str:
+        return self.lib.fasteq_last_cuda_error().decode()
 
     def backward(self, graph: U1DGraph, go: int, w: int, x: int, y: int, gw, gx, gy, stream: int) -> None:
         check(self.lib.fasteq_u1d_backward(C.byref(graph), go, w, x, y, gw, gx, gy, stream), self.lib,

@@ -131,6 +131,105 @@ extern "C" const char* fasteq_last_cuda_error(void) { return g_err; }
 """
 
 
+_NOALLOC_FORWARD = r"""
+// ---------------------------------------------------------------------------------------------
+// Forward without any allocation.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need the operator:
+// a molecular-dynamics engine plug-in that was handed a fixed device arena at start-up, code that
+// runs while a CUDA graph is being captured on the stream, or a real-time control loop where an
+// allocation (an implicit device synchronisation) is forbidden.  The regular entry point leaves
+// the CSR offsets and the per-CTA partition to the caller, who must own buffers for them.  This
+// variant builds both into a fixed array that lives inside this library image and then runs the
+// same forward kernel on them.
+//
+// Limits and rules:
+//   * at most FASTEQ_NOALLOC_MAX_ROWS output rows (receivers); larger calls are refused with
+//     FASTEQ_UNSUPPORTED and nothing is launched;
+//   * edges must already be sorted by receiver (there is no room for a permutation);
+//   * the array (about 1 MB) is reserved on every GPU that loads this library until the process
+//     exits, and all calls share it.  Every entry a call reads is written earlier in the same
+//     call, so nothing has to be cleared between calls, but two calls that overlap on the GPU
+//     (different streams, or different host threads) overwrite each other's offsets: serialise them;
+//   * the first call on each device looks up the array's device address (cudaGetSymbolAddress,
+//     with that device current).  Make that first call outside of any stream capture.
+// ---------------------------------------------------------------------------------------------
+#define FASTEQ_NOALLOC_MAX_ROWS 262144
+#define FASTEQ_NOALLOC_MAX_PARTS 4096
+static __device__ __align__(256) int g_noalloc_scratch[FASTEQ_NOALLOC_MAX_ROWS + 1 + FASTEQ_NOALLOC_MAX_PARTS + 1];
+
+namespace {
+__global__ void na_build_csr(const int* __restrict__ dst, long long n_edges, long long n_rows, int* __restrict__ seg_ptr) {
+  const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r > n_rows) return;
+  long long lo = 0, hi = n_edges;
+  while (lo < hi) {
+    const long long mid = (lo + hi) >> 1;
+    if ((long long)dst[mid] < r) lo = mid + 1; else hi = mid;
+  }
+  seg_ptr[r] = (int)lo;
+}
+__global__ void na_partition(const int* __restrict__ seg_ptr, long long n_rows, long long n_edges, int n_parts,
+                             int* __restrict__ part_ptr) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p > n_parts) return;
+  if (p == n_parts) { part_ptr[p] = (int)n_rows; return; }
+  const long long target = (n_edges + n_rows) * p / n_parts;
+  long long lo = 0, hi = n_rows;
+  while (lo < hi) {
+    const long long mid = (lo + hi) >> 1;
+    if ((long long)seg_ptr[mid] + mid < target) lo = mid + 1; else hi = mid;
+  }
+  part_ptr[p] = (int)lo;
+}
+constexpr int kMaxDevices = 64;
+int* g_noalloc_addr[kMaxDevices];   // device address of g_noalloc_scratch per device, filled on first use
+}  // namespace
+
+extern "C" int fasteq_u1d_forward_noalloc(const int32_t* dst_sorted, const int32_t* x_index, int64_t n_edges,
+                                          int64_t n_out_rows, int64_t x_rows, const void* w, const void* x,
+                                          const void* y, void* out, fasteq_stream_t stream) {
+  if (!cfg::SCATTERED || cfg::Y_INDEXED) return FASTEQ_UNSUPPORTED;
+  if (n_edges < 0 || n_out_rows < 0 || n_edges > 0x7fffffffLL) return FASTEQ_INVALID;
+  if (n_out_rows > FASTEQ_NOALLOC_MAX_ROWS) {
+    snprintf(g_err, sizeof(g_err), "fasteq_u1d_forward_noalloc: %lld output rows exceed the built-in scratch (%d rows)",
+             (long long)n_out_rows, FASTEQ_NOALLOC_MAX_ROWS);
+    return FASTEQ_UNSUPPORTED;
+  }
+  if (n_out_rows == 0) return FASTEQ_OK;
+  if (!out || (n_edges > 0 && (!dst_sorted || !w || !x || !y || (cfg::X_INDEXED && !x_index)))) return FASTEQ_INVALID;
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= kMaxDevices) return FASTEQ_UNSUPPORTED;
+  if (!g_noalloc_addr[dev]) {
+    // once per device, with that device current: the symbol's name is only a host-side handle
+    int* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return cuda_fail(e);
+    g_noalloc_addr[dev] = p;
+  }
+  int* seg_ptr = g_noalloc_addr[dev];
+  int* part_ptr = seg_ptr + FASTEQ_NOALLOC_MAX_ROWS + 1;
+  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  long long n_parts = (long long)sms * @MINB@ * cfg::PIPES;
+  if (n_parts > n_out_rows) n_parts = n_out_rows;
+  if (n_parts > FASTEQ_NOALLOC_MAX_PARTS) n_parts = FASTEQ_NOALLOC_MAX_PARTS;
+  cudaStream_t s = (cudaStream_t)stream;
+  na_build_csr<<<(int)((n_out_rows + 1 + 255) / 256), 256, 0, s>>>(dst_sorted, n_edges, n_out_rows, seg_ptr);
+  na_partition<<<(int)((n_parts + 1 + 255) / 256), 256, 0, s>>>(seg_ptr, n_out_rows, n_edges, (int)n_parts, part_ptr);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  fasteq_u1d_graph gh;
+  gh.n_edges = n_edges; gh.n_out_rows = n_out_rows; gh.x_rows = x_rows; gh.y_rows = n_edges;
+  gh.x_index = x_index; gh.y_index = nullptr; gh.seg_ptr = seg_ptr; gh.perm = nullptr; gh.part_ptr = part_ptr;
+  gh.n_parts = (int32_t)n_parts;
+  return fasteq_u1d_forward(&gh, w, x, y, out, stream);
+}
+"""
+
+
 def _prelude(spec: U1DSpec, tun: Tuning, extra_bytes: int, ncons_warps: int, emit_empty: bool = True) -> str:
     return ("// Generated by fasteq_b200.codegen.u1d -- do not edit.\n"
             "#include <cstdio>\n#include <cstdint>\n#include <cuda_runtime.h>\n"
@@ -343,6 +442,7 @@ extern "C" int fasteq_u1d_backward(const fasteq_u1d_graph*, const void*, const v
   return FASTEQ_UNSUPPORTED;  // this module holds the forward kernel only
 }}
 """)
+    src.append(_NOALLOC_FORWARD.replace("@MINB@", str(tun.min_blocks)))
     return "\n".join(src)
 
 

@@ -84,6 +84,22 @@ int fasteq_u1d_describe(fasteq_u1d_desc* out /* host */);
 int fasteq_u1d_forward(const fasteq_u1d_graph* g /* host */, const void* w, const void* x, const void* y,
                        void* out, fasteq_stream_t stream);
 
+/* Forward without any allocation (forward modules only).  No counterpart in the reference, whose
+ * entry points allocate their outputs and leave scatter to atomics.  For callers that cannot
+ * allocate device memory when they need the operator -- a plug-in of a simulation engine that
+ * owns a fixed device arena, code running during stream capture, a loop where an allocation's
+ * implicit synchronisation is not acceptable.  Takes the receiver index itself (non-decreasing,
+ * [n_edges]) and derives the CSR offsets and the per-CTA partition into an array built into the
+ * module (about 1 MB, reserved on every GPU that loads the module, shared by all calls), then runs
+ * the same kernel as fasteq_u1d_forward.  Limits: n_out_rows <= 262144 (else FASTEQ_UNSUPPORTED and
+ * fasteq_last_cuda_error() names the limit); scattered signatures with y not gathered; edges already
+ * sorted by receiver.  Calls that overlap on the GPU race on the shared array -- serialise them.
+ * The first call on each device resolves the array's device address; make it before any stream
+ * capture.  Calls no cudaMalloc / cudaFree or other allocating routine. */
+int fasteq_u1d_forward_noalloc(const int32_t* dst_sorted, const int32_t* x_index, int64_t n_edges,
+                               int64_t n_out_rows, int64_t x_rows, const void* w, const void* x, const void* y,
+                               void* out, fasteq_stream_t stream);
+
 /* grad_w / grad_x / grad_y may be NULL when the module was built without that gradient.
  * Gradients that are accumulated through an index (grad_x, grad_y when gathered, grad_w when
  * shared, grad_y when u is tiled) are zero-filled by this call on `stream` before the kernel. */
