@@ -136,9 +136,8 @@ _NOALLOC_FORWARD = r"""
 // Forward without any allocation.
 //
 // Some hosts of this library cannot call cudaMalloc at the point where they need the operator:
-// a molecular-dynamics engine plug-in that was handed a fixed device arena at start-up, code that
-// runs while a CUDA graph is being captured on the stream, or a real-time control loop where an
-// allocation (an implicit device synchronisation) is forbidden.  The regular entry point leaves
+// a molecular-dynamics engine plug-in that was handed a fixed device arena at start-up, or a
+// real-time control loop where an allocation (an implicit device synchronisation) is forbidden.  The regular entry point leaves
 // the CSR offsets and the per-CTA partition to the caller, who must own buffers for them.  This
 // variant builds both into a fixed array that lives inside this library image and then runs the
 // same forward kernel on them.

@@ -87,8 +87,8 @@ int fasteq_u1d_forward(const fasteq_u1d_graph* g /* host */, const void* w, cons
 /* Forward without any allocation (forward modules only).  No counterpart in the reference, whose
  * entry points allocate their outputs and leave scatter to atomics.  For callers that cannot
  * allocate device memory when they need the operator -- a plug-in of a simulation engine that
- * owns a fixed device arena, code running during stream capture, a loop where an allocation's
- * implicit synchronisation is not acceptable.  Takes the receiver index itself (non-decreasing,
+ * owns a fixed device arena, or a loop where an allocation's implicit synchronisation is not
+ * acceptable.  Takes the receiver index itself (non-decreasing,
  * [n_edges]) and derives the CSR offsets and the per-CTA partition into an array built into the
  * module (about 1 MB, reserved on every GPU that loads the module, shared by all calls), then runs
  * the same kernel as fasteq_u1d_forward.  Limits: n_out_rows <= 262144 (else FASTEQ_UNSUPPORTED and

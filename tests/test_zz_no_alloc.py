@@ -1,7 +1,7 @@
 """The allocation-free forward entry point against the regular one (collected last on purpose).
 
 ``fasteq_u1d_forward_noalloc`` serves callers that cannot allocate device memory at call time (a
-simulation-engine plug-in with a fixed arena, code under stream capture): it derives the CSR
+simulation-engine plug-in with a fixed arena, a loop that must not hit an allocation's implicit sync): it derives the CSR
 offsets and the CTA partition into an array built into the module instead of caller-owned buffers.
 Two calls in a row with different graphs check that what the first call left in that shared array
 does not leak into the second.
