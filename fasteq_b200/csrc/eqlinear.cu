@@ -1,0 +1,224 @@
+// SO3Linear (eqlinear) forward and grad_x as one grouped GEMM kernel, FP32 / FP64 FMA path.
+//
+//   C[b, c_row[g] + t, :] = sum_{q in group g} coeff[q] * A[b, a_row[q] + t, :] @ op(W[q])
+//
+// Forward: A = x, C = out, op = identity ([u, v]); paths are grouped by output row.
+// grad_x : A = grad_out, C = grad_x, op = transpose; paths are grouped by input row.
+// A "GEMM row" is one (batch entry, t) pair; the rows of a group are tiled 64 at a time, every
+// CTA produces a 64 x 64 tile with 4 x 4 outputs per thread and walks K through shared memory.
+// Reference semantics: test/test_eqlinear.py:38-69; problem / path layout
+// fasteq/cuda/src/eqlinear/common/eqlinear_common.h:30-62.
+#include <cstdio>
+#include <cstdint>
+#include <vector>
+#include <algorithm>
+#include <cuda_runtime.h>
+#include "fasteq_b200.h"
+#include "core_common.h"
+
+using namespace fasteq;
+
+namespace {
+
+constexpr int kMaxPaths = 64;
+constexpr int BM = 64, BN = 64, BK = 16, NT = 256;
+
+struct GroupTable {
+  int n_groups;
+  int n_paths;
+  int group_c_row[kMaxPaths];     // first row of C the group writes
+  int group_rows[kMaxPaths];      // 2l+1
+  int group_first[kMaxPaths + 1]; // paths of group g: [first[g], first[g+1])
+  int path_a_row[kMaxPaths];
+  int path_w[kMaxPaths];          // weight block
+  float path_coeff_f[kMaxPaths];
+  double path_coeff_d[kMaxPaths];
+  long long tile_first[kMaxPaths + 1];  // prefix of row tiles per group
+};
+
+template <typename T> __device__ __forceinline__ T coeff_of(const GroupTable& t, int q);
+template <> __device__ __forceinline__ float coeff_of<float>(const GroupTable& t, int q) { return t.path_coeff_f[q]; }
+template <> __device__ __forceinline__ double coeff_of<double>(const GroupTable& t, int q) { return t.path_coeff_d[q]; }
+
+// TRANS = false: W[q] is [K = u][N = v];  TRANS = true: W[q] is [N = u... stored [u][v]] used as [K = v][N = u]
+template <typename T, bool TRANS>
+__global__ void __launch_bounds__(NT) eqlinear_kernel(const __grid_constant__ GroupTable tab, const T* __restrict__ A,
+                                                      const T* __restrict__ W, T* __restrict__ C, long long batch,
+                                                      int a_rows_per_b, int c_rows_per_b, int K, int N, int u, int v) {
+  __shared__ T sA[BK][BM + 4];
+  __shared__ T sW[BK][BN + 4];
+  // locate this CTA's (group, row tile)
+  const long long tile = blockIdx.x;
+  int g = 0;
+  while (g + 1 < tab.n_groups && tile >= tab.tile_first[g + 1]) ++g;
+  const long long row0 = (tile - tab.tile_first[g]) * BM;
+  const int gi = tab.group_rows[g];
+  const long long n_rows = batch * gi;
+  const int n0 = blockIdx.y * BN;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;   // 16 x 16 threads, 4 x 4 outputs each
+  T acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = T(0);
+
+  // A tile [BM][BK]: thread loads elements (m = e*16 + tid/16, k = tid%16), 16 lanes along k (coalesced 64 B)
+  const int lk = threadIdx.x % BK, lm0 = threadIdx.x / BK;
+  size_t abase[4];
+  bool avalid[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const long long r = row0 + e * (NT / BK) + lm0;
+    avalid[e] = r < n_rows;
+    const long long rb = avalid[e] ? r / gi : 0;
+    const int rt = avalid[e] ? (int)(r % gi) : 0;
+    abase[e] = ((size_t)rb * a_rows_per_b + rt) * (size_t)K;
+  }
+
+  for (int q = tab.group_first[g]; q < tab.group_first[g + 1]; ++q) {
+    const T cq = coeff_of<T>(tab, q);
+    const T* aq = A + (size_t)tab.path_a_row[q] * K;
+    const T* wq = W + (size_t)tab.path_w[q] * u * v;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int k = k0 + lk;
+        sA[lk][e * (NT / BK) + lm0] = (avalid[e] && k < K) ? cq * aq[abase[e] + k] : T(0);
+      }
+      // W tile [BK][BN]: 1024 elements, 256 threads x 4
+#pragma unroll
+      for (int e = 0; e < (BK * BN) / NT; ++e) {
+        const int idx = e * NT + threadIdx.x;
+        const int k = idx / BN, n = idx % BN;
+        T val = T(0);
+        if (k0 + k < K && n0 + n < N)
+          val = TRANS ? wq[(size_t)(n0 + n) * v + (k0 + k)] : wq[(size_t)(k0 + k) * v + (n0 + n)];
+        sW[k][n] = val;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < BK; ++k) {
+        T a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] = sA[k][ty * 4 + i];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = sW[k][tx * 4 + j];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] += a[i] * b[j];
+      }
+      __syncthreads();
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const long long rr = row0 + ty * 4 + i;
+    if (rr >= n_rows) continue;
+    const long long b = rr / gi;
+    const int t = (int)(rr % gi);
+    T* crow = C + ((size_t)b * c_rows_per_b + tab.group_c_row[g] + t) * (size_t)N;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) crow[n] = acc[i][j];
+    }
+  }
+}
+
+// rows of C that no group writes must read as zero
+template <typename T>
+__global__ void zero_rows_kernel(T* C, long long batch, int c_rows_per_b, int N, const __grid_constant__ GroupTable tab) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = batch * c_rows_per_b * N;
+  if (idx >= total) return;
+  const int row = (int)((idx / N) % c_rows_per_b);
+  for (int g = 0; g < tab.n_groups; ++g)
+    if (row >= tab.group_c_row[g] && row < tab.group_c_row[g] + tab.group_rows[g]) return;
+  C[idx] = T(0);
+}
+
+int build_table(const fasteq_eqlinear_problem* p, bool dgrad, GroupTable* t, bool* covers_all) {
+  if (!p || p->num_paths < 1 || p->num_paths > kMaxPaths || p->u < 1 || p->v < 1 || p->batch < 0) return FASTEQ_INVALID;
+  if (!p->in_row || !p->out_row || !p->rows || !p->coeff) return FASTEQ_INVALID;
+  const int P = p->num_paths;
+  const int c_rows = dgrad ? p->in_rows : p->out_rows, a_rows = dgrad ? p->out_rows : p->in_rows;
+  std::vector<int> order(P);
+  for (int q = 0; q < P; ++q) order[q] = q;
+  auto crow = [&](int q) { return dgrad ? p->in_row[q] : p->out_row[q]; };
+  auto arow = [&](int q) { return dgrad ? p->out_row[q] : p->in_row[q]; };
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return crow(a) < crow(b); });
+  t->n_groups = 0; t->n_paths = P;
+  std::vector<char> covered(c_rows > 0 ? c_rows : 1, 0);
+  for (int k = 0; k < P; ++k) {
+    const int q = order[k];
+    if (p->rows[q] < 1 || crow(q) < 0 || crow(q) + p->rows[q] > c_rows || arow(q) < 0 || arow(q) + p->rows[q] > a_rows)
+      return FASTEQ_INVALID;
+    if (t->n_groups == 0 || crow(q) != t->group_c_row[t->n_groups - 1]) {
+      // groups must not overlap partially
+      if (t->n_groups > 0 && crow(q) < t->group_c_row[t->n_groups - 1] + t->group_rows[t->n_groups - 1]) return FASTEQ_UNSUPPORTED;
+      t->group_c_row[t->n_groups] = crow(q);
+      t->group_rows[t->n_groups] = p->rows[q];
+      t->group_first[t->n_groups] = k;
+      ++t->n_groups;
+      for (int r = 0; r < p->rows[q]; ++r) covered[crow(q) + r] = 1;
+    } else if (p->rows[q] != t->group_rows[t->n_groups - 1]) {
+      return FASTEQ_UNSUPPORTED;
+    }
+    t->path_a_row[k] = arow(q);
+    t->path_w[k] = q;
+    t->path_coeff_f[k] = (float)p->coeff[q];
+    t->path_coeff_d[k] = p->coeff[q];
+  }
+  t->group_first[t->n_groups] = P;
+  t->tile_first[0] = 0;
+  for (int g = 0; g < t->n_groups; ++g)
+    t->tile_first[g + 1] = t->tile_first[g] + (p->batch * t->group_rows[g] + BM - 1) / BM;
+  *covers_all = true;
+  for (int r = 0; r < c_rows; ++r) if (!covered[r]) *covers_all = false;
+  return FASTEQ_OK;
+}
+
+template <typename T>
+int launch(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const void* a, void* c, cudaStream_t s) {
+  GroupTable tab; bool covers = true;
+  int rc = build_table(p, dgrad, &tab, &covers);
+  if (rc != FASTEQ_OK) return rc;
+  if (p->batch == 0) return FASTEQ_OK;
+  if (!w || !a || !c) return FASTEQ_INVALID;
+  const int K = dgrad ? p->v : p->u, N = dgrad ? p->u : p->v;
+  const int a_rows = dgrad ? p->out_rows : p->in_rows, c_rows = dgrad ? p->in_rows : p->out_rows;
+  if (!covers) {
+    const long long total = p->batch * c_rows * N;
+    zero_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, s>>>((T*)c, p->batch, c_rows, N, tab);
+  }
+  const long long tiles = tab.tile_first[tab.n_groups];
+  if (tiles > 0x7fffffffLL) return FASTEQ_UNSUPPORTED;
+  dim3 grid((unsigned)tiles, (unsigned)((N + BN - 1) / BN));
+  if (dgrad) eqlinear_kernel<T, true><<<grid, NT, 0, s>>>(tab, (const T*)a, (const T*)w, (T*)c, p->batch, a_rows, c_rows, K, N, p->u, p->v);
+  else       eqlinear_kernel<T, false><<<grid, NT, 0, s>>>(tab, (const T*)a, (const T*)w, (T*)c, p->batch, a_rows, c_rows, K, N, p->u, p->v);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
+}
+
+int dispatch(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const void* a, void* c, fasteq_stream_t stream) {
+  if (!p) return FASTEQ_INVALID;
+  switch (p->precision) {
+    case FASTEQ_EQLIN_FP64: return launch<double>(p, dgrad, w, a, c, (cudaStream_t)stream);
+    case FASTEQ_EQLIN_FP32:
+    case FASTEQ_EQLIN_TF32X3: return launch<float>(p, dgrad, w, a, c, (cudaStream_t)stream);  // FP32 FMA satisfies the 3xTF32 bound
+    default: return FASTEQ_INVALID;
+  }
+}
+
+}  // namespace
+
+extern "C" int fasteq_eqlinear_forward(const fasteq_eqlinear_problem* p, const void* w, const void* x, void* out,
+                                       fasteq_stream_t stream) {
+  return dispatch(p, false, w, x, out, stream);
+}
+
+extern "C" int fasteq_eqlinear_dgrad(const fasteq_eqlinear_problem* p, const void* w, const void* grad_out, void* grad_x,
+                                     fasteq_stream_t stream) {
+  return dispatch(p, true, w, grad_out, grad_x, stream);
+}

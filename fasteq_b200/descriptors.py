@@ -156,3 +156,59 @@ def channelwise_tensor_product(irreps_in1, irreps_in2, irreps_out, instructions,
         out_seg_num=irreps_out.num_segments, u_dim=u, y_u_dim=1, instructions=tuple(table),
         irreps_in1=irreps_in1, irreps_in2=irreps_in2, irreps_out=irreps_out,
     )
+
+
+# --------------------------------------------------------------------------- SO3Linear
+
+@dataclass(frozen=True)
+class LinearPath:
+    indices: Tuple[int, int, int]   # (weight block, input segment, output segment)
+    coefficients: float
+
+
+class LinearDescriptor:
+    """``uv,iu,iv`` descriptor with the attribute protocol ``fast_equi_linear`` reads
+    (fasteq/ops/auto_schedule/eqlinear_descriptor.py:228-310): ``operands`` (weight, input,
+    output segment tuples), ``paths[q].indices / .coefficients``, ``get_dims``,
+    ``get_dimensions_dict``, ``operands_and_subscripts``, ``coefficient_subscripts``."""
+
+    coefficient_subscripts = ""
+
+    def __init__(self, in_dims: Sequence[int], out_dims: Sequence[int], u: int, v: int, paths: Sequence[LinearPath]):
+        self.u, self.v = int(u), int(v)
+        self.paths = list(paths)
+        self.operands = [tuple((self.u, self.v) for _ in self.paths), tuple((int(i), self.u) for i in in_dims),
+                         tuple((int(i), self.v) for i in out_dims)]
+        self.operands_and_subscripts = tuple(zip(self.operands, ("uv", "iu", "iv")))
+
+    def get_dims(self, name: str):
+        return {"u": [self.u], "v": [self.v]}[name]
+
+    def get_dimensions_dict(self):
+        return {"i": sorted({s[0] for s in self.operands[1] + self.operands[2]}), "u": [self.u], "v": [self.v]}
+
+    @property
+    def num_weights(self) -> int:
+        return len(self.paths) * self.u * self.v
+
+
+def linear(irreps_in, irreps_out, path_normalization: str = "element") -> LinearDescriptor:
+    """e3nn ``o3.Linear(irreps_in, irreps_out)`` as a uv,iu,iv descriptor.
+
+    One path per (input block, output block) pair of equal irrep, in e3nn's instruction order
+    (input-major); coefficient ``sqrt(1 / fan_in)`` with ``fan_in`` the summed input multiplicity
+    feeding the output block (e3nn/o3/_linear.py:148-159).  Weight block q is e3nn's
+    ``[mul_in, mul_out]`` matrix of instruction q, so ``weight.reshape(P, u, v)`` is the operand."""
+    irreps_in, irreps_out = Irreps(irreps_in), Irreps(irreps_out)
+    u, v = irreps_in.uniform_mul(), irreps_out.uniform_mul()
+    pairs = [(a, b) for a, ba in enumerate(irreps_in) for b, bb in enumerate(irreps_out) if ba.ir == bb.ir]
+    paths = []
+    for q, (a, b) in enumerate(pairs):
+        if path_normalization == "element":
+            fan = sum(irreps_in[a2].mul for a2, b2 in pairs if b2 == b)
+        elif path_normalization == "path":
+            fan = irreps_in[a].mul * len([1 for a2, b2 in pairs if b2 == b])
+        else:
+            fan = 1
+        paths.append(LinearPath((q, a, b), sqrt(1.0 / fan)))
+    return LinearDescriptor([b.ir.dim for b in irreps_in], [b.ir.dim for b in irreps_out], u, v, paths)

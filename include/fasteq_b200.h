@@ -131,6 +131,44 @@ int fasteq_graph_build_csr(const int32_t* dst_sorted, int64_t n_edges, int64_t n
 int fasteq_graph_partition(const int32_t* seg_ptr, int64_t n_rows, int64_t n_edges, int32_t n_parts,
                            int32_t* part_ptr, fasteq_stream_t stream);
 
+/* ------------------------------------------------------------------------- *
+ * SO3Linear ("eqlinear", subscripts uv,iu,iv): per-irrep channel mix
+ *
+ *   out[b, out_row[q] + t, :] += coeff[q] * x[b, in_row[q] + t, :] @ W[q]      t < rows[q]
+ *
+ * x is [batch, in_rows, u], W is [num_paths, u, v], out is [batch, out_rows, v], all contiguous.
+ * Replaces the forward_create / forward_run / dgrad_* entries of the reference's
+ * EqLinearBackendApi (fasteq/cuda/src/eqlinear/common/eqlinear_backend_api.h:12-27; problem layout
+ * eqlinear_common.h:30-62; path mapping (input_row, output_row, weight_path, rows) :32-37).
+ * Stateless: the small path tables are host arrays read during the call; there is no plan object
+ * to create or destroy and no weight repacking.
+ * ------------------------------------------------------------------------- */
+typedef enum fasteq_eqlinear_precision {
+  FASTEQ_EQLIN_TF32X3 = 0,   /* FP32 data, 3xTF32 split on tensor cores (error < 2e-5 rel. Frobenius) */
+  FASTEQ_EQLIN_FP32 = 1,     /* FP32 data, FP32 FMA */
+  FASTEQ_EQLIN_FP64 = 2      /* FP64 data, FP64 FMA */
+} fasteq_eqlinear_precision;
+
+typedef struct fasteq_eqlinear_problem {
+  int32_t precision;          /* fasteq_eqlinear_precision */
+  int32_t u, v;               /* channels in / out */
+  int32_t in_rows, out_rows;  /* I = rows of x per batch entry, J = rows of out per batch entry */
+  int32_t num_paths;          /* <= 64 */
+  int64_t batch;
+  const int32_t* in_row;      /* host [num_paths] first row of x the path reads */
+  const int32_t* out_row;     /* host [num_paths] first row of out the path writes */
+  const int32_t* rows;        /* host [num_paths] 2l+1 */
+  const double* coeff;        /* host [num_paths] */
+} fasteq_eqlinear_problem;
+
+/* out is fully overwritten (rows no path writes become zero). */
+int fasteq_eqlinear_forward(const fasteq_eqlinear_problem* p /* host */, const void* w, const void* x, void* out,
+                            fasteq_stream_t stream);
+/* grad_x[b, in_row[q]+t, :] = sum over paths reading that row of coeff[q] * grad_out[b, out_row[q]+t, :] @ W[q]^T
+ * (the reference exposes grad_x only, eqlinear_runtime.py:86-104). grad_x is fully overwritten. */
+int fasteq_eqlinear_dgrad(const fasteq_eqlinear_problem* p /* host */, const void* w, const void* grad_out,
+                          void* grad_x, fasteq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

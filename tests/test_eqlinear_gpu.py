@@ -1,0 +1,97 @@
+"""GPU parity of SO3Linear against the oracle, with the reference's configurations and bounds
+(test/test_eqlinear.py:15-22, :119-171)."""
+import numpy as np
+import pytest
+import torch
+
+from fasteq_b200.descriptors import linear
+from oracle import eqlinear_ref
+from tests.test_eqlinear_cpu import _FakeDescriptor
+
+pytestmark = pytest.mark.gpu
+
+CONFIGS = {
+    "SMALL_P1": (96, [1, 3, 5, 7]),
+    "MEDIUM_P1": (128, [1, 3, 5, 7]),
+    "MEDIUM_P2": (128, [1, 1, 3, 3, 3, 5, 5, 5, 7, 7]),
+    "LARGE_P1": (224, [1, 3, 5, 7]),
+    "LARGE_P3": (224, [1, 1, 1, 3, 3, 3, 3, 3, 5, 5, 5, 5, 5, 7, 7, 7, 7]),
+}
+
+
+def _make(shape, batch, dtype, seed=0):
+    u, i_dims = CONFIGS[shape]
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(batch, sum(i_dims) * u, generator=g, dtype=torch.float64).to(dtype)
+    w = torch.randn(len(i_dims) * u * u, generator=g, dtype=torch.float64).to(dtype)
+    cg = [float(0.01 + 0.001 * p) for p in range(len(i_dims))]
+    return x, w, cg, i_dims, u
+
+
+def _rel_fro(a, b):
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def _ref(x, w, i_dims, cg, u):
+    m = eqlinear_ref.mapping_from_i_dims(i_dims)
+    x3 = x.double().numpy().reshape(x.shape[0], -1, u)
+    w3 = w.double().numpy().reshape(len(i_dims), u, u)
+    return m, x3, w3, eqlinear_ref.eqlinear_forward(x3, w3, m, cg, eqlinear_ref.out_rows(i_dims))
+
+
+@pytest.mark.parametrize("shape", list(CONFIGS))
+@pytest.mark.parametrize("batch", [512, 2944])
+def test_fp64_forward_and_grad(shape, batch):
+    from fasteq_b200.ops.eqlinear import fast_equi_linear
+    x, w, cg, i_dims, u = _make(shape, batch, torch.float64)
+    m, x3, w3, ref = _ref(x, w, i_dims, cg, u)
+    xd = x.cuda().requires_grad_(True)
+    out = fast_equi_linear(_FakeDescriptor(i_dims, u, u, cg), w.cuda(), xd)
+    assert out.shape == (batch, eqlinear_ref.out_rows(i_dims) * u)
+    assert _rel_fro(out.detach().cpu().numpy().reshape(ref.shape), ref) <= 1e-12
+    r = torch.randn(out.shape, generator=torch.Generator().manual_seed(1), dtype=torch.float64)
+    (gx,) = torch.autograd.grad(out, xd, r.cuda())
+    ref_gx = eqlinear_ref.eqlinear_dgrad(r.numpy().reshape(ref.shape), w3, m, cg, sum(i_dims))
+    assert _rel_fro(gx.cpu().numpy().reshape(ref_gx.shape), ref_gx) <= 1e-12
+
+
+@pytest.mark.parametrize("shape", list(CONFIGS))
+@pytest.mark.parametrize("precision,bound", [("fp32", None), (None, 2e-5)])
+def test_fp32_paths(shape, precision, bound):
+    from fasteq_b200.ops.eqlinear import fast_equi_linear
+    batch = 1024
+    x, w, cg, i_dims, u = _make(shape, batch, torch.float32)
+    m, x3, w3, ref = _ref(x, w, i_dims, cg, u)
+    # error of a plain float32 evaluation of the same loop: the strict-FP32 yardstick of the reference
+    ref32 = np.zeros(ref.shape, dtype=np.float32)
+    for (ir, orow, wp, rows), c in zip(m, cg):
+        ref32[:, orow:orow + rows, :] += np.float32(c) * (x3[:, ir:ir + rows, :].astype(np.float32) @ w3[wp].astype(np.float32))
+    torch_rel = _rel_fro(ref32.astype(np.float64), ref)
+    xd = x.cuda().requires_grad_(True)
+    out = fast_equi_linear(_FakeDescriptor(i_dims, u, u, cg), w.cuda(), xd, compute_precision=precision)
+    err = _rel_fro(out.detach().cpu().double().numpy().reshape(ref.shape), ref)
+    assert err <= (bound if bound is not None else 1.05 * torch_rel + 1e-7), (err, torch_rel)
+    r = torch.randn(out.shape, generator=torch.Generator().manual_seed(1))
+    (gx,) = torch.autograd.grad(out, xd, r.cuda())
+    ref_gx = eqlinear_ref.eqlinear_dgrad(r.double().numpy().reshape(ref.shape), w3, m, cg, sum(i_dims))
+    errg = _rel_fro(gx.cpu().double().numpy().reshape(ref_gx.shape), ref_gx)
+    assert errg <= (bound if bound is not None else 1.05 * torch_rel + 1e-7)
+
+
+def test_e3nn_style_descriptor_with_shared_outputs_and_odd_sizes():
+    """Explicit path indices, several paths into one output block, u != v, batch not a tile multiple."""
+    from fasteq_b200.ops.eqlinear import fast_equi_linear, _descriptor_problem
+    d = linear("24x0e+24x0e+24x1o+24x2e", "40x0e+40x1o+40x1o+40x2e")
+    mapping, coeff, u, v, I, J = _descriptor_problem(d)
+    g = torch.Generator().manual_seed(5)
+    B = 333
+    x = torch.randn(B, I * u, generator=g, dtype=torch.float64)
+    w = torch.randn(len(d.paths) * u * v, generator=g, dtype=torch.float64)
+    ref = eqlinear_ref.eqlinear_forward(x.numpy().reshape(B, I, u), w.numpy().reshape(-1, u, v), mapping, coeff, J)
+    for dt, tol in ((torch.float64, 1e-12), (torch.float32, 2e-5)):
+        xd = x.to(dt).cuda().requires_grad_(True)
+        out = fast_equi_linear(d, w.to(dt).cuda(), xd)
+        assert _rel_fro(out.detach().cpu().double().numpy().reshape(ref.shape), ref) <= tol
+        (gx,) = torch.autograd.grad(out.sum(), xd)
+        ref_gx = eqlinear_ref.eqlinear_dgrad(np.ones_like(ref), w.numpy().reshape(-1, u, v), mapping, coeff, I)
+        assert _rel_fro(gx.cpu().double().numpy().reshape(ref_gx.shape), ref_gx) <= tol
