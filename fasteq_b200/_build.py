@@ -42,7 +42,7 @@ def nvcc_path() -> str:
 
 def compile_shared(sources: List[str], out_so: str, extra: Optional[List[str]] = None, verbose: bool = False) -> str:
     os.makedirs(os.path.dirname(out_so), exist_ok=True)
-    tmp = out_so + f".tmp{os.getpid()}"
+    tmp = out_so + f".tmp{os.getpid()}_{threading.get_ident()}"
     cmd = [nvcc_path()] + ARCH + COMMON + (extra or []) + ["-o", tmp] + sources
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
@@ -78,15 +78,19 @@ def build_generated(name: str, source: str, extra: Optional[List[str]] = None, f
     """Compile generated CUDA text into ``lib/jit/<name>.so`` unless an up-to-date build exists."""
     so = os.path.join(JIT, name + ".so")
     cu = os.path.join(JIT, name + ".cu")
-    with _lock:
-        if not force and os.path.exists(so) and os.path.exists(cu):
-            with open(cu) as f:
-                if f.read() == source and _newer(so, headers()):
-                    return so
-        os.makedirs(JIT, exist_ok=True)
-        with open(cu, "w") as f:
-            f.write(source)
-        log = compile_shared([cu], so, extra=["-Xptxas", "-v"] + (extra or []))
-        with open(os.path.join(JIT, name + ".log"), "w") as f:
-            f.write(log)
+    if not force and os.path.exists(so) and os.path.exists(cu):
+        with open(cu) as f:
+            if f.read() == source and _newer(so, headers()):
+                return so
+    os.makedirs(JIT, exist_ok=True)
+    tmp_cu = cu + f".tmp{os.getpid()}_{threading.get_ident()}.cu"
+    with open(tmp_cu, "w") as f:
+        f.write(source)
+    try:
+        log = compile_shared([tmp_cu], so, extra=["-Xptxas", "-v"] + (extra or []))
+    finally:
+        if os.path.exists(tmp_cu):
+            os.replace(tmp_cu, cu)
+    with open(os.path.join(JIT, name + ".log"), "w") as f:
+        f.write(log)
     return so

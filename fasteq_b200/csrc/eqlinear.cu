@@ -79,11 +79,16 @@ __global__ void __launch_bounds__(NT) eqlinear_kernel(const __grid_constant__ Gr
     const T cq = coeff_of<T>(tab, q);
     const T* aq = A + (size_t)tab.path_a_row[q] * K;
     const T* wq = W + (size_t)tab.path_w[q] * u * v;
+    T pacc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pacc[i][j] = T(0);
     for (int k0 = 0; k0 < K; k0 += BK) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int k = k0 + lk;
-        sA[lk][e * (NT / BK) + lm0] = (avalid[e] && k < K) ? cq * aq[abase[e] + k] : T(0);
+        sA[lk][e * (NT / BK) + lm0] = (avalid[e] && k < K) ? aq[abase[e] + k] : T(0);
       }
       // W tile [BK][BN]: 1024 elements, 256 threads x 4
 #pragma unroll
@@ -96,6 +101,14 @@ __global__ void __launch_bounds__(NT) eqlinear_kernel(const __grid_constant__ Gr
         sW[k][n] = val;
       }
       __syncthreads();
+      // blocked summation: a chunk of BK products is summed on its own, then added to the path's
+      // partial sum, which is scaled and added to the total -- the rounding error grows with the
+      // square roots of the three lengths instead of with the full K * paths
+      T part[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) part[i][j] = T(0);
 #pragma unroll
       for (int k = 0; k < BK; ++k) {
         T a[4], b[4];
@@ -106,10 +119,18 @@ __global__ void __launch_bounds__(NT) eqlinear_kernel(const __grid_constant__ Gr
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) acc[i][j] += a[i] * b[j];
+          for (int j = 0; j < 4; ++j) part[i][j] += a[i] * b[j];
       }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pacc[i][j] += part[i][j];
       __syncthreads();
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] += cq * pacc[i][j];
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {

@@ -212,3 +212,131 @@ def linear(irreps_in, irreps_out, path_normalization: str = "element") -> Linear
             fan = 1
         paths.append(LinearPath((q, a, b), sqrt(1.0 / fan)))
     return LinearDescriptor([b.ir.dim for b in irreps_in], [b.ir.dim for b in irreps_out], u, v, paths)
+
+
+# --------------------------------------------------------------------------- SymmetricContraction
+
+@dataclass
+class STCDescriptor:
+    """Path table of a symmetric tensor contraction in the reference's padded layout
+    (fasteq/ops/auto_schedule/models.py:49-66): row p = ``[a_1 .. a_n, d, v, pad ...]`` meaning
+    ``out[v] += coeff[p] * x1[a_1] * .. * x1[a_n] * x0[d]`` with ``n = 1..3``."""
+    paths: np.ndarray        # int64 [P, max_len], suffix padded with ``pad_value``
+    coeffs: np.ndarray       # float64 [P]
+    x1_segs: int
+    x0_segs: int
+    out_segs: int
+    u_dim: int
+    pad_value: int = -1
+    weight_layout: Tuple[Tuple[int, int, int], ...] = ()  # per x0 segment: (degree, out block, basis index)
+    irreps_in: Optional[Irreps] = None
+    irreps_out: Optional[Irreps] = None
+
+    @property
+    def num_paths(self) -> int:
+        return int(self.paths.shape[0])
+
+    def tensors(self, dtype=None, device=None):
+        """``(coeffs_tensor, paths_tensor [P, L], idx_lists_tensor [L, P])`` for ``fast_stc_uniform1d_jit``."""
+        import torch
+        dtype = dtype or torch.float32
+        p = torch.as_tensor(self.paths, dtype=torch.int32, device=device)
+        return torch.as_tensor(self.coeffs, dtype=dtype, device=device), p.contiguous(), p.t().contiguous()
+
+
+def _independent_rows(mat: np.ndarray, tol: float = 1e-9) -> List[int]:
+    """Greedy choice of linearly independent rows (modified Gram-Schmidt), keeping the originals
+    so that the selected basis tensors stay as sparse as the Clebsch-Gordan products they come from."""
+    chosen, basis = [], []
+    for r in range(mat.shape[0]):
+        v = mat[r].astype(np.float64).copy()
+        n0 = np.linalg.norm(v)
+        if n0 < tol:
+            continue
+        for b in basis:
+            v -= (b @ v) * b
+        for b in basis:  # second pass for stability
+            v -= (b @ v) * b
+        n = np.linalg.norm(v)
+        if n > tol * max(1.0, n0) and n > 1e-7 * n0:
+            basis.append(v / n)
+            chosen.append(r)
+    return chosen
+
+
+def symmetric_contraction(irreps_in, irreps_out, degrees: Sequence[int] = (1, 2, 3)) -> STCDescriptor:
+    """Symmetric contraction ``out_L = sum_nu sum_eta W[nu, L, eta] * B^{nu,L,eta}[a_1..a_nu, m] x[a_1]..x[a_nu]``.
+
+    For every degree ``nu`` and output irrep ``L`` the basis tensors ``B`` span the equivariant,
+    permutation-symmetric maps ``Sym^nu(V) -> L``, ``V`` being ``irreps_in`` at multiplicity one:
+    iterated real Clebsch-Gordan couplings are symmetrised over the inputs and a maximal
+    independent subset is kept (each scaled to unit Frobenius norm).  The role of
+    cuEquivariance's ``symmetric_contraction`` descriptor the reference benches call
+    (test/bench_tensor_product_uniform1d.py:185); the basis differs from that package's by an
+    invertible mix of the weights, which the learned weights absorb.  Entries that are equal under
+    index permutation are stored once with ``a_1 <= a_2 <= a_3`` and their multiplicity in the coefficient."""
+    import itertools
+    from math import factorial
+    irreps_in, irreps_out = Irreps(irreps_in), Irreps(irreps_out)
+    u = irreps_in.uniform_mul()
+    if any(b.mul != u for b in irreps_out):
+        raise ValueError("irreps_out must carry the multiplicity of irreps_in")
+    in_off = irreps_in.segment_offsets()
+    out_off = irreps_out.segment_offsets()
+    n_in = irreps_in.num_segments
+    blocks = [(b.ir.l, b.ir.p, o) for b, o in zip(irreps_in, in_off)]
+
+    def embed(t: np.ndarray, offs: Sequence[int]) -> np.ndarray:
+        full = np.zeros((n_in,) * len(offs) + (t.shape[-1],))
+        sl = tuple(slice(o, o + s) for o, s in zip(offs, t.shape[:-1])) + (slice(None),)
+        full[sl] = t
+        return full
+
+    paths, coeffs, layout = [], [], []
+    for ob, (oblk, ooff) in enumerate(zip(irreps_out, out_off)):
+        L, P = oblk.ir.l, oblk.ir.p
+        for nu in degrees:
+            cands = []
+            if nu == 1:
+                for (l1, p1, o1) in blocks:
+                    if l1 == L and p1 == P:
+                        cands.append(embed(np.eye(2 * L + 1)[:, :], [o1]))
+            elif nu == 2:
+                for (l1, p1, o1), (l2, p2, o2) in itertools.product(blocks, repeat=2):
+                    if p1 * p2 == P and abs(l1 - l2) <= L <= l1 + l2:
+                        cands.append(embed(wigner_3j(l1, l2, L), [o1, o2]))
+            elif nu == 3:
+                for (l1, p1, o1), (l2, p2, o2), (l3, p3, o3) in itertools.product(blocks, repeat=3):
+                    if p1 * p2 * p3 != P:
+                        continue
+                    for l12 in range(abs(l1 - l2), l1 + l2 + 1):
+                        if abs(l12 - l3) <= L <= l12 + l3:
+                            t = np.einsum("abn,ncm->abcm", wigner_3j(l1, l2, l12), wigner_3j(l12, l3, L))
+                            cands.append(embed(t, [o1, o2, o3]))
+            else:
+                raise NotImplementedError("degrees 1..3 are supported")
+            if not cands:
+                continue
+            sym = []
+            for t in cands:
+                s = sum(np.transpose(t, perm + (nu,)) for perm in itertools.permutations(range(nu))) / factorial(nu)
+                sym.append(s)
+            mat = np.stack([s.reshape(-1) for s in sym])
+            keep = _independent_rows(mat)
+            for eta, r in enumerate(keep):
+                b = sym[r] / np.linalg.norm(sym[r])
+                d = len(layout)
+                layout.append((nu, ob, eta))
+                for idx in zip(*np.nonzero(np.abs(b) > 1e-12)):
+                    a, m = idx[:-1], idx[-1]
+                    if tuple(sorted(a)) != tuple(a):
+                        continue  # the sorted representative carries the whole orbit
+                    mult = len(set(itertools.permutations(a)))
+                    paths.append(list(a) + [d, ooff + m])
+                    coeffs.append(mult * b[idx])
+    max_len = max(len(p) for p in paths)
+    arr = np.full((len(paths), max_len), -1, dtype=np.int64)
+    for r, p in enumerate(paths):
+        arr[r, :len(p)] = p
+    return STCDescriptor(arr, np.asarray(coeffs, dtype=np.float64), n_in, len(layout), irreps_out.num_segments, u,
+                         -1, tuple(layout), irreps_in, irreps_out)

@@ -46,15 +46,20 @@ def get_module(spec: U1DSpec, direction: str, needs=(False, False, False), tunin
     key = (spec, direction, tuple(needs), tun)
     with _lock:
         mod = _MODULES.get(key)
-        if mod is None:
-            tag = spec.key(f"{_EMITTER_VERSION}|{direction}|{tuple(needs)}|{tun}")
-            if direction == "fwd":
-                source = _emit.emit_forward(spec, tun)
-            else:
-                source = _emit.emit_backward(spec, tun, *needs)
-            so = _build.build_generated(f"u1d_{direction}_{tag}", source)
-            mod = _cabi.U1DModule(so)
-            _MODULES[key] = mod
+    if mod is None:
+        # compile outside the lock: different signatures build in parallel; the build itself is
+        # atomic (temporary file + rename), so a duplicate build of one signature is harmless
+        tag = spec.key(f"{_EMITTER_VERSION}|{direction}|{tuple(needs)}|{tun}")
+        if direction == "fwd":
+            source = _emit.emit_forward(spec, tun)
+        else:
+            source = _emit.emit_backward(spec, tun, *needs)
+        so = _build.build_generated(f"u1d_{direction}_{tag}", source)
+        with _lock:
+            mod = _MODULES.get(key)
+            if mod is None:
+                mod = _cabi.U1DModule(so)
+                _MODULES[key] = mod
     return mod
 
 

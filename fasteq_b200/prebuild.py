@@ -25,16 +25,36 @@ def cwtp_spec(in1: str, lmax_sh: int, lmax_out: int, dtype: str):
                      y_segs=d.y_seg_num, out_segs=d.out_seg_num, u=d.u_dim, dtype=dtype)
 
 
+# (irreps_in, irreps_out, dtypes) for the symmetric contraction
+STANDARD_STC = [
+    ("128x0e+128x1o+128x2e+128x3o", "128x0e+128x1o", ("f32", "f64")),   # config 1 product basis
+]
+
+
+def stc_spec(irreps_in: str, irreps_out: str, dtype: str):
+    from .codegen.stc import make_stc_spec
+    from .descriptors import symmetric_contraction
+    d = symmetric_contraction(irreps_in, irreps_out)
+    return make_stc_spec(d.paths, d.coeffs, x1_segs=d.x1_segs, x0_segs=d.x0_segs, out_segs=d.out_segs, u=d.u_dim, dtype=dtype)
+
+
 def build_standard_modules(verbose: bool = False) -> None:
     from .ops.uniform1d_jit import get_module
+    from .ops import stc_uniform1d_jit as stc
     jobs = []
     for in1, lsh, lout, dtypes in STANDARD_CWTP:
         for dt in dtypes:
             spec = cwtp_spec(in1, lsh, lout, dt)
             jobs.append((spec, "fwd", (False, False, False)))
             jobs.append((spec, "bwd", (True, True, True)))
+    stc_jobs = []
+    for a, b, dtypes in STANDARD_STC:
+        for dt in dtypes:
+            sp = stc_spec(a, b, dt)
+            stc_jobs += [(sp, "fwd", False), (sp, "bwd", False), (sp, "bwd", True)]
     t0 = time.time()
     with ThreadPoolExecutor(max_workers=8) as ex:
         list(ex.map(lambda j: get_module(*j), jobs))
+        list(ex.map(lambda j: stc.get_module(*j), stc_jobs))
     if verbose:
-        print(f"built {len(jobs)} Uniform1D modules in {time.time() - t0:.1f} s")
+        print(f"built {len(jobs)} Uniform1D and {len(stc_jobs)} symmetric-contraction modules in {time.time() - t0:.1f} s")

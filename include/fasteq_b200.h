@@ -111,6 +111,31 @@ int fasteq_u1d_backward(const fasteq_u1d_graph* g /* host */, const void* grad_o
 int fasteq_u1d_device_status(int32_t* code /* host */);
 
 /* ------------------------------------------------------------------------- *
+ * Symmetric tensor contraction (STC Uniform1D) generated modules.
+ *
+ *   out[b, v, u] = sum_p c_p * prod_t x1[b, a_{p,t}, u] * x0[i0[b], d_p, u]
+ *
+ * x1 [batch, x1_segs, u], x0 [n_species, x0_segs, u], i0 int32 [batch], out [batch, out_segs, u].
+ * Replaces the pybind `run(x1, x0_g, V)` / `run(grad_out, x1, x0_g, V)` of the reference's JIT
+ * modules (fasteq/ops/stc_uniform1d_jit.py:857,1070); the species gather x0[i0] is done inside.
+ * ------------------------------------------------------------------------- */
+typedef struct fasteq_stc_desc {
+  int32_t abi_version, dtype, u, x1_segs, x0_segs, out_segs, num_paths;
+  int32_t direction;   /* 0 forward module, 1 backward module */
+  int32_t need_gx0;    /* backward: also writes the per-node weight gradient */
+} fasteq_stc_desc;
+
+int fasteq_stc_describe(fasteq_stc_desc* out /* host */);
+int fasteq_stc_forward(const void* x1, const void* x0, const int32_t* i0, int64_t batch, int64_t n_species, void* out,
+                       fasteq_stream_t stream);
+/* grad_x1 [batch, x1_segs, u] is fully overwritten.  grad_x0_per_node [batch, x0_segs, u] (modules
+ * built with need_gx0; else pass NULL) holds each node's contribution; the caller sums rows of equal
+ * species (the reference does the same with index_add_, stc_uniform1d_jit.py:883-886). */
+int fasteq_stc_backward(const void* grad_out, const void* x1, const void* x0, const int32_t* i0, int64_t batch,
+                        int64_t n_species, void* grad_x1, void* grad_x0_per_node, fasteq_stream_t stream);
+int fasteq_stc_device_status(int32_t* code /* host */);
+
+/* ------------------------------------------------------------------------- *
  * Core library.
  * ------------------------------------------------------------------------- */
 const char* fasteq_status_string(int status);
