@@ -136,6 +136,15 @@ int fasteq_stc_backward(const void* grad_out, const void* x1, const void* x0, co
 int fasteq_stc_device_status(int32_t* code /* host */);
 
 /* ------------------------------------------------------------------------- *
+ * Spherical harmonics generated modules (one per degree list / dtype / normalisation):
+ * vec [n, 3] -> out [n, sum(2l+1)], and the gradient with respect to vec.  Replaces the
+ * reference's Triton kernels behind fasteq/triton/spherical_harmonics.py:493-570.
+ * ------------------------------------------------------------------------- */
+int fasteq_sh_num_outputs(void);
+int fasteq_sh_forward(const void* vec, int64_t n, void* out, fasteq_stream_t stream);
+int fasteq_sh_backward(const void* vec, const void* grad_out, int64_t n, void* grad_vec, fasteq_stream_t stream);
+
+/* ------------------------------------------------------------------------- *
  * Core library.
  * ------------------------------------------------------------------------- */
 const char* fasteq_status_string(int status);
