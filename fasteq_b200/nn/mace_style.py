@@ -1,0 +1,124 @@
+"""Synthetic MACE-style model for the BASELINE model configurations (energy + forces).
+
+Architecture (configuration 1): species embedding -> ``num_layers`` x { SO3Linear (up),
+ChannelwiseTensorProduct with SH(l <= 3) edge attributes and radial-MLP weights + scatter-sum,
+SO3Linear (mix to 128x{0e,1o,2e,3o}), SymmetricContraction (correlation 3) -> hidden, SO3Linear }
+-> per-layer scalar readout; ``E = sum_atoms``; ``F = -dE/dpos`` by autograd.  Radial basis: 8 Bessel
+functions times a p = 5 polynomial envelope (…/nequip/nn/embedding/_edge.py:174-189,
+…/nequip/nn/embedding/cutoffs.py:17-27), fed to a 64-64-64 SiLU MLP per layer.  Random weights;
+this is a throughput and parity vehicle, not a trained potential.
+
+Every tensor between operators is ``ir_mul``; nothing is transposed.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from ..descriptors import full_channelwise_instructions
+from ..irreps import Irreps
+from ..ops.spherical_harmonics import SphericalHarmonics
+from .modules import ChannelwiseTensorProduct, SO3Linear, SymmetricContraction
+
+
+def bessel_basis(r: torch.Tensor, r_max: float, num_basis: int) -> torch.Tensor:
+    n = torch.arange(1, num_basis + 1, device=r.device, dtype=r.dtype)
+    return math.sqrt(2.0 / r_max) * torch.sin(n * math.pi * r.unsqueeze(-1) / r_max) / r.unsqueeze(-1)
+
+
+def polynomial_cutoff(r: torch.Tensor, r_max: float, p: int = 5) -> torch.Tensor:
+    x = r / r_max
+    env = 1.0 - (p + 1.0) * (p + 2.0) / 2.0 * x ** p + p * (p + 2.0) * x ** (p + 1) - p * (p + 1.0) / 2.0 * x ** (p + 2)
+    return env * (x < 1.0)
+
+
+class RadialMLP(torch.nn.Module):
+    def __init__(self, num_basis: int, hidden: List[int], out_dim: int):
+        super().__init__()
+        dims = [num_basis] + hidden + [out_dim]
+        self.layers = torch.nn.ModuleList(torch.nn.Linear(a, b, bias=False) for a, b in zip(dims[:-1], dims[1:]))
+        for lin in self.layers:
+            torch.nn.init.normal_(lin.weight, std=1.0 / math.sqrt(lin.in_features))
+
+    def forward(self, x):
+        for i, lin in enumerate(self.layers):
+            x = lin(x)
+            if i + 1 < len(self.layers):
+                x = torch.nn.functional.silu(x)
+        return x
+
+
+class InteractionLayer(torch.nn.Module):
+    def __init__(self, irreps_in: Irreps, hidden: Irreps, sh_lmax: int, lmax_mid: int, num_species: int, num_basis: int,
+                 radial_hidden: List[int], correlation: int, avg_num_neighbors: float):
+        super().__init__()
+        mul = irreps_in.uniform_mul()
+        sh = Irreps.spherical_harmonics(sh_lmax)
+        self.linear_up = SO3Linear(irreps_in, irreps_in)
+        irreps_tp, instr = full_channelwise_instructions(irreps_in, sh, lmax_mid)
+        self.conv_tp = ChannelwiseTensorProduct(irreps_in, sh, irreps_tp, instr)
+        self.radial = RadialMLP(num_basis, radial_hidden, self.conv_tp.weight_numel)
+        self.irreps_mid = Irreps([(mul, (l, (-1) ** l)) for l in range(lmax_mid + 1)])
+        self.linear_mid = SO3Linear(irreps_tp, self.irreps_mid)
+        self.product = SymmetricContraction(self.irreps_mid, hidden, num_species, correlation)
+        self.linear_out = SO3Linear(hidden, hidden)
+        self.inv_neighbors = 1.0 / avg_num_neighbors
+
+    def forward(self, h, species, edge_sh, edge_radial, edge_dst, edge_src):
+        up = self.linear_up(h)
+        w = self.radial(edge_radial)
+        msg = self.conv_tp(up, edge_sh, w, edge_dst, edge_src)
+        mid = self.linear_mid(msg) * self.inv_neighbors
+        prod = self.product(mid, species)
+        return self.linear_out(prod)
+
+
+class MACEStyleModel(torch.nn.Module):
+    def __init__(self, num_species: int = 4, channels: int = 128, hidden_lmax: int = 1, sh_lmax: int = 3, lmax_mid: int = 3,
+                 num_layers: int = 2, r_max: float = 5.0, num_basis: int = 8, radial_hidden=(64, 64, 64), correlation: int = 3,
+                 avg_num_neighbors: float = 52.0, envelope_p: int = 5):
+        super().__init__()
+        self.r_max, self.num_basis, self.envelope_p, self.channels = r_max, num_basis, envelope_p, channels
+        hidden = Irreps([(channels, (l, (-1) ** l)) for l in range(hidden_lmax + 1)])
+        self.hidden = hidden
+        self.embedding = torch.nn.Parameter(torch.randn(num_species, channels))
+        self.sh = SphericalHarmonics(list(range(sh_lmax + 1)), True, "component")
+        layers = []
+        irreps_in = Irreps([(channels, (0, 1))])
+        for _ in range(num_layers):
+            layers.append(InteractionLayer(irreps_in, hidden, sh_lmax, lmax_mid, num_species, num_basis, list(radial_hidden),
+                                           correlation, avg_num_neighbors))
+            irreps_in = hidden
+        self.layers = torch.nn.ModuleList(layers)
+        self.readouts = torch.nn.ParameterList(torch.nn.Parameter(torch.randn(channels) / math.sqrt(channels)) for _ in range(num_layers))
+
+    def edge_features(self, pos, edge_src, edge_dst, edge_shift):
+        vec = pos[edge_src] + edge_shift - pos[edge_dst]
+        r = vec.norm(dim=-1)
+        radial = bessel_basis(r, self.r_max, self.num_basis) * polynomial_cutoff(r, self.r_max, self.envelope_p).unsqueeze(-1)
+        return self.sh(vec), radial
+
+    def node_energies(self, pos, species, edge_src, edge_dst, edge_shift):
+        edge_sh, edge_radial = self.edge_features(pos, edge_src, edge_dst, edge_shift)
+        h = self.embedding[species]
+        e = pos.new_zeros(pos.shape[0])
+        for layer, ro in zip(self.layers, self.readouts):
+            h = layer(h, species, edge_sh, edge_radial, edge_dst, edge_src)
+            e = e + h[:, : self.channels] @ ro          # scalars are the first segment of the ir_mul row
+        return e
+
+    def forward(self, pos, species, edge_src, edge_dst, edge_shift, node_graph=None, n_graphs: int = 1, forces: bool = True):
+        if forces:
+            pos = pos.detach().requires_grad_(True)
+        e_node = self.node_energies(pos, species, edge_src, edge_dst, edge_shift)
+        if node_graph is None:
+            energy = e_node.sum().reshape(1)
+        else:
+            energy = torch.zeros(n_graphs, dtype=e_node.dtype, device=e_node.device).index_add(0, node_graph, e_node)
+        out = {"energy": energy}
+        if forces:
+            (g,) = torch.autograd.grad(e_node.sum(), pos)
+            out["forces"] = -g
+        return out

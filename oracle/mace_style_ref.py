@@ -1,0 +1,86 @@
+"""CPU oracle of the synthetic MACE-style model: the same architecture evaluated with dense torch
+operations straight from the path tables (float64, autograd for the forces).
+
+Each operator is the path formula of the corresponding oracle (``uniform1d_ref``, ``eqlinear_ref``,
+``stc_ref``) written with differentiable torch ops; the model structure follows
+``fasteq_b200.nn.mace_style`` and shares its parameters through ``load_from``.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from oracle import sh_ref
+
+
+def u1d_scatter(w, x, y, d, src, dst, n_out):
+    """ir_mul Uniform1D with gather + scatter: w [E, I*U], x [N, J*U], y [E, K]."""
+    U = d.u_dim
+    w3, x3 = w.reshape(-1, d.w_seg_num, U), x.reshape(-1, d.x_seg_num, U)[src]
+    msg = torch.zeros(w.shape[0], d.out_seg_num, U, dtype=x.dtype)
+    cols = [msg[:, v, :] for v in range(d.out_seg_num)]
+    acc = [None] * d.out_seg_num
+    for i, j, k, v, c in zip(d.i_list, d.j_list, d.k_list, d.v_list, d.coeff_list):
+        t = float(c) * w3[:, i, :] * x3[:, j, :] * y[:, k:k + 1]
+        acc[v] = t if acc[v] is None else acc[v] + t
+    msg = torch.stack([a if a is not None else torch.zeros_like(w3[:, 0, :]) for a in acc], dim=1)
+    out = torch.zeros(n_out, d.out_seg_num, U, dtype=x.dtype).index_add(0, dst, msg)
+    return out.reshape(n_out, -1)
+
+
+def eqlinear(x, w, desc):
+    from fasteq_b200.ops.eqlinear import _descriptor_problem
+    mapping, coeff, u, v, I, J = _descriptor_problem(desc)
+    x3, w3 = x.reshape(-1, I, u), w.reshape(len(mapping), u, v)
+    rows = [None] * J
+    for (ir, orow, wp, n), c in zip(mapping, coeff):
+        t = float(c) * (x3[:, ir:ir + n, :] @ w3[wp])
+        for k in range(n):
+            rows[orow + k] = t[:, k, :] if rows[orow + k] is None else rows[orow + k] + t[:, k, :]
+    zero = torch.zeros(x3.shape[0], v, dtype=x.dtype)
+    return torch.stack([r if r is not None else zero for r in rows], dim=1).reshape(x3.shape[0], -1)
+
+
+def stc(x1, x0, i0, d):
+    from oracle.stc_ref import split_paths
+    U = d.u_dim
+    x3, wg = x1.reshape(-1, d.x1_segs, U), x0[i0]
+    acc = [None] * d.out_segs
+    for (a, dd, v), c in zip(split_paths(d.paths), d.coeffs):
+        t = float(c) * wg[:, dd, :]
+        for ai in a:
+            t = t * x3[:, ai, :]
+        acc[v] = t if acc[v] is None else acc[v] + t
+    zero = torch.zeros(x3.shape[0], U, dtype=x1.dtype)
+    return torch.stack([r if r is not None else zero for r in acc], dim=1).reshape(x3.shape[0], -1)
+
+
+def energy_and_forces(model, pos, species, edge_src, edge_dst, edge_shift):
+    """Evaluate ``model`` (a ``MACEStyleModel`` whose parameters were moved to CPU/float64) with the oracle operators."""
+    from fasteq_b200.nn.mace_style import bessel_basis, polynomial_cutoff
+    pos = pos.detach().double().requires_grad_(True)
+    p = {k: v.detach().double().cpu() for k, v in model.state_dict().items()}
+    vec = pos[edge_src] + edge_shift.double() - pos[edge_dst]
+    r = vec.norm(dim=-1)
+    radial = bessel_basis(r, model.r_max, model.num_basis) * polynomial_cutoff(r, model.r_max, model.envelope_p).unsqueeze(-1)
+    ysh = sh_ref.spherical_harmonics(max(model.sh._ls), vec, normalize=True, normalization="component")
+    h = p["embedding"][species]
+    e = torch.zeros(pos.shape[0], dtype=torch.float64)
+    for li, layer in enumerate(model.layers):
+        pre = f"layers.{li}."
+        up = eqlinear(h, p[pre + "linear_up.weight"], layer.linear_up.descriptor)
+        w = radial
+        n_lin = len(layer.radial.layers)
+        for k in range(n_lin):
+            w = w @ p[pre + f"radial.layers.{k}.weight"].T
+            if k + 1 < n_lin:
+                w = torch.nn.functional.silu(w)
+        msg = u1d_scatter(w, up, ysh, layer.conv_tp.descriptor, edge_src, edge_dst, pos.shape[0])
+        mid = eqlinear(msg, p[pre + "linear_mid.weight"], layer.linear_mid.descriptor) * layer.inv_neighbors
+        prod = stc(mid, p[pre + "product.weight"], species, layer.product.descriptor)
+        h = eqlinear(prod, p[pre + "linear_out.weight"], layer.linear_out.descriptor)
+        e = e + h[:, : model.channels] @ p[f"readouts.{li}"]
+    (g,) = torch.autograd.grad(e.sum(), pos)
+    return e.detach(), -g
