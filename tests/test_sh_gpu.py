@@ -34,7 +34,7 @@ def test_normalizations_and_degree_subsets(normalization):
     assert (out.cpu() - ref).abs().max() < 1e-12
     assert str(mod.irreps_out) == "1x1o+1x3o"
     with pytest.raises(ValueError):
-        SphericalHarmonics("1x1e", True)          # parity inconsistent with a vector input
+        SphericalHarmonics("1x2o", True)          # an even degree cannot be odd
     with pytest.raises(ValueError):
         mod(torch.zeros(4, 2, device="cuda"))
 
