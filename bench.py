@@ -148,6 +148,47 @@ def cpu_reference_run(inp, steps: int, warmup: int, threads: int):
     return inp["E"] * len(times) / sum(times), float(np.mean(times))
 
 
+def model_inputs(n_boxes: int, seed: int, dtype, device):
+    from fasteq_b200.graph import config1_batch
+    b = config1_batch(n_boxes, seed=seed)
+    t = lambda a, dt=None: torch.from_numpy(a).to(dt) if dt is not None else torch.from_numpy(a)
+    host = dict(pos=t(b.positions, dtype), species=t(b.species), src=t(b.edge_src), dst=t(b.edge_dst), shift=t(b.edge_shift, dtype),
+                graph=t(b.node_graph))
+    return b, {k: v.to(device) for k, v in host.items()}
+
+
+def model_bench(args, dev, rank, dist, n_boxes: int):
+    """Energy + forces of the synthetic MACE-style model of BASELINE config 1 (FP32): atom-steps/s."""
+    from fasteq_b200.nn.mace_style import MACEStyleModel
+    torch.manual_seed(0)
+    model = MACEStyleModel().to(dev)
+    for prm in model.parameters():          # inference + forces: no weight gradients
+        prm.requires_grad_(False)
+    b, d = model_inputs(n_boxes, rank, torch.float32, dev)
+    run = lambda: model(d["pos"], d["species"], d["src"], d["dst"], d["shift"], d["graph"], b.n_graphs)
+    for _ in range(3):
+        out = run()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    k = max(3, min(args.steps, 10))
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(k):
+        out = run()
+    ev1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([ev0.elapsed_time(ev1), float(b.n_nodes)], dtype=torch.float64, device=dev)
+    ms, atoms = float(t[0]), float(t[1])
+    if dist is not None:
+        tm = t.clone(); dist.all_reduce(tm, op=dist.ReduceOp.MAX); ms = float(tm[0])
+        ts = t.clone(); dist.all_reduce(ts, op=dist.ReduceOp.SUM); atoms = float(ts[1])
+    return {"metric": "MACE atom-steps/s (energy + forces)", "value": atoms * k / (ms * 1e-3), "unit": "atom-steps/s",
+            "ms_per_step": ms / k, "steps": k, "atoms": int(atoms), "edges_per_gpu": b.n_edges,
+            "config": "config 1: 2 layers, 128x0e+128x1o, SH l<=3, correlation 3, 8 Bessel x p=5 envelope, 64-64-64 SiLU radial MLP, FP32",
+            "energy_finite": bool(torch.isfinite(out["energy"]).all()), "forces_finite": bool(torch.isfinite(out["forces"]).all())}
+
+
 def reference_arm(args):
     """The reference's CPU path (e3nn algorithm, restated in oracle/) on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -191,6 +232,7 @@ def main():
     ap.add_argument("--boxes", type=int, default=None, help="boxes per GPU (default: the workload's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-model", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -302,6 +344,12 @@ def main():
                "d2h_bytes_per_step": 8, "steps": ke,
                "note": "pinned host w/x/y/grad_out/indices copied in each step (PCIe-bound: per-edge weights dominate)"}
 
+    model = None
+    if not args.no_model:
+        del devt, w, x, y            # the operator benchmark's 10+ GB of weights are not needed any more
+        torch.cuda.empty_cache()
+        model = model_bench(args, dev, rank, dist, args.boxes or WORKLOADS[args.workload][3])
+
     status = {name: m.device_status() for name, m in (("fwd", u1d.get_module(call.spec, "fwd")),
                                                       ("bwd", u1d.get_module(call.spec, "bwd", (True, True, True))))}
 
@@ -320,7 +368,7 @@ def main():
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32" if dtype == torch.float32 else "f64", "data": "synthetic",
             "config": dict(config_dict(args.workload, inp, world), atoms_per_gpu=N, edges_per_gpu=E),
-            "roofline": roof, "roofline_fwd": roof_fwd, "roofline_fwd_bwd": roof_both, "cpu_baseline": cpu, "e2e": e2e,
+            "roofline": roof, "roofline_fwd": roof_fwd, "roofline_fwd_bwd": roof_both, "cpu_baseline": cpu, "e2e": e2e, "model": model,
             "gpu_launches": 2 * args.steps, "clocks": clocks.summary(), "device_status": status,
         }
         print(json.dumps(line), flush=True)

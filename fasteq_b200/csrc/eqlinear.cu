@@ -15,6 +15,7 @@
 #include <cuda_runtime.h>
 #include "fasteq_b200.h"
 #include "core_common.h"
+#include "gemm_tf32x3.h"
 
 using namespace fasteq;
 
@@ -222,12 +223,64 @@ int launch(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const vo
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }
 
+// Bt[q][n][k] = coeff[q] * op(W[q])[k][n]: the K-major, pre-scaled weight blocks the tensor-core GEMM multiplies with.
+// Forward: K = u, N = v (a transpose of W[q]); grad_x: K = v, N = u (W[q] as stored).
+__global__ void pack_weights_kernel(const float* __restrict__ W, float* __restrict__ Bt, const __grid_constant__ GroupTable tab,
+                                    int u, int v, bool dgrad) {
+  const int K = dgrad ? v : u, N = dgrad ? u : v;
+  const long long total = (long long)tab.n_paths * N * K;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int k = (int)(i % K), n = (int)((i / K) % N), q = (int)(i / ((long long)K * N));
+    const float* wq = W + (size_t)tab.path_w[q] * u * v;
+    Bt[i] = tab.path_coeff_f[q] * (dgrad ? wq[(size_t)n * v + k] : wq[(size_t)k * v + n]);
+  }
+}
+
+int launch_tensorcore(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const void* a, void* c, cudaStream_t s,
+                      bool* used) {
+  *used = false;
+  GroupTable tab; bool covers = true;
+  int rc = build_table(p, dgrad, &tab, &covers);
+  if (rc != FASTEQ_OK) return rc;
+  const int K = dgrad ? p->v : p->u, N = dgrad ? p->u : p->v;
+  const int a_rows = dgrad ? p->out_rows : p->in_rows, c_rows = dgrad ? p->in_rows : p->out_rows;
+  if (p->batch == 0 || !w || !a || !c) return FASTEQ_OK;   // the FMA path reports the error / no-op
+  if (!tc::supported(p->batch, a_rows, K, p->num_paths, N, c_rows, a, w, c)) return FASTEQ_OK;
+  tc::TcTable t{};
+  t.n_groups = tab.n_groups; t.n_items = 0;
+  for (int g = 0; g < tab.n_groups; ++g) {
+    t.group_c_row[g] = tab.group_c_row[g]; t.group_first[g] = tab.group_first[g];
+    t.item_first[g] = t.n_items; t.n_items += tab.group_rows[g];
+  }
+  t.group_first[tab.n_groups] = tab.group_first[tab.n_groups];
+  t.item_first[tab.n_groups] = t.n_items;
+  for (int q = 0; q < tab.n_paths; ++q) { t.path_a_row[q] = tab.path_a_row[q]; t.path_w[q] = q; }   // packed in table order
+  float* bt = nullptr;
+  cudaError_t e = cudaMallocAsync((void**)&bt, (size_t)p->num_paths * N * K * sizeof(float), s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  const long long total = (long long)p->num_paths * N * K;
+  pack_weights_kernel<<<(unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096), 256, 0, s>>>((const float*)w, bt, tab, p->u, p->v, dgrad);
+  if (!covers) {
+    const long long tot = p->batch * c_rows * N;
+    zero_rows_kernel<float><<<(unsigned)((tot + 255) / 256), 256, 0, s>>>((float*)c, p->batch, c_rows, N, tab);
+  }
+  rc = tc::launch(t, (const float*)a, p->batch, a_rows, K, bt, p->num_paths, N, (float*)c, c_rows, s);
+  cudaFreeAsync(bt, s);
+  if (rc == FASTEQ_OK) *used = true;
+  return rc;
+}
+
 int dispatch(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const void* a, void* c, fasteq_stream_t stream) {
   if (!p) return FASTEQ_INVALID;
   switch (p->precision) {
     case FASTEQ_EQLIN_FP64: return launch<double>(p, dgrad, w, a, c, (cudaStream_t)stream);
-    case FASTEQ_EQLIN_FP32:
-    case FASTEQ_EQLIN_TF32X3: return launch<float>(p, dgrad, w, a, c, (cudaStream_t)stream);  // FP32 FMA satisfies the 3xTF32 bound
+    case FASTEQ_EQLIN_TF32X3: {
+      bool used = false;
+      int rc = launch_tensorcore(p, dgrad, w, a, c, (cudaStream_t)stream, &used);
+      if (rc != FASTEQ_OK || used) return rc;
+      return launch<float>(p, dgrad, w, a, c, (cudaStream_t)stream);   // shapes the tensor-core kernel does not take
+    }
+    case FASTEQ_EQLIN_FP32: return launch<float>(p, dgrad, w, a, c, (cudaStream_t)stream);
     default: return FASTEQ_INVALID;
   }
 }

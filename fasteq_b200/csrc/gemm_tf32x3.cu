@@ -1,0 +1,329 @@
+// 3xTF32 grouped GEMM on the sm_100a tensor cores (tcgen05 + TMEM + TMA), used for the dense
+// contractions of the path: SO3Linear forward / grad_x and the radial MLP layers.
+//
+//   C[b, c_row(item), n] = sum_{segments s of item} sum_k A[b, a_row(s), k] * Bt[w(s), n, k]
+//
+// A is a [M, rows_a, K] FP32 tensor (K contiguous), Bt a [P, N, K] FP32 tensor (K contiguous), C a
+// [M, rows_c, N] FP32 tensor.  A plain GEMM is the case rows_a = rows_c = P = 1.
+//
+// Precision: each FP32 operand v is split into hi = v with the 13 low mantissa bits cleared (exact in
+// TF32) and lo = v - hi (exact in FP32); the kernel accumulates hi*hi + hi*lo + lo*hi in FP32, which
+// keeps the relative error near 2^-21 (the reference's tf32x3 scheme,
+// fasteq/cuda/src/eqlinear/backends/tf32/shape_plan.cu:109-113: three MMAs, no lo*lo term).
+//
+// Structure of one CTA (one 128 x BN output tile of one item):
+//   warp 0       : TMA producer -- 3-D tiled loads (SWIZZLE_128B) of the raw A and Bt k-blocks
+//   warp 1       : allocates TMEM, issues tcgen05.mma (kind::tf32, M = 128, N = BN, K = 8) from one lane,
+//                  releases ring stages and signals the epilogue with tcgen05.commit
+//   warps 2..5   : split each raw k-block into hi / lo tiles in place (the swizzle is position
+//                  preserving, so no layout knowledge is needed), then read the accumulator with
+//                  tcgen05.ld and store the tile
+// Every mbarrier wait is bounded (about two seconds), after which a status word is set and the
+// waiter falls through; TMEM is always released before the CTA ends.  No multicast, no clusters.
+#include <cstdio>
+#include <cstdint>
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_runtime.h>
+#include "fasteq_b200.h"
+#include "core_common.h"
+#include "fasteq_device.cuh"
+#include "gemm_tf32x3.h"
+
+namespace fasteq {
+namespace tc {
+
+constexpr int BM = 128, BK = 32, STAGES = 3;
+constexpr int NT = 192;   // 6 warps
+
+template <int BN> struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 4;          // 16 KB
+  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* barriers */ + 1024 /* alignment slack */;
+};
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  // K-major, SWIZZLE_128B: rows of 128 bytes, 8-row groups 1024 bytes apart
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+  d |= (uint64_t)1 << 16;                    // leading byte offset (unused for swizzled K-major), 16 B
+  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
+  d |= (uint64_t)1 << 46;                    // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NT, 1)
+gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ TcTable tab, float* __restrict__ C, long long M, int c_rows_per_b, int N, int K,
+                   int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using C_ = Cfg<BN>;
+  unsigned char* stage_base = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C_::STAGE_BYTES);
+  uint64_t* full_raw = bars;                 // [STAGES] TMA landed
+  uint64_t* full_split = bars + STAGES;      // [STAGES] hi / lo tiles ready
+  uint64_t* empty = bars + 2 * STAGES;       // [STAGES] MMAs have consumed the stage
+  uint64_t* acc_full = bars + 3 * STAGES;    // accumulator complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // which (group, t) this CTA works on
+  int g = 0;
+  while (g + 1 < tab.n_groups && (int)blockIdx.z >= tab.item_first[g + 1]) ++g;
+  const int t = (int)blockIdx.z - tab.item_first[g];
+  const int seg0 = tab.group_first[g], nseg = tab.group_first[g + 1] - seg0;
+  const int kb_per_seg = (K + BK - 1) / BK;
+  const int n_kb = nseg * kb_per_seg;
+  const long long m0 = (long long)blockIdx.x * BM;
+  const int n0 = blockIdx.y * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_raw[s], 1); mbar_init(&full_split[s], 4); mbar_init(&empty[s], 1); }
+    mbar_init(acc_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int kb = 0; kb < n_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1u;
+        mbar_wait(&empty[s], ph ^ 1u, status);
+        unsigned char* st = stage_base + (size_t)s * C_::STAGE_BYTES;
+        const int seg = seg0 + kb / kb_per_seg;
+        const int k0 = (kb % kb_per_seg) * BK;
+        mbar_arrive_expect_tx(&full_raw[s], (uint32_t)(C_::A_BYTES + C_::B_BYTES));
+        tma_load_3d(st, &tmA, k0, tab.path_a_row[seg] + t, (int)m0, &full_raw[s]);
+        tma_load_3d(st + 2 * C_::A_BYTES, &tmB, k0, n0, tab.path_w[seg], &full_raw[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      for (int kb = 0; kb < n_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1u;
+        mbar_wait(&full_split[s], ph, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_hi = smem_u32(stage_base + (size_t)s * C_::STAGE_BYTES);
+        const uint32_t a_lo = a_hi + C_::A_BYTES;
+        const uint32_t b_hi = a_hi + 2 * C_::A_BYTES;
+        const uint32_t b_lo = b_hi + C_::B_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BK / 8; ++kk) {
+          const uint32_t off = kk * 32;   // 8 TF32 values = 32 bytes along K inside the 128-byte swizzle row
+          mma_tf32(tmem_base, make_desc(a_lo + off), make_desc(b_hi + off), idesc, (kb | kk) ? 1u : 0u);
+          mma_tf32(tmem_base, make_desc(a_hi + off), make_desc(b_lo + off), idesc, 1u);
+          mma_tf32(tmem_base, make_desc(a_hi + off), make_desc(b_hi + off), idesc, 1u);
+        }
+        mma_commit(&empty[s]);            // the stage may be refilled once these MMAs have read it
+      }
+      mma_commit(acc_full);
+    }
+  } else {
+    // ------------------------------------------------------------------ split, then epilogue
+    const int tid = threadIdx.x - 64;     // 0..127
+    for (int kb = 0; kb < n_kb; ++kb) {
+      const int s = kb % STAGES;
+      const uint32_t ph = (kb / STAGES) & 1u;
+      mbar_wait(&full_raw[s], ph, status);
+      unsigned char* st = stage_base + (size_t)s * C_::STAGE_BYTES;
+      float4* a_hi = reinterpret_cast<float4*>(st);
+      float4* a_lo = reinterpret_cast<float4*>(st + C_::A_BYTES);
+      float4* b_hi = reinterpret_cast<float4*>(st + 2 * C_::A_BYTES);
+      float4* b_lo = reinterpret_cast<float4*>(st + 2 * C_::A_BYTES + C_::B_BYTES);
+      auto split = [](float4 v, float4& hi, float4& lo) {
+        hi.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); lo.x = v.x - hi.x;
+        hi.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); lo.y = v.y - hi.y;
+        hi.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); lo.z = v.z - hi.z;
+        hi.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); lo.w = v.w - hi.w;
+      };
+#pragma unroll
+      for (int i = 0; i < C_::A_BYTES / 16 / 128; ++i) {
+        float4 hi, lo; split(a_hi[tid + i * 128], hi, lo);
+        a_hi[tid + i * 128] = hi; a_lo[tid + i * 128] = lo;
+      }
+#pragma unroll
+      for (int i = 0; i < C_::B_BYTES / 16 / 128; ++i) {
+        float4 hi, lo; split(b_hi[tid + i * 128], hi, lo);
+        b_hi[tid + i * 128] = hi; b_lo[tid + i * 128] = lo;
+      }
+      fence_async_smem();                 // generic-proxy writes -> visible to the tensor core's async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full_split[s]);
+    }
+    // epilogue: TMEM lane = tile row; warp w may touch lanes 32 * (w % 4) .. + 31
+    mbar_wait(acc_full, 0u, status);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int quarter = warp & 3;
+    const long long row = m0 + quarter * 32 + lane;
+    float* crow = C + ((size_t)(row < M ? row : 0) * c_rows_per_b + tab.group_c_row[g] + t) * (size_t)N;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32);
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+          : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+            "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+            "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+            "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          : "r"(taddr)
+          : "memory");
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (row < M) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const int n = n0 + c * 32 + j;
+          if (n + 3 < N) {
+            *reinterpret_cast<float4*>(crow + n) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                               __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+          } else {
+            for (int e = 0; e < 4; ++e) if (n + e < N) crow[n + e] = __uint_as_float(r[j + e]);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+  }
+}
+
+// --------------------------------------------------------------------------------- host side
+__device__ int g_tc_status;
+
+static PFN_cuTensorMapEncodeTiled get_encode() {
+  static PFN_cuTensorMapEncodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(p);
+  }
+  return fn;
+}
+
+// 3-D FP32 tensor [d2][d1][d0] (d0 contiguous), box [b2][b1][b0], 128-byte swizzle, zero fill outside
+static int make_map(CUtensorMap* m, const float* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_elems,
+                    uint64_t stride2_elems, uint32_t b0, uint32_t b1, uint32_t b2) {
+  PFN_cuTensorMapEncodeTiled enc = get_encode();
+  if (!enc) return FASTEQ_INTERNAL;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_elems * 4, stride2_elems * 4};
+  cuuint32_t box[3] = {b0, b1, b2};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return FASTEQ_CUDA_ERROR;
+  }
+  return FASTEQ_OK;
+}
+
+bool supported(long long M, int a_rows, int K, int P, int N, int c_rows, const void* A, const void* Bt, const void* C) {
+  if (M < 1 || K < 4 || N < 4 || (K % 4) || (N % 4)) return false;                 // 16-byte global strides
+  if (M > 0x7fffffffLL) return false;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bt) | reinterpret_cast<uintptr_t>(C)) & 15u) return false;
+  if ((long long)a_rows * K > (1LL << 36) || (long long)N * K > (1LL << 36)) return false;
+  return true;
+}
+
+template <int BN>
+static int launch_bn(const TcTable& tab, const CUtensorMap& ma, const CUtensorMap& mb, float* C, long long M, int c_rows, int N,
+                     int K, cudaStream_t s) {
+  int* st = nullptr;
+  cudaError_t e = cudaGetSymbolAddress((void**)&st, g_tc_status);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
+  if (e != cudaSuccess) return cuda_fail(e);
+  dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)((N + BN - 1) / BN), (unsigned)tab.n_items);
+  gemm_tf32x3_kernel<BN><<<grid, NT, Cfg<BN>::SMEM_BYTES, s>>>(ma, mb, tab, C, M, c_rows, N, K, st);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
+}
+
+int launch(const TcTable& tab, const float* A, long long M, int a_rows, int K, const float* Bt, int P, int N, float* C,
+           int c_rows, cudaStream_t s) {
+  if (tab.n_items < 1 || tab.n_items > 65535) return FASTEQ_UNSUPPORTED;
+  const int BN = N <= 64 ? 64 : 128;
+  alignas(64) CUtensorMap ma, mb;
+  int rc = make_map(&ma, A, (uint64_t)K, (uint64_t)a_rows, (uint64_t)M, (uint64_t)K, (uint64_t)a_rows * K, BK, 1, BM);
+  if (rc != FASTEQ_OK) return rc;
+  rc = make_map(&mb, Bt, (uint64_t)K, (uint64_t)N, (uint64_t)P, (uint64_t)K, (uint64_t)N * K, BK, (uint32_t)BN, 1);
+  if (rc != FASTEQ_OK) return rc;
+  return BN == 64 ? launch_bn<64>(tab, ma, mb, C, M, c_rows, N, K, s) : launch_bn<128>(tab, ma, mb, C, M, c_rows, N, K, s);
+}
+
+int device_status(int* code) {
+  int v = 0, zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+  if (e != cudaSuccess) return cuda_fail(e);
+  *code = v;
+  return FASTEQ_OK;
+}
+
+}  // namespace tc
+}  // namespace fasteq
+
+// C[M, N] = A[M, K] @ Bt[N, K]^T, FP32 data, 3xTF32 tensor-core arithmetic (a layer of the radial MLP:
+// Bt is torch's [out_features, in_features] weight).  K and N multiples of 4, 16-byte aligned pointers.
+extern "C" int fasteq_gemm_tf32x3(const void* A, const void* Bt, void* C, int64_t M, int32_t N, int32_t K,
+                                  fasteq_stream_t stream) {
+  using namespace fasteq;
+  if (M < 0 || N < 1 || K < 1) return FASTEQ_INVALID;
+  if (M == 0) return FASTEQ_OK;
+  if (!A || !Bt || !C) return FASTEQ_INVALID;
+  if (!tc::supported(M, 1, K, 1, N, 1, A, Bt, C)) return FASTEQ_UNSUPPORTED;
+  tc::TcTable tab{};
+  tab.n_groups = 1; tab.n_items = 1; tab.group_c_row[0] = 0; tab.group_first[0] = 0; tab.group_first[1] = 1;
+  tab.item_first[0] = 0; tab.item_first[1] = 1; tab.path_a_row[0] = 0; tab.path_w[0] = 0;
+  return tc::launch(tab, (const float*)A, M, 1, K, (const float*)Bt, 1, N, (float*)C, 1, (cudaStream_t)stream);
+}
+
+extern "C" int fasteq_tensorcore_device_status(int32_t* code) {
+  if (!code) return FASTEQ_INVALID;
+  return fasteq::tc::device_status(code);
+}

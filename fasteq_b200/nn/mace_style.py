@@ -19,6 +19,7 @@ import torch
 
 from ..descriptors import full_channelwise_instructions
 from ..irreps import Irreps
+from ..ops.dense import dense
 from ..ops.spherical_harmonics import SphericalHarmonics
 from .modules import ChannelwiseTensorProduct, SO3Linear, SymmetricContraction
 
@@ -44,7 +45,7 @@ class RadialMLP(torch.nn.Module):
 
     def forward(self, x):
         for i, lin in enumerate(self.layers):
-            x = lin(x)
+            x = dense(x, lin.weight)
             if i + 1 < len(self.layers):
                 x = torch.nn.functional.silu(x)
         return x

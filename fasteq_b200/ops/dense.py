@@ -1,0 +1,77 @@
+"""Dense layer ``y = x @ weight.T`` on the tensor cores with 3xTF32 arithmetic (FP32 data, relative
+error near 1e-6), for the radial MLP that produces the tensor-product weights.  FP64 tensors and
+shapes the kernel does not take go through ``torch.matmul`` (cuBLAS FP64 / FP32 without TF32).
+The gradient with respect to ``x`` uses the same kernel; the weight gradient, needed only for
+training, is a plain ``torch.matmul`` reduction over the edges.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _cabi
+
+_ready = False
+
+
+def _lib():
+    global _ready
+    lib = _cabi.core()
+    if not _ready:
+        lib.fasteq_gemm_tf32x3.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]
+        lib.fasteq_tensorcore_device_status.argtypes = [C.POINTER(C.c_int32)]
+        _ready = True
+    return lib
+
+
+def tensorcore_device_status() -> int:
+    v = C.c_int32(0)
+    lib = _lib()
+    _cabi.check(lib.fasteq_tensorcore_device_status(C.byref(v)), lib, "fasteq_tensorcore_device_status")
+    return int(v.value)
+
+
+def _usable(x: torch.Tensor, n: int, k: int) -> bool:
+    return x.is_cuda and x.dtype == torch.float32 and k % 4 == 0 and n % 4 == 0 and k >= 4 and n >= 4 and x.shape[0] > 0
+
+
+def _gemm(a: torch.Tensor, bt: torch.Tensor) -> torch.Tensor:
+    """a [M, K] @ bt[N, K]^T -> [M, N]."""
+    a, bt = a.contiguous(), bt.contiguous()
+    M, K = a.shape
+    N = bt.shape[0]
+    out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    lib = _lib()
+    with torch.cuda.device(a.device):
+        rc = lib.fasteq_gemm_tf32x3(a.data_ptr(), bt.data_ptr(), out.data_ptr(), M, N, K, torch.cuda.current_stream(a.device).cuda_stream)
+    if rc == 1:   # FASTEQ_UNSUPPORTED: alignment
+        return a @ bt.t()
+    _cabi.check(rc, lib, "fasteq_gemm_tf32x3")
+    return out
+
+
+class _Dense(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight):
+        ctx.save_for_backward(x, weight)
+        return _gemm(x, weight)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, weight = ctx.saved_tensors
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = _gemm(grad_out, weight.t().contiguous())       # [M, N] @ [N, K] with Bt = weight^T [K, N]
+        if ctx.needs_input_grad[1]:
+            gw = grad_out.t() @ x
+        return gx, gw
+
+
+def dense(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``x [..., K] @ weight[N, K]^T``."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if _usable(x2, weight.shape[0], weight.shape[1]) and weight.dtype == torch.float32:
+        return _Dense.apply(x2, weight).reshape(*lead, weight.shape[0])
+    return x @ weight.t()

@@ -203,6 +203,14 @@ int fasteq_eqlinear_forward(const fasteq_eqlinear_problem* p /* host */, const v
 int fasteq_eqlinear_dgrad(const fasteq_eqlinear_problem* p /* host */, const void* w, const void* grad_out,
                           void* grad_x, fasteq_stream_t stream);
 
+/* Dense layer of the radial MLP: C[M, N] = A[M, K] @ Bt[N, K]^T, FP32 data, 3xTF32 arithmetic on the
+ * tensor cores (Bt is a torch.nn.Linear weight, [out_features, in_features]).  K and N multiples of 4,
+ * pointers 16-byte aligned, else FASTEQ_UNSUPPORTED.  The reference leaves this MLP to the model
+ * package (torch); it has no entry point of its own for it. */
+int fasteq_gemm_tf32x3(const void* A, const void* Bt, void* C, int64_t M, int32_t N, int32_t K, fasteq_stream_t stream);
+/* Reads and clears the status word of the tensor-core kernels (synchronises). */
+int fasteq_tensorcore_device_status(int32_t* code /* host */);
+
 #ifdef __cplusplus
 }
 #endif
