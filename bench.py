@@ -157,6 +157,44 @@ def model_inputs(n_boxes: int, seed: int, dtype, device):
     return b, {k: v.to(device) for k, v in host.items()}
 
 
+def halo_model_bench(args, dev, rank, world, dist):
+    """BASELINE config 3 geometry (20,000 atoms, cutoff 4 A, one periodic cube) through the MACE-style
+    model, partitioned by receiver range with a halo exchange per layer: strong scaling."""
+    from fasteq_b200.graph import large_box
+    from fasteq_b200.nn.mace_style import MACEStyleModel
+    from fasteq_b200.parallel import HaloExchange, partition_by_receiver_range
+    torch.manual_seed(0)
+    model = MACEStyleModel(num_species=2, channels=64, r_max=4.0, avg_num_neighbors=27.0).to(dev)
+    for prm in model.parameters():
+        prm.requires_grad_(False)
+    b = large_box(seed=0)
+    lg = partition_by_receiver_range(b.n_nodes, b.edge_src, b.edge_dst, world)[rank]
+    halo = HaloExchange(lg, dev) if world > 1 else None
+    t = lambda a, dt=None: torch.from_numpy(a).to(dev) if dt is None else torch.from_numpy(a).to(dt).to(dev)
+    pos, spec = t(b.positions[lg.start:lg.stop], torch.float32), t(b.species[lg.start:lg.stop])
+    src, dst, shift = t(lg.edge_src), t(lg.edge_dst), t(b.edge_shift[lg.edge_ids], torch.float32)
+    run = lambda: model(pos, spec, src, dst, shift, halo=halo)
+    for _ in range(3):
+        out = run()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    k = max(3, min(args.steps, 10))
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(k):
+        out = run()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return {"metric": "MACE-style atom-steps/s, one 20,000-atom graph, receiver-range partition + halo", "scaling": "strong",
+            "value": b.n_nodes * k / (float(ms[0]) * 1e-3), "unit": "atom-steps/s", "ms_per_step": float(ms[0]) / k,
+            "atoms": b.n_nodes, "edges": b.n_edges, "owned": lg.n_owned, "ghosts": int(len(lg.ghost_global)),
+            "config": "2 layers, 64x0e+64x1o, SH l<=3, correlation 3, cutoff 4 A, FP32"}
+
+
 def model_bench(args, dev, rank, dist, n_boxes: int):
     """Energy + forces of the synthetic MACE-style model of BASELINE config 1 (FP32): atom-steps/s."""
     from fasteq_b200.nn.mace_style import MACEStyleModel
@@ -233,6 +271,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-model", action="store_true")
+    ap.add_argument("--no-halo", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -349,6 +388,8 @@ def main():
         del devt, w, x, y            # the operator benchmark's 10+ GB of weights are not needed any more
         torch.cuda.empty_cache()
         model = model_bench(args, dev, rank, dist, args.boxes or WORKLOADS[args.workload][3])
+        if not args.no_halo:
+            model["single_graph"] = halo_model_bench(args, dev, rank, world, dist)
 
     status = {name: m.device_status() for name, m in (("fwd", u1d.get_module(call.spec, "fwd")),
                                                       ("bwd", u1d.get_module(call.spec, "bwd", (True, True, True))))}

@@ -56,6 +56,64 @@ def periodic_radius_graph(pos: np.ndarray, side: float, cutoff: float):
     return src[order], dst[order], vec[order], sh[order]
 
 
+def periodic_radius_graph_cells(pos: np.ndarray, side: float, cutoff: float):
+    """Same result as ``periodic_radius_graph`` for ``cutoff <= side / 3``, by a cell list: O(N) memory.
+
+    Atoms are binned into cubic cells at least ``cutoff`` wide; every cell is compared with its 27
+    neighbours (periodic wrap carries the image shift)."""
+    n = pos.shape[0]
+    ncell = int(np.floor(side / cutoff))
+    if ncell < 3:
+        return periodic_radius_graph(pos, side, cutoff)
+    w = side / ncell
+    cell = np.minimum((pos / w).astype(np.int64), ncell - 1)
+    cid = (cell[:, 0] * ncell + cell[:, 1]) * ncell + cell[:, 2]
+    order = np.argsort(cid, kind="stable")
+    cstart = np.searchsorted(cid[order], np.arange(ncell ** 3 + 1))
+    maxocc = int(np.diff(cstart).max())
+    # padded [cells, maxocc] table of atom ids (-1 = empty)
+    table = np.full((ncell ** 3, maxocc), -1, dtype=np.int64)
+    occ = np.arange(n) - cstart[cid[order]]
+    table[cid[order], occ] = order
+    c2 = cutoff * cutoff
+    src_l, dst_l, vec_l, sh_l = [], [], [], []
+    cx, cy, cz = np.meshgrid(np.arange(ncell), np.arange(ncell), np.arange(ncell), indexing="ij")
+    base = np.stack([cx, cy, cz], -1).reshape(-1, 3)
+    for off in np.stack(np.meshgrid([-1, 0, 1], [-1, 0, 1], [-1, 0, 1], indexing="ij"), -1).reshape(-1, 3):
+        nb = base + off
+        wrap = np.floor_divide(nb, ncell)
+        nbw = nb - wrap * ncell
+        nid = (nbw[:, 0] * ncell + nbw[:, 1]) * ncell + nbw[:, 2]
+        shift = wrap.astype(np.float64) * side                      # image offset of the sender cell
+        recv = table                                                # [C, m] receivers in the cell
+        send = table[nid]                                           # [C, m] senders in the neighbour cell
+        valid = (recv[:, :, None] >= 0) & (send[:, None, :] >= 0)
+        pr = pos[np.maximum(recv, 0)]                               # [C, m, 3]
+        ps = pos[np.maximum(send, 0)] + shift[:, None, :]
+        d = ps[:, None, :, :] - pr[:, :, None, :]                   # [C, m_recv, m_send, 3]
+        r2 = (d * d).sum(-1)
+        mask = valid & (r2 < c2) & ~((recv[:, :, None] == send[:, None, :]) & (np.abs(shift).sum(-1) == 0)[:, None, None])
+        ci, ri, si = np.nonzero(mask)
+        src_l.append(send[ci, si]); dst_l.append(recv[ci, ri]); vec_l.append(d[ci, ri, si]); sh_l.append(shift[ci])
+    src = np.concatenate(src_l); dst = np.concatenate(dst_l); vec = np.concatenate(vec_l); sh = np.concatenate(sh_l)
+    order = np.lexsort((sh[:, 2], sh[:, 1], sh[:, 0], src, dst))
+    return src[order], dst[order], vec[order], sh[order]
+
+
+def large_box(n_atoms: int = 20000, side: float = 58.5, cutoff: float = 4.0, n_species: int = 2, seed: int = 0) -> Batch:
+    """BASELINE config 3 data: one periodic cube, atoms sorted along a space-filling order of the
+    cells so that contiguous node ranges are spatially compact (small halos)."""
+    rng = np.random.default_rng(seed)
+    pos = rng.uniform(0.0, side, size=(n_atoms, 3))
+    ncell = max(1, int(np.floor(side / cutoff)))
+    cell = np.minimum((pos / (side / ncell)).astype(np.int64), ncell - 1)
+    order = np.lexsort((cell[:, 2], cell[:, 1], cell[:, 0]))         # slabs along x, then y, then z
+    pos = pos[order]
+    spec = rng.integers(0, n_species, size=n_atoms)
+    s, d, v, sh = periodic_radius_graph_cells(pos, side, cutoff)
+    return Batch(pos, spec, s, d, v, sh, np.zeros(n_atoms, dtype=np.int64), 1)
+
+
 def make_boxes(n_boxes: int, atoms, side, cutoff: float, n_species: int, seed: int = 0) -> Batch:
     """``atoms`` / ``side`` may be scalars or per-box sequences."""
     rng = np.random.default_rng(seed)

@@ -67,10 +67,13 @@ class InteractionLayer(torch.nn.Module):
         self.linear_out = SO3Linear(hidden, hidden)
         self.inv_neighbors = 1.0 / avg_num_neighbors
 
-    def forward(self, h, species, edge_sh, edge_radial, edge_dst, edge_src):
+    def forward(self, h, species, edge_sh, edge_radial, edge_dst, edge_src, halo=None):
         up = self.linear_up(h)
+        n_owned = up.shape[0]
+        if halo is not None:
+            up = halo(up)                    # owned rows, then ghost rows of the senders other ranks own
         w = self.radial(edge_radial)
-        msg = self.conv_tp(up, edge_sh, w, edge_dst, edge_src)
+        msg = self.conv_tp(up, edge_sh, w, edge_dst, edge_src)[:n_owned]
         mid = self.linear_mid(msg) * self.inv_neighbors
         prod = self.product(mid, species)
         return self.linear_out(prod)
@@ -101,19 +104,23 @@ class MACEStyleModel(torch.nn.Module):
         radial = bessel_basis(r, self.r_max, self.num_basis) * polynomial_cutoff(r, self.r_max, self.envelope_p).unsqueeze(-1)
         return self.sh(vec), radial
 
-    def node_energies(self, pos, species, edge_src, edge_dst, edge_shift):
-        edge_sh, edge_radial = self.edge_features(pos, edge_src, edge_dst, edge_shift)
+    def node_energies(self, pos, species, edge_src, edge_dst, edge_shift, halo=None):
+        """``halo`` (a ``parallel.HaloExchange``) extends per-node tensors with ghost rows; ``pos`` and
+        ``species`` then hold the owned nodes only and the edge indices are local ids."""
+        pos_ext = pos if halo is None else halo(pos)
+        edge_sh, edge_radial = self.edge_features(pos_ext, edge_src, edge_dst, edge_shift)
         h = self.embedding[species]
         e = pos.new_zeros(pos.shape[0])
         for layer, ro in zip(self.layers, self.readouts):
-            h = layer(h, species, edge_sh, edge_radial, edge_dst, edge_src)
+            h = layer(h, species, edge_sh, edge_radial, edge_dst, edge_src, halo)
             e = e + h[:, : self.channels] @ ro          # scalars are the first segment of the ir_mul row
         return e
 
-    def forward(self, pos, species, edge_src, edge_dst, edge_shift, node_graph=None, n_graphs: int = 1, forces: bool = True):
+    def forward(self, pos, species, edge_src, edge_dst, edge_shift, node_graph=None, n_graphs: int = 1, forces: bool = True,
+                halo=None):
         if forces:
             pos = pos.detach().requires_grad_(True)
-        e_node = self.node_energies(pos, species, edge_src, edge_dst, edge_shift)
+        e_node = self.node_energies(pos, species, edge_src, edge_dst, edge_shift, halo)
         if node_graph is None:
             energy = e_node.sum().reshape(1)
         else:

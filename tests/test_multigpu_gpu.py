@@ -1,0 +1,67 @@
+"""Two-GPU run of the MACE-style model on one graph partitioned by receiver range with a halo
+exchange (NCCL): energies and forces must equal the single-GPU evaluation.  Skipped with < 2 GPUs."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from fasteq_b200.graph import make_boxes
+    from fasteq_b200.nn.mace_style import MACEStyleModel
+    from fasteq_b200.parallel import HaloExchange, partition_by_receiver_range
+    torch.manual_seed(0)
+    model = MACEStyleModel(num_species=2, channels=32, r_max=3.5, avg_num_neighbors=12.0).double().to(dev)
+    b = make_boxes(1, 80, 9.0, 3.5, 2, seed=11)
+    lg = partition_by_receiver_range(b.n_nodes, b.edge_src, b.edge_dst, world)[rank]
+    halo = HaloExchange(lg, dev)
+    t = lambda a: torch.from_numpy(a).to(dev)
+    out = model(t(b.positions[lg.start:lg.stop]), t(b.species[lg.start:lg.stop]), t(lg.edge_src), t(lg.edge_dst),
+                t(b.edge_shift[lg.edge_ids]), halo=halo)
+    e_tot = out["energy"].clone()
+    dist.all_reduce(e_tot)
+    res = {"rank": rank, "lo": lg.start, "hi": lg.stop, "forces": out["forces"].cpu().numpy(), "energy": float(e_tot)}
+    if rank == 0:
+        full = model(t(b.positions), t(b.species), t(b.edge_src), t(b.edge_dst), t(b.edge_shift))
+        res["ref_energy"] = float(full["energy"]); res["ref_forces"] = full["forces"].cpu().numpy()
+    q.put(res)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_halo_matches_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=600) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    ref = next(g for g in got if "ref_forces" in g)
+    f = np.zeros_like(ref["ref_forces"])
+    for g in got:
+        f[g["lo"]:g["hi"]] = g["forces"]
+        assert abs(g["energy"] - ref["ref_energy"]) <= 1e-10 * abs(ref["ref_energy"])
+    assert np.abs(f - ref["ref_forces"]).max() <= 1e-9 * np.abs(ref["ref_forces"]).max()
