@@ -24,15 +24,26 @@ def test_every_declared_symbol_is_exported():
     spec = cwtp_spec("32x0e+32x1o", 2, 2, "f32")
     fwd = ctypes.CDLL(get_module(spec, "fwd").path)
     bwd = ctypes.CDLL(get_module(spec, "bwd", (True, True, True)).path)
+    from fasteq_b200.ops import spherical_harmonics as shmod, stc_uniform1d_jit as stcmod
+    from fasteq_b200.prebuild import stc_spec
+    import torch
+    sh = shmod._module((0, 1, 2), torch.float32, True, "component")
+    sspec = stc_spec("4x0e+4x1o", "4x0e", "f32")
+    stc_fwd = ctypes.CDLL(stcmod.get_module(sspec, "fwd").path)
+    stc_bwd = ctypes.CDLL(stcmod.get_module(sspec, "bwd", False).path)
     names = _declared_functions()
-    assert len(names) >= 10
+    assert len(names) >= 20
     for n in names:
+        if n.startswith("fasteq_sh_"):
+            assert hasattr(sh, n), n
+            continue
+        if n.startswith("fasteq_stc_"):
+            assert hasattr(stc_fwd, n) and hasattr(stc_bwd, n), n
+            continue
         if n.startswith("fasteq_u1d_"):
             assert hasattr(fwd, n) or hasattr(bwd, n), n
             if n != "fasteq_u1d_forward_noalloc":
                 assert hasattr(fwd, n) and hasattr(bwd, n), n
-        elif n.startswith("fasteq_stc_"):
-            continue  # generated STC modules are checked in their own test
         else:
             assert hasattr(core, n), n
     core.fasteq_status_string.restype = ctypes.c_char_p
