@@ -33,13 +33,14 @@
 namespace fasteq {
 namespace tc {
 
-constexpr int BM = 128, BK = 32, STAGES = 3;
+constexpr int BM = 128, BK = 32;
 constexpr int NT = 192;   // 6 warps
 
 template <int BN> struct Cfg {
   static constexpr int A_BYTES = BM * BK * 4;          // 16 KB
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  static constexpr int STAGES = (BN <= 64) ? 4 : 3;     // ring depth that fits the 227 KB of one CTA
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* barriers */ + 1024 /* alignment slack */;
 };
 
@@ -81,6 +82,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using C_ = Cfg<BN>;
+  constexpr int STAGES = C_::STAGES;
   unsigned char* stage_base = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C_::STAGE_BYTES);
   uint64_t* full_raw = bars;                 // [STAGES] TMA landed
@@ -228,6 +230,180 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// "A-stationary" variant for a shallow, wide layer (K <= 128, many N tiles: the last layer of the radial
+// MLP, 64 -> weight_numel).  One CTA owns a 128-row block of A, loads and splits it once, then walks
+// all N tiles: pre-split weight tiles (hi / lo arrays prepared once per call) stream through a ring,
+// two TMEM accumulators alternate so that the MMAs of tile n+1 overlap the stores of tile n.
+constexpr int AS_BN = 128, AS_RING = 4, AS_MAX_KB = 4;
+
+template <int KB>
+struct AsCfg {
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int B_BYTES = AS_BN * BK * 4;
+  static constexpr int RING = (KB <= 2) ? AS_RING : 2;
+  static constexpr int SMEM_BYTES = KB * 2 * A_BYTES + RING * 2 * B_BYTES + 1024 + 1024;
+};
+
+template <int KB>
+__global__ void __launch_bounds__(NT, 1)
+gemm_tf32x3_as_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBhi,
+                      const __grid_constant__ CUtensorMap tmBlo, float* __restrict__ C, long long M, int N, int K, int* status) {
+  using C_ = AsCfg<KB>;
+  constexpr int RING = C_::RING;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* a_base = smem;                                   // [KB][hi 16 KB | lo 16 KB]
+  unsigned char* b_base = smem + KB * 2 * C_::A_BYTES;            // [RING][hi 16 KB | lo 16 KB]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(b_base + RING * 2 * C_::B_BYTES);
+  uint64_t* a_full = bars;            // 1
+  uint64_t* a_split = bars + 1;       // 4 warps
+  uint64_t* b_full = bars + 2;        // [RING]
+  uint64_t* b_empty = b_full + RING;  // [RING]
+  uint64_t* acc_full = b_empty + RING;   // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long m0 = (long long)blockIdx.x * BM;
+  const int n_tiles = (N + AS_BN - 1) / AS_BN;
+  const int n_kb = (K + BK - 1) / BK;            // <= KB
+
+  if (threadIdx.x == 0) {
+    mbar_init(a_full, 1); mbar_init(a_split, 4);
+    for (int s = 0; s < RING; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(a_full, (uint32_t)(n_kb * C_::A_BYTES));
+      for (int kb = 0; kb < n_kb; ++kb) tma_load_3d(a_base + (size_t)kb * 2 * C_::A_BYTES, &tmA, kb * BK, 0, (int)m0, a_full);
+      int it = 0;
+      for (int nt = 0; nt < n_tiles; ++nt) {
+        for (int kb = 0; kb < n_kb; ++kb, ++it) {
+          const int s = it % RING;
+          mbar_wait(&b_empty[s], ((it / RING) & 1u) ^ 1u, status);
+          unsigned char* st = b_base + (size_t)s * 2 * C_::B_BYTES;
+          mbar_arrive_expect_tx(&b_full[s], (uint32_t)(2 * C_::B_BYTES));
+          tma_load_3d(st, &tmBhi, kb * BK, nt * AS_BN, 0, &b_full[s]);
+          tma_load_3d(st + C_::B_BYTES, &tmBlo, kb * BK, nt * AS_BN, 0, &b_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(AS_BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      mbar_wait(a_split, 0u, status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      int it = 0;
+      for (int nt = 0; nt < n_tiles; ++nt) {
+        const int buf = nt & 1;
+        mbar_wait(&acc_empty[buf], (((uint32_t)nt >> 1) & 1u) ^ 1u, status);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * AS_BN);
+        for (int kb = 0; kb < n_kb; ++kb, ++it) {
+          const int s = it % RING;
+          mbar_wait(&b_full[s], (it / RING) & 1u, status);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_hi = smem_u32(a_base + (size_t)kb * 2 * C_::A_BYTES), a_lo = a_hi + C_::A_BYTES;
+          const uint32_t b_hi = smem_u32(b_base + (size_t)s * 2 * C_::B_BYTES), b_lo = b_hi + C_::B_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 8; ++kk) {
+            const uint32_t off = kk * 32;
+            mma_tf32(tmem_d, make_desc(a_lo + off), make_desc(b_hi + off), idesc, (kb | kk) ? 1u : 0u);
+            mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_lo + off), idesc, 1u);
+            mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_hi + off), idesc, 1u);
+          }
+          mma_commit(&b_empty[s]);
+        }
+        mma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    const int tid = threadIdx.x - 64;
+    mbar_wait(a_full, 0u, status);
+    for (int kb = 0; kb < n_kb; ++kb) {
+      float4* hi = reinterpret_cast<float4*>(a_base + (size_t)kb * 2 * C_::A_BYTES);
+      float4* lo = reinterpret_cast<float4*>(a_base + (size_t)kb * 2 * C_::A_BYTES + C_::A_BYTES);
+#pragma unroll
+      for (int i = 0; i < C_::A_BYTES / 16 / 128; ++i) {
+        const float4 v = hi[tid + i * 128];
+        float4 h, l;
+        h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = v.x - h.x;
+        h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = v.y - h.y;
+        h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = v.z - h.z;
+        h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = v.w - h.w;
+        hi[tid + i * 128] = h; lo[tid + i * 128] = l;
+      }
+    }
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(a_split);
+    const int quarter = warp & 3;
+    const long long row = m0 + quarter * 32 + lane;
+    float* crow = C + (size_t)(row < M ? row : 0) * (size_t)N;
+    for (int nt = 0; nt < n_tiles; ++nt) {
+      const int buf = nt & 1;
+      mbar_wait(&acc_full[buf], ((uint32_t)nt >> 1) & 1u, status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int c = 0; c < AS_BN / 32; ++c) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * AS_BN + c * 32);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+              "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < M) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const int n = nt * AS_BN + c * 32 + j;
+            if (n + 3 < N) {
+              *reinterpret_cast<float4*>(crow + n) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                 __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else {
+              for (int e = 0; e < 4; ++e) if (n + e < N) crow[n + e] = __uint_as_float(r[j + e]);
+            }
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+  }
+}
+
+__global__ void split_weights_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float v = w[i];
+    const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+    hi[i] = h; lo[i] = v - h;
+  }
+}
+
 // --------------------------------------------------------------------------------- host side
 __device__ int g_tc_status;
 
@@ -295,6 +471,38 @@ int launch(const TcTable& tab, const float* A, long long M, int a_rows, int K, c
   return BN == 64 ? launch_bn<64>(tab, ma, mb, C, M, c_rows, N, K, s) : launch_bn<128>(tab, ma, mb, C, M, c_rows, N, K, s);
 }
 
+template <int KB>
+static int launch_as_kb(const CUtensorMap& ma, const CUtensorMap& mbh, const CUtensorMap& mbl, float* C, long long M, int N, int K,
+                        cudaStream_t s) {
+  int* st = nullptr;
+  cudaError_t e = cudaGetSymbolAddress((void**)&st, g_tc_status);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaFuncSetAttribute(gemm_tf32x3_as_kernel<KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, AsCfg<KB>::SMEM_BYTES);
+  if (e != cudaSuccess) return cuda_fail(e);
+  gemm_tf32x3_as_kernel<KB><<<(unsigned)((M + BM - 1) / BM), NT, AsCfg<KB>::SMEM_BYTES, s>>>(ma, mbh, mbl, C, M, N, K, st);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
+}
+
+// plain C[M, N] = A[M, K] @ Bt[N, K]^T with K <= 128 and several N tiles
+int launch_a_stationary(const float* A, long long M, int K, const float* Bt, int N, float* C, cudaStream_t s) {
+  float* split = nullptr;
+  const long long nw = (long long)N * K;
+  cudaError_t e = cudaMallocAsync((void**)&split, (size_t)nw * 2 * sizeof(float), s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  split_weights_kernel<<<(unsigned)((nw + 255) / 256 < 1024 ? (nw + 255) / 256 : 1024), 256, 0, s>>>(Bt, split, split + nw, nw);
+  alignas(64) CUtensorMap ma, mbh, mbl;
+  int rc = make_map(&ma, A, (uint64_t)K, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, BK, 1, BM);
+  if (rc == FASTEQ_OK) rc = make_map(&mbh, split, (uint64_t)K, (uint64_t)N, 1, (uint64_t)K, (uint64_t)N * K, BK, AS_BN, 1);
+  if (rc == FASTEQ_OK) rc = make_map(&mbl, split + nw, (uint64_t)K, (uint64_t)N, 1, (uint64_t)K, (uint64_t)N * K, BK, AS_BN, 1);
+  if (rc == FASTEQ_OK) {
+    const int kb = (K + BK - 1) / BK;
+    rc = kb <= 2 ? launch_as_kb<2>(ma, mbh, mbl, C, M, N, K, s) : launch_as_kb<4>(ma, mbh, mbl, C, M, N, K, s);
+  }
+  cudaFreeAsync(split, s);
+  return rc;
+}
+
 int device_status(int* code) {
   int v = 0, zero = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
@@ -317,6 +525,7 @@ extern "C" int fasteq_gemm_tf32x3(const void* A, const void* Bt, void* C, int64_
   if (M == 0) return FASTEQ_OK;
   if (!A || !Bt || !C) return FASTEQ_INVALID;
   if (!tc::supported(M, 1, K, 1, N, 1, A, Bt, C)) return FASTEQ_UNSUPPORTED;
+  if (K <= 128 && N >= 256) return tc::launch_a_stationary((const float*)A, M, K, (const float*)Bt, N, (float*)C, (cudaStream_t)stream);
   tc::TcTable tab{};
   tab.n_groups = 1; tab.n_items = 1; tab.group_c_row[0] = 0; tab.group_first[0] = 0; tab.group_first[1] = 1;
   tab.item_first[0] = 0; tab.item_first[1] = 1; tab.path_a_row[0] = 0; tab.path_w[0] = 0;
