@@ -38,9 +38,9 @@ class Tuning:
 def default_tuning(spec: U1DSpec, direction: str) -> Tuning:
     """Defaults from sweeps on B200 (128-channel FP32 signatures with 55 and 106 output segments).
 
-    Forward: one channel per thread, the receiver row in registers; two thread groups split the
-    output segments when there are too many for one thread.  Backward: packed two-channel
-    arithmetic with two pipelines per CTA when the channel count allows, else one channel per thread."""
+    With 128-channel FP32 tiles both directions use packed two-channel arithmetic; the forward keeps
+    the receiver row in registers (two thread groups split the output segments when there are too
+    many for one thread), the backward runs two pipelines per CTA.  Other shapes: one channel per thread."""
     f32 = spec.dtype == "f32"
     cap = 128 if f32 else 64
     ct = min((spec.u + 31) // 32 * 32, cap)
@@ -51,6 +51,12 @@ def default_tuning(spec: U1DSpec, direction: str) -> Tuning:
                 break
     big = spec.out_segs > 64
     if direction == "fwd":
+        if f32 and spec.u % 128 == 0:
+            # packed arithmetic; a small row fits one thread group (two pipelines fill the four
+            # sub-partitions), a large row is split over two groups
+            if big:
+                return Tuning(ct=128, groups=2, stages=6, min_blocks=1, vec=2, pipes=1)
+            return Tuning(ct=128, groups=1, stages=6, min_blocks=2, vec=2, pipes=2)
         if f32:
             return Tuning(ct=ct, groups=2 if big else 1, stages=8, min_blocks=1 if big else 3)
         return Tuning(ct=ct, groups=1, stages=4, min_blocks=2)

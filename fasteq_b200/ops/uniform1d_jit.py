@@ -257,7 +257,7 @@ def _tuning_for(spec: U1DSpec, direction: str, tensors) -> Optional[_emit.Tuning
     tun = _TUNING_OVERRIDE.get(direction) or _emit.default_tuning(spec, direction)
     if tun.vec == 2 and any(t is not None and t.data_ptr() % 8 for t in tensors):
         import dataclasses
-        return dataclasses.replace(tun, vec=1, pipes=1, min_blocks=min(tun.min_blocks + 1, 3))
+        return dataclasses.replace(tun, vec=1, pipes=1, groups=max(tun.groups, 1), min_blocks=min(tun.min_blocks + 1, 3))
     return tun
 
 
