@@ -231,6 +231,65 @@ def model_bench(args, dev, rank, dist, n_boxes: int):
             "energy_finite": bool(torch.isfinite(out["energy"]).all()), "forces_finite": bool(torch.isfinite(out["forces"]).all())}
 
 
+def operator_extras(args, dev):
+    """Standalone timings of the other two operators of the path (BASELINE config 4 asks for the
+    SymmetricContraction on 200k nodes; SO3Linear at config 1's node count)."""
+    from fasteq_b200.descriptors import linear, symmetric_contraction
+    from fasteq_b200.ops import fast_equi_linear, fast_stc_uniform1d_jit
+    g = torch.Generator().manual_seed(0)
+    out = {}
+
+    def timed(fn, k=10):
+        fn(); fn(); torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(k):
+            fn()
+        b.record(); torch.cuda.synchronize()
+        return a.elapsed_time(b) / k * 1e-3
+
+    # SymmetricContraction, correlation 3, 128 channels, 10 species, 200k nodes
+    d = symmetric_contraction("128x0e+128x1o+128x2e+128x3o", "128x0e+128x1o")
+    B, U = 200000, d.u_dim
+    x1 = (torch.randn(B, d.x1_segs, U, generator=g) * 0.3).to(dev).requires_grad_(True)
+    x0 = (torch.randn(10, d.x0_segs, U, generator=g) * 0.1).to(dev)
+    i0 = torch.randint(0, 10, (B,), generator=g).to(dev)
+    r = torch.randn(B, d.out_segs * U, generator=g).to(dev)
+    coeffs, paths, idx = d.tensors(torch.float32, dev)
+    with torch.no_grad():
+        t_f = timed(lambda: fast_stc_uniform1d_jit(x1, x0, i0, coeffs, paths, idx, d.out_segs))
+    def fb():
+        o = fast_stc_uniform1d_jit(x1, x0, i0, coeffs, paths, idx, d.out_segs)
+        torch.autograd.grad(o, x1, r)
+    t_fb = timed(fb)
+    lens = (d.paths != -1).sum(1) - 1                       # multiplications + add per path (SURVEY: flops = B*U*sum L_p)
+    flops = float(B) * U * float(lens.sum())
+    byts = 4.0 * (B * d.x1_segs * U + B * d.out_segs * U + 10 * d.x0_segs * U) + 4 * B
+    out["stc_200k"] = {"nodes": B, "paths": d.num_paths, "fwd_ms": t_f * 1e3, "fwd_bwd_ms": t_fb * 1e3, "nodes_per_s_fwd": B / t_f,
+                       "fwd_gflops_path_count": flops / t_f / 1e9, "fwd_hbm_gbs": byts / t_f / 1e9}
+    # SO3Linear after the tensor product of config 1: 55 -> 16 rows, 128 channels, 12,288 nodes
+    from fasteq_b200.descriptors import full_channelwise_instructions
+    from fasteq_b200.irreps import Irreps
+    irr_tp, _ = full_channelwise_instructions("128x0e+128x1o", Irreps.spherical_harmonics(3), 3)
+    dl = linear(irr_tp, "128x0e+128x1o+128x2e+128x3o")
+    N = 12288
+    x = torch.randn(N, irr_tp.dim, generator=g).to(dev).requires_grad_(True)
+    w = torch.randn(dl.num_weights, generator=g).to(dev)
+    ro = torch.randn(N, 16 * 128, generator=g).to(dev)
+    with torch.no_grad():
+        t_l = timed(lambda: fast_equi_linear(dl, w, x))
+    def lb():
+        o = fast_equi_linear(dl, w, x)
+        torch.autograd.grad(o, x, ro)
+    t_lb = timed(lb)
+    rows = sum(p_rows for p_rows in [irr_tp[p.indices[1]].ir.dim for p in dl.paths])
+    lbytes = 4.0 * (N * irr_tp.dim + N * 16 * 128 + dl.num_weights)
+    out["so3linear_after_tp"] = {"nodes": N, "paths": len(dl.paths), "fwd_ms": t_l * 1e3, "fwd_bwd_ms": t_lb * 1e3,
+                                 "fwd_hbm_gbs": lbytes / t_l / 1e9, "fwd_tflops": 2.0 * N * 128 * 128 * rows / t_l / 1e12,
+                                 "precision": "3xTF32 on tcgen05"}
+    return out
+
+
 def reference_arm(args):
     """The reference's CPU path (e3nn algorithm, restated in oracle/) on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -398,6 +457,10 @@ def main():
         if not args.no_halo:
             model["single_graph"] = halo_model_bench(args, dev, rank, world, dist)
 
+    extras = None
+    if rank == 0 and not args.no_model:
+        extras = operator_extras(args, dev)
+
     status = {name: m.device_status() for name, m in (("fwd", u1d.get_module(call.spec, "fwd")),
                                                       ("bwd", u1d.get_module(call.spec, "bwd", (True, True, True))))}
 
@@ -416,7 +479,7 @@ def main():
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32" if dtype == torch.float32 else "f64", "data": "synthetic",
             "config": dict(config_dict(args.workload, inp, world), atoms_per_gpu=N, edges_per_gpu=E),
-            "roofline": roof, "roofline_fwd": roof_fwd, "roofline_fwd_bwd": roof_both, "cpu_baseline": cpu, "e2e": e2e, "model": model,
+            "roofline": roof, "roofline_fwd": roof_fwd, "roofline_fwd_bwd": roof_both, "cpu_baseline": cpu, "e2e": e2e, "model": model, "operators": extras,
             "gpu_launches": 2 * args.steps, "clocks": clocks.summary(), "device_status": status,
         }
         print(json.dumps(line), flush=True)
