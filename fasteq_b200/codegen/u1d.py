@@ -33,6 +33,7 @@ class Tuning:
     vec: int = 1       # channels per thread: 2 = packed f32x2 arithmetic (FP32, even u)
     two_pass: bool = False  # backward: evaluate a block once for grad_w and once for grad_x / grad_y
     pipes: int = 1     # independent producer/consumer pipelines per CTA (keeps all four SM sub-partitions busy)
+    go_smem: bool = True   # backward: stage the receiver's grad_out row in shared memory (else read it through L1)
 
 
 def default_tuning(spec: U1DSpec, direction: str) -> Tuning:
@@ -510,7 +511,7 @@ def emit_backward(spec: U1DSpec, tun: Tuning, need_gw: bool, need_gx: bool, need
     src = [_prelude(spec, tun, extra, ncons_warps, emit_empty=False)]
     src.append(f"""
 constexpr int NTHREADS = {threads};
-constexpr int NGO = 1;                                 // grad_out row buffers
+constexpr int NGO = {1 if tun.go_smem else 0};                                 // grad_out row buffers in shared memory (0: read through L1)
 constexpr int GO_BYTES = round_up(OSEG * CT * (int)sizeof(T), 128);
 constexpr int PIPE_BYTES = BAR_BYTES + STAGES * STAGE_BYTES + NGO * GO_BYTES;
 constexpr int SMEM_BYTES = cfg::PIPES * PIPE_BYTES;
@@ -546,9 +547,10 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
     Producer p{{g, w, x, y, stages, full, empty, lane, 0u, (int)blockIdx.x * cfg::PIPES + pipe}};
     uint32_t nseg = 0;
     auto begin = [&](int row, int ct, int ln) {{
+      if (NGO == 0) return;
       // stage the receiver's grad_out tile once per segment
-      const int b = nseg % NGO;
-      const uint32_t ph = (nseg / NGO) & 1u;
+      const int b = nseg % (NGO ? NGO : 1);
+      const uint32_t ph = (nseg / (NGO ? NGO : 1)) & 1u;
       mbar_wait(&go_empty[b], ph ^ 1u, g.status);
       const int valid = (U - ct * CT) < CT ? (U - ct * CT) : CT;
       if (ln == 0) mbar_arrive_expect_tx(&go_full[b], g.bulk_ok ? (uint32_t)(OSEG * valid * sizeof(T)) : 0u);
@@ -595,8 +597,8 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
     const Meta m = *reinterpret_cast<const Meta*>(st + OFF_META);
     const int valid = (U % CT == 0) ? CT : ((U - m.ct * CT) < CT ? (U - m.ct * CT) : CT);
     const bool live = ch < valid;
-    const int gb = nseg % NGO;
-    if (m.flags & F_FIRST) mbar_wait(&go_full[gb], (nseg / NGO) & 1u, g.status);""")
+    const int gb = nseg % (NGO ? NGO : 1);
+    if (NGO && (m.flags & F_FIRST)) mbar_wait(&go_full[gb], (nseg / (NGO ? NGO : 1)) & 1u, g.status);""")
     if spec.w_shared and need_gw:
         L.append("    if ((m.flags & (F_DATA | F_DONE)) && (m.ct != gws_ct || (m.flags & F_DONE))) {")
         L.append("      if (ch < ((U - gws_ct * CT) < CT ? (U - gws_ct * CT) : CT)) {")
@@ -611,13 +613,16 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
     L.append("    if ((m.flags & F_DATA) && live) {")
     L.append("      const T* sx = reinterpret_cast<const T*>(st + OFF_X) + ch;")
     L.append(f"      const T* sy = reinterpret_cast<const T*>(st + OFF_Y){' + ch' if spec.y_vec else ''};")
-    L.append("      const T* sgo = reinterpret_cast<const T*>(gobuf + (size_t)gb * GO_BYTES) + ch;")
+    if tun.go_smem:
+        L.append("      const T* sgo = reinterpret_cast<const T*>(gobuf + (size_t)gb * GO_BYTES) + ch;")
+    else:
+        L.append("      const T* sgo = go + (size_t)m.row * OSEG * U + (size_t)m.ct * CT + ch;")
     if spec.w_shared:
         L.append("#define W(i) VS::ld(w + (size_t)(i) * U + m.ct * CT + ch)")
     else:
         L.append("      const T* sw = reinterpret_cast<const T*>(st + OFF_W) + ch;")
         L.append("#define W(i) VS::ld(sw + (i) * CT)")
-    L.append("#define GO(v) VS::ld(sgo + (v) * CT)")
+    L.append("#define GO(v) VS::ld(sgo + (v) * CT)" if tun.go_smem else "#define GO(v) VS::ldg(sgo + (size_t)(v) * U)")
     L += _load_xy(spec, "      ")
     if need_gx:
         L += [f"      V gx{j} = VS::zero();" for j in range(spec.x_segs)]
@@ -740,7 +745,7 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
         L.append("    }")
     L.append("""    __syncwarp();
     if (lane == 0) {
-      if (m.flags & F_LAST) mbar_arrive(&go_empty[gb]);
+      if (NGO && (m.flags & F_LAST)) mbar_arrive(&go_empty[gb]);
       mbar_arrive(&empty[stage]);
     }
     if (m.flags & F_LAST) ++nseg;

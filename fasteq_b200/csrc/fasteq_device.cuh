@@ -141,6 +141,7 @@ template <> struct VT<float> {
   static __device__ __forceinline__ float zero() { return 0.f; }
   static __device__ __forceinline__ float hsum(float v) { return v; }
   static __device__ __forceinline__ float ld(const float* p) { return *p; }
+  static __device__ __forceinline__ float ldg(const float* p) { return __ldg(p); }
   static __device__ __forceinline__ void st(float* p, float v) { *p = v; }
   static __device__ __forceinline__ void red(float* p, float v) { red_add(p, v); }
 };
@@ -150,6 +151,7 @@ template <> struct VT<double> {
   static __device__ __forceinline__ double zero() { return 0.0; }
   static __device__ __forceinline__ double hsum(double v) { return v; }
   static __device__ __forceinline__ double ld(const double* p) { return *p; }
+  static __device__ __forceinline__ double ldg(const double* p) { return __ldg(p); }
   static __device__ __forceinline__ void st(double* p, double v) { *p = v; }
   static __device__ __forceinline__ void red(double* p, double v) { red_add(p, v); }
 };
@@ -159,6 +161,7 @@ template <> struct VT<float2> {
   static __device__ __forceinline__ float2 zero() { return make_float2(0.f, 0.f); }
   static __device__ __forceinline__ float hsum(float2 v) { return v.x + v.y; }
   static __device__ __forceinline__ float2 ld(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ float2 ldg(const float* p) { return __ldg(reinterpret_cast<const float2*>(p)); }
   static __device__ __forceinline__ void st(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
   static __device__ __forceinline__ void red(float* p, float2 v) { red_add2(p, v); }
 };
