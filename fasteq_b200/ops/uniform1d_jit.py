@@ -285,9 +285,68 @@ def _run_bwd(call: _Call, grad_out, w, x, y, needs):
     return gw, gx, gy
 
 
+class FastUniform1dBackwardFunction(torch.autograd.Function):
+    """First backward as a differentiable function (reference: fasteq/ops/uniform1d_jit.py:3098-3188),
+    so that force losses can be trained.  The operator is trilinear in (w, x, y), hence every term of
+    the second backward is again a forward or a one-gradient backward of the same signature with two
+    operands swapped for incoming second-order gradients; no separate double-backward kernels exist:
+
+        d_go = F(ggw, x, y) + F(w, ggx, y) + F(w, x, ggy)
+        d_w  = Bw(go; ggx, y) + Bw(go; x, ggy)      (Bw = gradient with respect to the weight slot)
+        d_x  = Bx(go; ggw, y) + Bx(go; w, ggy)
+        d_y  = By(go; ggw, x) + By(go; w, ggx)
+    """
+
+    @staticmethod
+    def forward(ctx, grad_out, w, x, y, call, needs):
+        gw, gx, gy = _run_bwd(call, grad_out, w, x, y, needs)
+        ctx.call, ctx.needs = call, needs
+        ctx.save_for_backward(grad_out, w, x, y)
+        ctx.set_materialize_grads(False)
+        outs = tuple(g if g is not None else t.new_empty((0,)) for g, t in ((gw, w), (gx, x), (gy, y)))
+        return outs
+
+    @staticmethod
+    def backward(ctx, ggw, ggx, ggy):
+        go, w, x, y = ctx.saved_tensors
+        call, needs = ctx.call, ctx.needs
+        ggw = ggw.contiguous() if (ggw is not None and needs[0]) else None
+        ggx = ggx.contiguous() if (ggx is not None and needs[1]) else None
+        ggy = ggy.contiguous() if (ggy is not None and needs[2]) else None
+        want_go, want_w, want_x, want_y = ctx.needs_input_grad[:4]
+
+        def add(a, b):
+            return b if a is None else (a if b is None else a + b)
+
+        d_go = d_w = d_x = d_y = None
+        if want_go:
+            if ggw is not None:
+                d_go = add(d_go, _run_fwd(call, ggw, x, y))
+            if ggx is not None:
+                d_go = add(d_go, _run_fwd(call, w, ggx, y))
+            if ggy is not None:
+                d_go = add(d_go, _run_fwd(call, w, x, ggy))
+        if want_w:
+            if ggx is not None:
+                d_w = add(d_w, _run_bwd(call, go, w, ggx, y, (True, False, False))[0])
+            if ggy is not None:
+                d_w = add(d_w, _run_bwd(call, go, w, x, ggy, (True, False, False))[0])
+        if want_x:
+            if ggw is not None:
+                d_x = add(d_x, _run_bwd(call, go, ggw, x, y, (False, True, False))[1])
+            if ggy is not None:
+                d_x = add(d_x, _run_bwd(call, go, w, x, ggy, (False, True, False))[1])
+        if want_y:
+            if ggw is not None:
+                d_y = add(d_y, _run_bwd(call, go, ggw, x, y, (False, False, True))[2])
+            if ggx is not None:
+                d_y = add(d_y, _run_bwd(call, go, w, ggx, y, (False, False, True))[2])
+        return d_go, d_w, d_x, d_y, None, None
+
+
 class FastUniform1dJITFunction(torch.autograd.Function):
-    """Autograd wrapper (reference: fasteq/ops/uniform1d_jit.py:3194-3326).  The backward
-    produces exactly the gradients autograd asks for; it is not itself differentiable."""
+    """Autograd wrapper (reference: fasteq/ops/uniform1d_jit.py:3194-3326).  The backward produces
+    exactly the gradients autograd asks for and is itself differentiable."""
 
     @staticmethod
     def forward(ctx, w, x, y, input_indices, output_indices, meta):
@@ -303,9 +362,8 @@ class FastUniform1dJITFunction(torch.autograd.Function):
         needs = tuple(bool(n) for n in ctx.needs_input_grad[:3])
         if not any(needs):
             return None, None, None, None, None, None
-        grad_out = grad_out.contiguous()
-        gw, gx, gy = _run_bwd(ctx.call, grad_out, w, x, y, needs)
-        return gw, gx, gy, None, None, None
+        gw, gx, gy = FastUniform1dBackwardFunction.apply(grad_out.contiguous(), w, x, y, ctx.call, needs)
+        return (gw if needs[0] else None), (gx if needs[1] else None), (gy if needs[2] else None), None, None, None
 
 
 def fast_uniform1d_jit(w, x, y, input_indices, output_indices, meta, use_multiwarp_candidates: Optional[bool] = None):

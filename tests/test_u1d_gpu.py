@@ -162,3 +162,34 @@ def test_no_device_fault_recorded():
     torch.cuda.synchronize()
     for mod in uniform1d_jit._MODULES.values():
         assert mod.device_status() == 0
+
+
+def test_double_backward_matches_torch_autograd():
+    """Gradients of a function of the first-order gradients (a force-matching loss) against torch
+    autograd through a dense float64 restatement of the operator."""
+    from fasteq_b200.ops import fast_uniform1d_jit
+    from oracle.mace_style_ref import u1d_scatter
+    d, paths = _tp("32x0e+32x1o", 2, 2)
+    N, E, U = 12, 60, d.u_dim
+    g = torch.Generator().manual_seed(4)
+    src = torch.randint(0, N, (E,), generator=g)
+    dst, order = torch.sort(torch.randint(0, N, (E,), generator=g), stable=True)
+    src = src[order]
+    w = torch.randn(E, d.w_seg_num * U, generator=g, dtype=torch.float64)
+    x = torch.randn(N, d.x_seg_num * U, generator=g, dtype=torch.float64)
+    y = torch.randn(E, d.y_seg_num, generator=g, dtype=torch.float64)
+    r = torch.randn(N, d.out_seg_num * U, generator=g, dtype=torch.float64)
+    ax, ay, aw = (torch.randn(t.shape, generator=g, dtype=torch.float64) for t in (x, y, w))
+
+    def loss(op, dev):
+        wd, xd, yd = (t.to(dev).requires_grad_(True) for t in (w, x, y))
+        out = op(wd, xd, yd)
+        gw, gx, gy = torch.autograd.grad((out * r.to(dev)).sum(), (wd, xd, yd), create_graph=True)
+        second = (gx * ax.to(dev)).sum() + (gy * ay.to(dev)).sum() + (gw * aw.to(dev)).sum() + (out ** 2).sum()
+        return torch.autograd.grad(second, (wd, xd, yd))
+
+    meta = d.meta(torch.float64, "cuda")
+    got = loss(lambda a, b, c: fast_uniform1d_jit(a, b, c, {1: src.int().cuda()}, {0: dst.int().cuda()}, meta), "cuda")
+    ref = loss(lambda a, b, c: u1d_scatter(a, b, c, d, src, dst, N), "cpu")
+    for name, a, b in zip(("w", "x", "y"), got, ref):
+        _close(a, b.numpy(), torch.float64, f"second-order gradient wrt {name}")
