@@ -1,0 +1,138 @@
+// Equivariant gate non-linearity (e3nn ``nn.Gate``) on ir_mul tensors, forward and backward.
+//
+//   out = [ c_i * act_i(scalar_i) ] (+) [ c_j * act_j(gate_j) * gated_j ]
+//
+// Input row layout [segments, u]: the scalar segments, then one gate segment per gated irrep block,
+// then the gated irreps ((2l+1) segments each).  Output: scalar segments, then the gated irreps.
+// The reference treats the gate as a neighbour of the hot path and ships it among its e3nn shims
+// (fasteq/e3nn/triton/nn/_gate.py:17-39, fasteq/triton/fused_equivariant_gate.py).
+#include <cstdio>
+#include <cstdint>
+#include <cuda_runtime.h>
+#include "fasteq_b200.h"
+#include "core_common.h"
+
+using namespace fasteq;
+
+namespace {
+constexpr int kMaxSeg = 96;
+
+struct GateTable {
+  int n_in, n_out, n_scalar, n_gate;
+  int act[kMaxSeg];        // per scalar / gate segment (index = input segment): activation code
+  float cst[kMaxSeg];      // second-moment normalisation constant of that activation
+  int gate_of[kMaxSeg];    // per gated INPUT segment: its gate's input segment; -1 for scalars / gates
+  int first_gated[kMaxSeg];// per gate segment: first gated input segment of its block
+  int n_gated[kMaxSeg];    // per gate segment: 2l+1
+};
+
+template <typename T> __device__ __forceinline__ T act_f(int code, T x) {
+  switch (code) {
+    case 1: return x / (T(1) + exp(-x));               // silu
+    case 2: return tanh(x);
+    case 3: return T(1) / (T(1) + exp(-x));             // sigmoid
+    case 4: return fabs(x);
+    default: return x;
+  }
+}
+template <typename T> __device__ __forceinline__ T act_d(int code, T x) {
+  switch (code) {
+    case 1: { const T s = T(1) / (T(1) + exp(-x)); return s * (T(1) + x * (T(1) - s)); }
+    case 2: { const T t = tanh(x); return T(1) - t * t; }
+    case 3: { const T s = T(1) / (T(1) + exp(-x)); return s * (T(1) - s); }
+    case 4: return x >= T(0) ? T(1) : T(-1);
+    default: return T(1);
+  }
+}
+
+template <typename T>
+__global__ void gate_fwd_kernel(const T* __restrict__ x, T* __restrict__ out, long long batch, int u, const __grid_constant__ GateTable t) {
+  const long long total = batch * t.n_out * u;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % u);
+    const int so = (int)((i / u) % t.n_out);
+    const long long b = i / ((long long)u * t.n_out);
+    const T* row = x + (size_t)b * t.n_in * u;
+    if (so < t.n_scalar) {
+      out[i] = T(t.cst[so]) * act_f<T>(t.act[so], row[(size_t)so * u + c]);
+    } else {
+      const int si = so + t.n_gate;                 // gated input segment
+      const int g = t.gate_of[si];
+      out[i] = T(t.cst[g]) * act_f<T>(t.act[g], row[(size_t)g * u + c]) * row[(size_t)si * u + c];
+    }
+  }
+}
+
+template <typename T>
+__global__ void gate_bwd_kernel(const T* __restrict__ x, const T* __restrict__ go, T* __restrict__ gx, long long batch, int u,
+                                const __grid_constant__ GateTable t) {
+  const long long total = batch * t.n_in * u;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % u);
+    const int si = (int)((i / u) % t.n_in);
+    const long long b = i / ((long long)u * t.n_in);
+    const T* row = x + (size_t)b * t.n_in * u;
+    const T* grow = go + (size_t)b * t.n_out * u;
+    if (si < t.n_scalar) {
+      gx[i] = grow[(size_t)si * u + c] * T(t.cst[si]) * act_d<T>(t.act[si], row[(size_t)si * u + c]);
+    } else if (si < t.n_scalar + t.n_gate) {
+      T acc = T(0);
+      for (int m = 0; m < t.n_gated[si]; ++m) {
+        const int sg = t.first_gated[si] + m;
+        acc += grow[(size_t)(sg - t.n_gate) * u + c] * row[(size_t)sg * u + c];
+      }
+      gx[i] = acc * T(t.cst[si]) * act_d<T>(t.act[si], row[(size_t)si * u + c]);
+    } else {
+      const int g = t.gate_of[si];
+      gx[i] = grow[(size_t)(si - t.n_gate) * u + c] * T(t.cst[g]) * act_f<T>(t.act[g], row[(size_t)g * u + c]);
+    }
+  }
+}
+
+int build(const fasteq_gate_problem* p, GateTable* t) {
+  if (!p || p->n_scalar < 0 || p->n_gate < 0 || p->u < 1 || p->batch < 0) return FASTEQ_INVALID;
+  if ((p->n_scalar + p->n_gate) > 0 && (!p->act || !p->cst)) return FASTEQ_INVALID;
+  if (p->n_gate > 0 && !p->gated_dims) return FASTEQ_INVALID;
+  int gated = 0;
+  for (int k = 0; k < p->n_gate; ++k) gated += p->gated_dims[k];
+  t->n_scalar = p->n_scalar; t->n_gate = p->n_gate;
+  t->n_in = p->n_scalar + p->n_gate + gated; t->n_out = p->n_scalar + gated;
+  if (t->n_in > kMaxSeg) return FASTEQ_UNSUPPORTED;
+  for (int s = 0; s < t->n_in; ++s) { t->act[s] = 0; t->cst[s] = 1.f; t->gate_of[s] = -1; t->first_gated[s] = 0; t->n_gated[s] = 0; }
+  for (int s = 0; s < p->n_scalar + p->n_gate; ++s) { t->act[s] = p->act[s]; t->cst[s] = (float)p->cst[s]; }
+  int pos = p->n_scalar + p->n_gate;
+  for (int k = 0; k < p->n_gate; ++k) {
+    const int g = p->n_scalar + k;
+    t->first_gated[g] = pos; t->n_gated[g] = p->gated_dims[k];
+    for (int m = 0; m < p->gated_dims[k]; ++m) t->gate_of[pos++] = g;
+  }
+  return FASTEQ_OK;
+}
+}  // namespace
+
+extern "C" int fasteq_gate_forward(const fasteq_gate_problem* p, const void* x, void* out, fasteq_stream_t stream) {
+  GateTable t; int rc = build(p, &t);
+  if (rc != FASTEQ_OK) return rc;
+  if (p->batch == 0) return FASTEQ_OK;
+  if (!x || !out) return FASTEQ_INVALID;
+  const long long total = p->batch * t.n_out * p->u;
+  const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
+  if (p->dtype == FASTEQ_F32) gate_fwd_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)x, (float*)out, p->batch, p->u, t);
+  else gate_fwd_kernel<double><<<blocks, 256, 0, (cudaStream_t)stream>>>((const double*)x, (double*)out, p->batch, p->u, t);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
+}
+
+extern "C" int fasteq_gate_backward(const fasteq_gate_problem* p, const void* x, const void* grad_out, void* grad_x,
+                                    fasteq_stream_t stream) {
+  GateTable t; int rc = build(p, &t);
+  if (rc != FASTEQ_OK) return rc;
+  if (p->batch == 0) return FASTEQ_OK;
+  if (!x || !grad_out || !grad_x) return FASTEQ_INVALID;
+  const long long total = p->batch * t.n_in * p->u;
+  const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
+  if (p->dtype == FASTEQ_F32) gate_bwd_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)x, (const float*)grad_out, (float*)grad_x, p->batch, p->u, t);
+  else gate_bwd_kernel<double><<<blocks, 256, 0, (cudaStream_t)stream>>>((const double*)x, (const double*)grad_out, (double*)grad_x, p->batch, p->u, t);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
+}

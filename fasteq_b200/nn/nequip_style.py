@@ -1,0 +1,92 @@
+"""Synthetic NequIP-style model for BASELINE configuration 3 (energy + forces).
+
+Hidden features ``C x (0e+0o+1e+1o+2e+2o)``, edge attributes SH(l <= 2), ``num_layers`` interaction
+blocks of { SO3Linear, ChannelwiseTensorProduct + scatter-sum with radial-MLP weights, SO3Linear to the
+gate's input, species-independent self connection, Gate (SiLU on even scalars, tanh on odd scalars,
+SiLU gates) } following …/nequip/nn/interaction_block.py:79-198, then a scalar readout.  The
+species-dependent self connection of NequIP is a FullyConnectedTensorProduct with a one-hot
+operand (outside this path); a plain SO3Linear stands in for it.  With ``halo`` the sender features
+are extended by ghost rows before every tensor product (…/interaction_block.py:183-198).
+"""
+from __future__ import annotations
+
+import math
+from typing import List
+
+import torch
+
+from ..descriptors import full_channelwise_instructions
+from ..irreps import Irreps
+from ..ops.gate import GateSpec, gate
+from ..ops.spherical_harmonics import SphericalHarmonics
+from .mace_style import RadialMLP, bessel_basis, polynomial_cutoff
+from .modules import ChannelwiseTensorProduct, SO3Linear
+
+
+def hidden_irreps(channels: int, lmax: int) -> Irreps:
+    return Irreps([(channels, (l, p)) for l in range(lmax + 1) for p in (1, -1)])
+
+
+class NequIPStyleLayer(torch.nn.Module):
+    def __init__(self, irreps_in: Irreps, channels: int, lmax: int, sh_lmax: int, num_basis: int, radial_hidden: List[int],
+                 avg_num_neighbors: float):
+        super().__init__()
+        sh = Irreps.spherical_harmonics(sh_lmax)
+        hid = hidden_irreps(channels, lmax)
+        gated = [b for b in hid if b.ir.l > 0]
+        self.gate_in = Irreps([(channels, (0, 1)), (channels, (0, -1))] + [(channels, (0, 1))] * len(gated) + [(b.mul, b.ir) for b in gated])
+        self.gate_spec = GateSpec(channels, ["silu", "tanh"], ["silu"] * len(gated), [b.ir.l for b in gated])
+        self.linear_1 = SO3Linear(irreps_in, irreps_in)
+        irreps_tp, instr = full_channelwise_instructions(irreps_in, sh, lmax)
+        self.conv_tp = ChannelwiseTensorProduct(irreps_in, sh, irreps_tp, instr)
+        self.radial = RadialMLP(num_basis, radial_hidden, self.conv_tp.weight_numel)
+        self.linear_2 = SO3Linear(irreps_tp, self.gate_in)
+        self.self_connection = SO3Linear(irreps_in, self.gate_in)
+        self.inv_neighbors = 1.0 / avg_num_neighbors
+        self.irreps_out = hid
+
+    def forward(self, h, edge_sh, edge_radial, edge_dst, edge_src, halo=None):
+        up = self.linear_1(h)
+        n_owned = up.shape[0]
+        if halo is not None:
+            up = halo(up)
+        msg = self.conv_tp(up, edge_sh, self.radial(edge_radial), edge_dst, edge_src)[:n_owned]
+        pre = self.linear_2(msg) * self.inv_neighbors + self.self_connection(h)
+        return gate(pre, self.gate_spec)
+
+
+class NequIPStyleModel(torch.nn.Module):
+    def __init__(self, num_species: int = 2, channels: int = 64, lmax: int = 2, sh_lmax: int = 2, num_layers: int = 4,
+                 r_max: float = 4.0, num_basis: int = 8, radial_hidden=(64, 64), avg_num_neighbors: float = 27.0, envelope_p: int = 5):
+        super().__init__()
+        self.r_max, self.num_basis, self.envelope_p, self.channels = r_max, num_basis, envelope_p, channels
+        self.embedding = torch.nn.Parameter(torch.randn(num_species, channels))
+        self.sh = SphericalHarmonics(list(range(sh_lmax + 1)), True, "component")
+        layers, irreps_in = [], Irreps([(channels, (0, 1))])
+        for _ in range(num_layers):
+            layer = NequIPStyleLayer(irreps_in, channels, lmax, sh_lmax, num_basis, list(radial_hidden), avg_num_neighbors)
+            layers.append(layer)
+            irreps_in = layer.irreps_out
+        self.layers = torch.nn.ModuleList(layers)
+        self.readout = torch.nn.Parameter(torch.randn(channels) / math.sqrt(channels))
+
+    def node_energies(self, pos, species, edge_src, edge_dst, edge_shift, halo=None):
+        pos_ext = pos if halo is None else halo(pos)
+        vec = pos_ext[edge_src] + edge_shift - pos_ext[edge_dst]
+        r = vec.norm(dim=-1)
+        radial = bessel_basis(r, self.r_max, self.num_basis) * polynomial_cutoff(r, self.r_max, self.envelope_p).unsqueeze(-1)
+        edge_sh = self.sh(vec)
+        h = self.embedding[species]
+        for layer in self.layers:
+            h = layer(h, edge_sh, radial, edge_dst, edge_src, halo)
+        return h[:, : self.channels] @ self.readout
+
+    def forward(self, pos, species, edge_src, edge_dst, edge_shift, forces: bool = True, halo=None):
+        if forces:
+            pos = pos.detach().requires_grad_(True)
+        e_node = self.node_energies(pos, species, edge_src, edge_dst, edge_shift, halo)
+        out = {"energy": e_node.sum().reshape(1)}
+        if forces:
+            (g,) = torch.autograd.grad(e_node.sum(), pos)
+            out["forces"] = -g
+        return out

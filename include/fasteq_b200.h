@@ -203,6 +203,26 @@ int fasteq_eqlinear_forward(const fasteq_eqlinear_problem* p /* host */, const v
 int fasteq_eqlinear_dgrad(const fasteq_eqlinear_problem* p /* host */, const void* w, const void* grad_out,
                           void* grad_x, fasteq_stream_t stream);
 
+/* ------------------------------------------------------------------------- *
+ * Gate non-linearity (e3nn nn.Gate) on ir_mul rows [segments, u]: input = scalar segments, one gate
+ * segment per gated irrep block, then the gated irreps; output = scalar segments, gated irreps.
+ * Activation codes: 0 identity, 1 silu, 2 tanh, 3 sigmoid, 4 abs; cst = the activation's
+ * normalisation constant.  Counterpart of fasteq/e3nn/triton/nn/_gate.py:17-39 (a neighbour of the
+ * hot path, needed by NequIP-style networks).
+ * ------------------------------------------------------------------------- */
+typedef struct fasteq_gate_problem {
+  int32_t dtype;                /* fasteq_dtype */
+  int32_t u;
+  int32_t n_scalar, n_gate;
+  int64_t batch;
+  const int32_t* act;           /* host [n_scalar + n_gate] */
+  const double* cst;            /* host [n_scalar + n_gate] */
+  const int32_t* gated_dims;    /* host [n_gate] 2l+1 of each gated block */
+} fasteq_gate_problem;
+int fasteq_gate_forward(const fasteq_gate_problem* p /* host */, const void* x, void* out, fasteq_stream_t stream);
+int fasteq_gate_backward(const fasteq_gate_problem* p /* host */, const void* x, const void* grad_out, void* grad_x,
+                         fasteq_stream_t stream);
+
 /* Dense layer of the radial MLP: C[M, N] = A[M, K] @ Bt[N, K]^T, FP32 data, 3xTF32 arithmetic on the
  * tensor cores (Bt is a torch.nn.Linear weight, [out_features, in_features]).  K and N multiples of 4,
  * pointers 16-byte aligned, else FASTEQ_UNSUPPORTED.  The reference leaves this MLP to the model

@@ -84,3 +84,48 @@ def energy_and_forces(model, pos, species, edge_src, edge_dst, edge_shift):
         e = e + h[:, : model.channels] @ p[f"readouts.{li}"]
     (g,) = torch.autograd.grad(e.sum(), pos)
     return e.detach(), -g
+
+
+def gate_ref(x, spec):
+    """Dense torch restatement of the gate on an ir_mul row (e3nn/nn/_gate.py: activations on the
+    scalars, gated irreps times the activated gates)."""
+    u = spec.u
+    x3 = x.reshape(x.shape[0], spec.n_in, u)
+    act = {0: lambda t: t, 1: torch.nn.functional.silu, 2: torch.tanh, 3: torch.sigmoid, 4: torch.abs}
+    outs = [spec.csts[s] * act[spec.acts[s]](x3[:, s]) for s in range(spec.n_scalar)]
+    pos = spec.n_scalar + spec.n_gate
+    for k, dim in enumerate(spec.gated_dims):
+        g = spec.n_scalar + k
+        gv = spec.csts[g] * act[spec.acts[g]](x3[:, g])
+        for m in range(dim):
+            outs.append(gv * x3[:, pos + m])
+        pos += dim
+    return torch.stack(outs, dim=1).reshape(x.shape[0], -1)
+
+
+def nequip_energy_and_forces(model, pos, species, edge_src, edge_dst, edge_shift):
+    """Oracle evaluation of ``fasteq_b200.nn.nequip_style.NequIPStyleModel`` (float64, CPU)."""
+    from fasteq_b200.nn.mace_style import bessel_basis, polynomial_cutoff
+    pos = pos.detach().double().requires_grad_(True)
+    p = {k: v.detach().double().cpu() for k, v in model.state_dict().items()}
+    vec = pos[edge_src] + edge_shift.double() - pos[edge_dst]
+    r = vec.norm(dim=-1)
+    radial = bessel_basis(r, model.r_max, model.num_basis) * polynomial_cutoff(r, model.r_max, model.envelope_p).unsqueeze(-1)
+    ysh = sh_ref.spherical_harmonics(max(model.sh._ls), vec, normalize=True, normalization="component")
+    h = p["embedding"][species]
+    for li, layer in enumerate(model.layers):
+        pre = f"layers.{li}."
+        up = eqlinear(h, p[pre + "linear_1.weight"], layer.linear_1.descriptor)
+        w = radial
+        n_lin = len(layer.radial.layers)
+        for k in range(n_lin):
+            w = w @ p[pre + f"radial.layers.{k}.weight"].T
+            if k + 1 < n_lin:
+                w = torch.nn.functional.silu(w)
+        msg = u1d_scatter(w, up, ysh, layer.conv_tp.descriptor, edge_src, edge_dst, pos.shape[0])
+        x = eqlinear(msg, p[pre + "linear_2.weight"], layer.linear_2.descriptor) * layer.inv_neighbors \
+            + eqlinear(h, p[pre + "self_connection.weight"], layer.self_connection.descriptor)
+        h = gate_ref(x, layer.gate_spec)
+    e = h[:, : model.channels] @ p["readout"]
+    (g,) = torch.autograd.grad(e.sum(), pos)
+    return e.detach(), -g

@@ -97,6 +97,20 @@ for name, a, b in (("simple", "4x0e+4x1o+4x2e", "6x0e+6x1o+6x2e"), ("multi", "4x
     out[f"lin_{name}_ins"] = np.array([(i.i_in, i.i_out) for i in lin.instructions], dtype=np.int64)
     out[f"lin_{name}_pw"] = np.array([i.path_weight for i in lin.instructions])
 
+# 5. e3nn Gate (scalars through SiLU / tanh, gated irreps times SiLU(gates)), with the second-moment
+#    normalisation constants e3nn attaches to the activations
+from e3nn.nn._gate import Gate  # noqa: E402
+gate = Gate("6x0e+6x0o", [torch.nn.functional.silu, torch.tanh], "18x0e", [torch.nn.functional.silu], "6x1o+6x1e+6x2e")
+g = torch.Generator().manual_seed(9)
+gx = torch.randn(11, gate.irreps_in.dim, generator=g, requires_grad=True)
+gout = gate(gx)
+gr = torch.randn(gout.shape, generator=g)
+(ggx,) = torch.autograd.grad((gout * gr).sum(), gx)
+out["gate_irreps"] = np.array([str(gate.irreps_in), str(gate.irreps_out)])
+out["gate_x"], out["gate_out"], out["gate_r"], out["gate_gx"] = gx.detach().numpy(), gout.detach().numpy(), gr.numpy(), ggx.numpy()
+out["gate_cst_scalars"] = np.array([a.cst if a is not None else 1.0 for a in gate.act_scalars.acts])
+out["gate_cst_gates"] = np.array([a.cst if a is not None else 1.0 for a in gate.act_gates.acts])
+
 dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "e3nn_golden.npz")
 np.savez_compressed(dst, **out)
 print("wrote", dst, os.path.getsize(dst), "bytes,", len(out), "arrays")
