@@ -20,7 +20,7 @@ constexpr int kMaxSeg = 96;
 struct GateTable {
   int n_in, n_out, n_scalar, n_gate;
   int act[kMaxSeg];        // per scalar / gate segment (index = input segment): activation code
-  float cst[kMaxSeg];      // second-moment normalisation constant of that activation
+  double cst[kMaxSeg];     // second-moment normalisation constant of that activation
   int gate_of[kMaxSeg];    // per gated INPUT segment: its gate's input segment; -1 for scalars / gates
   int first_gated[kMaxSeg];// per gate segment: first gated input segment of its block
   int n_gated[kMaxSeg];    // per gate segment: 2l+1
@@ -98,8 +98,8 @@ int build(const fasteq_gate_problem* p, GateTable* t) {
   t->n_scalar = p->n_scalar; t->n_gate = p->n_gate;
   t->n_in = p->n_scalar + p->n_gate + gated; t->n_out = p->n_scalar + gated;
   if (t->n_in > kMaxSeg) return FASTEQ_UNSUPPORTED;
-  for (int s = 0; s < t->n_in; ++s) { t->act[s] = 0; t->cst[s] = 1.f; t->gate_of[s] = -1; t->first_gated[s] = 0; t->n_gated[s] = 0; }
-  for (int s = 0; s < p->n_scalar + p->n_gate; ++s) { t->act[s] = p->act[s]; t->cst[s] = (float)p->cst[s]; }
+  for (int s = 0; s < t->n_in; ++s) { t->act[s] = 0; t->cst[s] = 1.0; t->gate_of[s] = -1; t->first_gated[s] = 0; t->n_gated[s] = 0; }
+  for (int s = 0; s < p->n_scalar + p->n_gate; ++s) { t->act[s] = p->act[s]; t->cst[s] = p->cst[s]; }
   int pos = p->n_scalar + p->n_gate;
   for (int k = 0; k < p->n_gate; ++k) {
     const int g = p->n_scalar + k;
