@@ -38,20 +38,24 @@ def stc_spec(irreps_in: str, irreps_out: str, dtype: str):
     return make_stc_spec(d.paths, d.coeffs, x1_segs=d.x1_segs, x0_segs=d.x0_segs, out_segs=d.out_segs, u=d.u_dim, dtype=dtype)
 
 
-def model_jobs(dtype: str = "f32", **model_kwargs):
-    """Module signatures a ``MACEStyleModel`` needs at run time (forward, force backward)."""
+def model_jobs(dtype: str = "f32", kind: str = "mace", **model_kwargs):
+    """Module signatures a synthetic model needs at run time (forward, force backward)."""
     from .codegen.stc import make_stc_spec
-    from .nn.mace_style import MACEStyleModel
-    model = MACEStyleModel(**model_kwargs)
+    if kind == "mace":
+        from .nn.mace_style import MACEStyleModel as Model
+    else:
+        from .nn.nequip_style import NequIPStyleModel as Model
+    model = Model(**model_kwargs)
     u1d, stcj = [], []
     for layer in model.layers:
         d = layer.conv_tp.descriptor
         spec = make_spec(d.i_list, d.j_list, d.k_list, d.v_list, d.coeff_list, w_segs=d.w_seg_num, x_segs=d.x_seg_num,
                          y_segs=d.y_seg_num, out_segs=d.out_seg_num, u=d.u_dim, dtype=dtype)
         u1d += [(spec, "fwd", (False, False, False)), (spec, "bwd", (True, True, True)), (spec, "bwd", (True, False, True))]
-        s = layer.product.descriptor
-        sp = make_stc_spec(s.paths, s.coeffs, x1_segs=s.x1_segs, x0_segs=s.x0_segs, out_segs=s.out_segs, u=s.u_dim, dtype=dtype)
-        stcj += [(sp, "fwd", False), (sp, "bwd", False)]
+        if hasattr(layer, "product"):
+            s = layer.product.descriptor
+            sp = make_stc_spec(s.paths, s.coeffs, x1_segs=s.x1_segs, x0_segs=s.x0_segs, out_segs=s.out_segs, u=s.u_dim, dtype=dtype)
+            stcj += [(sp, "fwd", False), (sp, "bwd", False)]
     return u1d, stcj, tuple(model.sh._ls)
 
 
@@ -72,8 +76,9 @@ def build_standard_modules(verbose: bool = False) -> None:
     import torch
     from .ops import spherical_harmonics as shmod
     sh_jobs = []
-    for dt, kw in (("f32", {}), ("f32", dict(num_species=2, channels=64, r_max=4.0)), ("f64", dict(num_species=3, channels=32, r_max=3.5))):
-        a, b, ls = model_jobs(dt, **kw)
+    for dt, kind, kw in (("f32", "mace", {}), ("f64", "mace", dict(num_species=3, channels=32, r_max=3.5)),
+                         ("f32", "nequip", dict(num_species=2, channels=64, lmax=2, sh_lmax=2, num_layers=4, r_max=4.0))):
+        a, b, ls = model_jobs(dt, kind, **kw)
         jobs += a
         stc_jobs += b
         sh_jobs.append((ls, torch.float32 if dt == "f32" else torch.float64, True, "component"))
