@@ -59,14 +59,36 @@ def default_tuning(spec: U1DSpec, direction: str) -> Tuning:
                 return Tuning(ct=128, groups=2, stages=6, min_blocks=1, vec=2, pipes=1)
             return Tuning(ct=128, groups=1, stages=6, min_blocks=2, vec=2, pipes=2)
         if f32:
-            return Tuning(ct=ct, groups=2 if big else 1, stages=8, min_blocks=1 if big else 3)
+            groups = 2 if big else 1
+            pipes = max(1, 4 // (groups * (ct // 32)))       # four consumer warps per CTA
+            stages = 6
+            per_pipe = 256 + stages * _stage_bytes(spec, ct, 0)
+            return Tuning(ct=ct, groups=groups, stages=stages, pipes=pipes,
+                          min_blocks=max(1, min(3 if not big else 2, _SMEM_BUDGET // (pipes * per_pipe))))
         return Tuning(ct=ct, groups=1, stages=4, min_blocks=2)
     if f32 and spec.u % 128 == 0:
         return Tuning(ct=128, groups=1, stages=3, min_blocks=1 if big else 2, vec=2, pipes=2)
     if f32:
-        return Tuning(ct=ct, groups=1, stages=3, min_blocks=2 if big else 3)
+        pipes = max(1, 4 // (ct // 32))
+        extra = (ct // 32) * spec.y_segs * 4
+        per_pipe = 256 + 3 * _stage_bytes(spec, ct, extra) + spec.out_segs * ct * 4
+        fit = max(1, _SMEM_BUDGET // per_pipe)                 # pipelines one SM can hold
+        if fit < 2 * pipes:                                    # not room for two CTAs: one CTA with all of them
+            return Tuning(ct=ct, groups=1, stages=3, pipes=min(fit, 4), min_blocks=1)
+        return Tuning(ct=ct, groups=1, stages=3, pipes=pipes, min_blocks=max(1, min(3, fit // pipes)))
     return Tuning(ct=ct, groups=1, stages=3, min_blocks=2)
 
+
+_SMEM_BUDGET = 220 * 1024
+
+
+def _stage_bytes(spec: U1DSpec, ct: int, extra: int) -> int:
+    """Shared memory of one ring stage (mirrors the layout constants of u1d_pipeline.cuh)."""
+    e = spec.elem_bytes
+    w = 0 if spec.w_shared else spec.w_segs * ct * e
+    x = spec.x_segs * ct * e
+    y = spec.y_segs * ct * e if spec.y_vec else (spec.y_segs * e + 15) // 16 * 16
+    return (w + x + y + 32 + extra + 127) // 128 * 128
 
 def _cfg(spec: U1DSpec, tun: Tuning, extra_bytes: int, ncons_warps: int, emit_empty: bool = True) -> str:
     b = lambda v: "true" if v else "false"
