@@ -226,7 +226,28 @@ def model_bench(args, dev, rank, dist, n_boxes: int):
     if dist is not None:
         tm = t.clone(); dist.all_reduce(tm, op=dist.ReduceOp.MAX); ms = float(tm[0])
         ts = t.clone(); dist.all_reduce(ts, op=dist.ReduceOp.SUM); atoms = float(ts[1])
-    return {"metric": "MACE atom-steps/s (energy + forces)", "value": atoms * k / (ms * 1e-3), "unit": "atom-steps/s",
+    # end to end through the model call: pinned host positions / species / edge lists in, energies and forces out
+    hb = model_inputs(n_boxes, rank, torch.float32, "cpu")[1]
+    hp = {kk: v.pin_memory() for kk, v in hb.items()}
+    def e2e_step():
+        dd = {kk: v.to(dev, non_blocking=True) for kk, v in hp.items()}
+        o = model(dd["pos"], dd["species"], dd["src"], dd["dst"], dd["shift"], dd["graph"], b.n_graphs)
+        return o["energy"].cpu(), o["forces"].cpu()
+    e2e_step()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(k):
+        en, fo = e2e_step()
+    torch.cuda.synchronize()
+    te = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    h2d = sum(v.numel() * v.element_size() for v in hp.values())
+    e2e = {"value": atoms * k / float(te[0]), "unit": "atom-steps/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": int(en.numel() * 4 + fo.numel() * 4)}
+    return {"metric": "MACE atom-steps/s (energy + forces)", "value": atoms * k / (ms * 1e-3), "unit": "atom-steps/s", "e2e": e2e,
             "ms_per_step": ms / k, "steps": k, "atoms": int(atoms), "edges_per_gpu": b.n_edges,
             "config": "config 1: 2 layers, 128x0e+128x1o, SH l<=3, correlation 3, 8 Bessel x p=5 envelope, 64-64-64 SiLU radial MLP, FP32",
             "energy_finite": bool(torch.isfinite(out["energy"]).all()), "forces_finite": bool(torch.isfinite(out["forces"]).all())}
