@@ -5,7 +5,7 @@
 
 One step = one forward + one backward (grad_w, grad_x, grad_y) of the fused
 gather / tensor-product / scatter operator over one synthetic batch.  Default
-workload: the interaction of BASELINE config 1 -- 64 periodic boxes x 192 atoms
+workload: the interaction of benchmark configuration 1 -- 64 periodic boxes x 192 atoms
 (cutoff 5 A, ~52 neighbours), hidden 128x0e+128x1o (x) SH l<=3 -> all paths l<=3,
 FP32, per-edge weights materialised.  With N > 1 every rank processes its own
 batch of whole structures (no data-path collective): weak scaling.
@@ -162,7 +162,7 @@ def model_inputs(n_boxes: int, seed: int, dtype, device):
 
 
 def halo_model_bench(args, dev, rank, world, dist):
-    """BASELINE config 3: NequIP-style network (64 x {0e,0o,1e,1o,2e,2o}, SH l <= 2, 4 gated interaction
+    """benchmark configuration 3: NequIP-style network (64 x {0e,0o,1e,1o,2e,2o}, SH l <= 2, 4 gated interaction
     layers, FP32) on one periodic cube of 20,000 atoms (cutoff 4 A), partitioned by receiver range
     with a halo exchange per layer: strong scaling."""
     from fasteq_b200.graph import large_box
@@ -201,7 +201,7 @@ def halo_model_bench(args, dev, rank, world, dist):
 
 
 def model_bench(args, dev, rank, dist, n_boxes: int):
-    """Energy + forces of the synthetic MACE-style model of BASELINE config 1 (FP32): atom-steps/s."""
+    """Energy + forces of the synthetic MACE-style model of benchmark configuration 1 (FP32): atom-steps/s."""
     from fasteq_b200.nn.mace_style import MACEStyleModel
     torch.manual_seed(0)
     model = MACEStyleModel().to(dev)
@@ -254,7 +254,7 @@ def model_bench(args, dev, rank, dist, n_boxes: int):
 
 
 def operator_extras(args, dev):
-    """Standalone timings of the other two operators of the path (BASELINE config 4 asks for the
+    """Standalone timings of the other two operators of the path (benchmark configuration 4 asks for the
     SymmetricContraction on 200k nodes; SO3Linear at config 1's node count)."""
     from fasteq_b200.descriptors import linear, symmetric_contraction
     from fasteq_b200.ops import fast_equi_linear, fast_stc_uniform1d_jit
@@ -284,7 +284,7 @@ def operator_extras(args, dev):
         o = fast_stc_uniform1d_jit(x1, x0, i0, coeffs, paths, idx, d.out_segs)
         torch.autograd.grad(o, x1, r)
     t_fb = timed(fb)
-    lens = (d.paths != -1).sum(1) - 1                       # multiplications + add per path (SURVEY: flops = B*U*sum L_p)
+    lens = (d.paths != -1).sum(1) - 1                       # multiplications + add per path: flops = B * U * sum of path lengths
     flops = float(B) * U * float(lens.sum())
     byts = 4.0 * (B * d.x1_segs * U + B * d.out_segs * U + 10 * d.x0_segs * U) + 4 * B
     out["stc_200k"] = {"nodes": B, "paths": d.num_paths, "fwd_ms": t_f * 1e3, "fwd_bwd_ms": t_fb * 1e3, "nodes_per_s_fwd": B / t_f,

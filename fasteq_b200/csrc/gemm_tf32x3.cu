@@ -242,20 +242,23 @@ struct AsCfg {
   static constexpr int A_BYTES = BM * BK * 4;
   static constexpr int B_BYTES = AS_BN * BK * 4;
   static constexpr int RING = (KB <= 2) ? AS_RING : 2;
-  static constexpr int SMEM_BYTES = KB * 2 * A_BYTES + RING * 2 * B_BYTES + 1024 + 1024;
+  static constexpr int STORE_BYTES = 4 * 2 * 4096;    // per epilogue warp: two 32 x 32 FP32 slabs for the TMA stores
+  static constexpr int SMEM_BYTES = KB * 2 * A_BYTES + RING * 2 * B_BYTES + STORE_BYTES + 1024 + 1024;
 };
 
 template <int KB>
 __global__ void __launch_bounds__(NT, 1)
 gemm_tf32x3_as_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBhi,
-                      const __grid_constant__ CUtensorMap tmBlo, float* __restrict__ C, long long M, int N, int K, int* status) {
+                      const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmC, long long M, int N, int K,
+                      int* status) {
   using C_ = AsCfg<KB>;
   constexpr int RING = C_::RING;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* a_base = smem;                                   // [KB][hi 16 KB | lo 16 KB]
   unsigned char* b_base = smem + KB * 2 * C_::A_BYTES;            // [RING][hi 16 KB | lo 16 KB]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(b_base + RING * 2 * C_::B_BYTES);
+  unsigned char* store_base = b_base + RING * 2 * C_::B_BYTES;    // [4 warps][2 slabs][32 rows x 128 B], 1024-aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(store_base + C_::STORE_BYTES);
   uint64_t* a_full = bars;            // 1
   uint64_t* a_split = bars + 1;       // 4 warps
   uint64_t* b_full = bars + 2;        // [RING]
@@ -350,14 +353,16 @@ gemm_tf32x3_as_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     __syncwarp();
     if (lane == 0) mbar_arrive(a_split);
     const int quarter = warp & 3;
-    const long long row = m0 + quarter * 32 + lane;
-    float* crow = C + (size_t)(row < M ? row : 0) * (size_t)N;
+    // this warp's 32 rows leave through its own pair of staging slabs: registers -> swizzled shared
+    // memory -> one 32 x 32 TMA store per column chunk (full 128-byte lines, clipped at the edges of C)
+    unsigned char* slab = store_base + (size_t)quarter * 2 * 4096;
+    int chunk_no = 0;
     for (int nt = 0; nt < n_tiles; ++nt) {
       const int buf = nt & 1;
       mbar_wait(&acc_full[buf], ((uint32_t)nt >> 1) & 1u, status);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-      for (int c = 0; c < AS_BN / 32; ++c) {
+      for (int c = 0; c < AS_BN / 32; ++c, ++chunk_no) {
         uint32_t r[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * AS_BN + c * 32);
         asm volatile(
@@ -370,23 +375,33 @@ gemm_tf32x3_as_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             : "r"(taddr)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < M) {
+        unsigned char* sl = slab + (size_t)(chunk_no & 1) * 4096;
+        // the slab used two chunks ago must have been read by its store
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const int n = nt * AS_BN + c * 32 + j;
-            if (n + 3 < N) {
-              *reinterpret_cast<float4*>(crow + n) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                                 __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-            } else {
-              for (int e = 0; e < 4; ++e) if (n + e < N) crow[n + e] = __uint_as_float(r[j + e]);
-            }
+        for (int j = 0; j < 8; ++j) {
+          // SWIZZLE_128B: 16-byte chunk j of row `lane` sits at chunk position j ^ (lane & 7)
+          *reinterpret_cast<float4*>(sl + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+              make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int col0 = nt * AS_BN + c * 32;
+          const long long row0 = m0 + quarter * 32;
+          if (col0 < N && row0 < M) {
+            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                         ::"l"(&tmC), "r"(col0), "r"((int)row0), "r"(0), "r"(smem_u32(sl)) : "memory");
           }
+          bulk_commit();
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
+    if (lane == 0) bulk_wait_read<0>();   // the staging slabs must outlive their stores
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -472,14 +487,14 @@ int launch(const TcTable& tab, const float* A, long long M, int a_rows, int K, c
 }
 
 template <int KB>
-static int launch_as_kb(const CUtensorMap& ma, const CUtensorMap& mbh, const CUtensorMap& mbl, float* C, long long M, int N, int K,
-                        cudaStream_t s) {
+static int launch_as_kb(const CUtensorMap& ma, const CUtensorMap& mbh, const CUtensorMap& mbl, const CUtensorMap& mc, long long M, int N,
+                        int K, cudaStream_t s) {
   int* st = nullptr;
   cudaError_t e = cudaGetSymbolAddress((void**)&st, g_tc_status);
   if (e != cudaSuccess) return cuda_fail(e);
   e = cudaFuncSetAttribute(gemm_tf32x3_as_kernel<KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, AsCfg<KB>::SMEM_BYTES);
   if (e != cudaSuccess) return cuda_fail(e);
-  gemm_tf32x3_as_kernel<KB><<<(unsigned)((M + BM - 1) / BM), NT, AsCfg<KB>::SMEM_BYTES, s>>>(ma, mbh, mbl, C, M, N, K, st);
+  gemm_tf32x3_as_kernel<KB><<<(unsigned)((M + BM - 1) / BM), NT, AsCfg<KB>::SMEM_BYTES, s>>>(ma, mbh, mbl, mc, M, N, K, st);
   e = cudaGetLastError();
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }
@@ -491,13 +506,14 @@ int launch_a_stationary(const float* A, long long M, int K, const float* Bt, int
   cudaError_t e = cudaMallocAsync((void**)&split, (size_t)nw * 2 * sizeof(float), s);
   if (e != cudaSuccess) return cuda_fail(e);
   split_weights_kernel<<<(unsigned)((nw + 255) / 256 < 1024 ? (nw + 255) / 256 : 1024), 256, 0, s>>>(Bt, split, split + nw, nw);
-  alignas(64) CUtensorMap ma, mbh, mbl;
+  alignas(64) CUtensorMap ma, mbh, mbl, mc;
   int rc = make_map(&ma, A, (uint64_t)K, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, BK, 1, BM);
+  if (rc == FASTEQ_OK) rc = make_map(&mc, C, (uint64_t)N, (uint64_t)M, 1, (uint64_t)N, (uint64_t)N * M, 32, 32, 1);
   if (rc == FASTEQ_OK) rc = make_map(&mbh, split, (uint64_t)K, (uint64_t)N, 1, (uint64_t)K, (uint64_t)N * K, BK, AS_BN, 1);
   if (rc == FASTEQ_OK) rc = make_map(&mbl, split + nw, (uint64_t)K, (uint64_t)N, 1, (uint64_t)K, (uint64_t)N * K, BK, AS_BN, 1);
   if (rc == FASTEQ_OK) {
     const int kb = (K + BK - 1) / BK;
-    rc = kb <= 2 ? launch_as_kb<2>(ma, mbh, mbl, C, M, N, K, s) : launch_as_kb<4>(ma, mbh, mbl, C, M, N, K, s);
+    rc = kb <= 2 ? launch_as_kb<2>(ma, mbh, mbl, mc, M, N, K, s) : launch_as_kb<4>(ma, mbh, mbl, mc, M, N, K, s);
   }
   cudaFreeAsync(split, s);
   return rc;

@@ -101,7 +101,7 @@ def periodic_radius_graph_cells(pos: np.ndarray, side: float, cutoff: float):
 
 
 def large_box(n_atoms: int = 20000, side: float = 58.5, cutoff: float = 4.0, n_species: int = 2, seed: int = 0) -> Batch:
-    """BASELINE config 3 data: one periodic cube, atoms sorted along a space-filling order of the
+    """benchmark configuration 3 data: one periodic cube, atoms sorted along a space-filling order of the
     cells so that contiguous node ranges are spatially compact (small halos)."""
     rng = np.random.default_rng(seed)
     pos = rng.uniform(0.0, side, size=(n_atoms, 3))
@@ -134,7 +134,7 @@ def make_boxes(n_boxes: int, atoms, side, cutoff: float, n_species: int, seed: i
 
 
 def config1_batch(n_boxes: int = 64, seed: int = 0) -> Batch:
-    """BASELINE config 1 data: periodic cubic boxes of side 12.4 A, 192 atoms, 4 species, cutoff 5 A."""
+    """benchmark configuration 1 data: periodic cubic boxes of side 12.4 A, 192 atoms, 4 species, cutoff 5 A."""
     return make_boxes(n_boxes, 192, 12.4, 5.0, 4, seed)
 
 

@@ -1,4 +1,4 @@
-"""Synthetic MACE-style model for the BASELINE model configurations (energy + forces).
+"""Synthetic MACE-style model for the benchmark's model configurations (energy + forces).
 
 Architecture (configuration 1): species embedding -> ``num_layers`` x { SO3Linear (up),
 ChannelwiseTensorProduct with SH(l <= 3) edge attributes and radial-MLP weights + scatter-sum,

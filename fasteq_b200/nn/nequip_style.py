@@ -1,4 +1,4 @@
-"""Synthetic NequIP-style model for BASELINE configuration 3 (energy + forces).
+"""Synthetic NequIP-style model for benchmark configuration 3 (energy + forces).
 
 Hidden features ``C x (0e+0o+1e+1o+2e+2o)``, edge attributes SH(l <= 2), ``num_layers`` interaction
 blocks of { SO3Linear, ChannelwiseTensorProduct + scatter-sum with radial-MLP weights, SO3Linear to the

@@ -8,7 +8,7 @@ from .codegen.u1d_common import make_spec
 from .descriptors import channelwise_tensor_product, full_channelwise_instructions
 from .irreps import Irreps
 
-# (irreps_in1, SH lmax, lmax_out, dtypes): BASELINE configs and the test / smoke signatures
+# (irreps_in1, SH lmax, lmax_out, dtypes): benchmark configurations and the test / smoke signatures
 STANDARD_CWTP = [
     ("128x0e+128x1o+128x2e", 3, 3, ("f32", "f64")),   # config 0
     ("128x0e+128x1o", 3, 3, ("f32",)),                # config 1 interaction

@@ -1,7 +1,7 @@
 """Generate golden vectors from the e3nn 0.5.6 sources vendored in the reference tree.
 
-Run where the reference is mounted:  python tests/golden/make_golden.py
-Writes tests/golden/e3nn_golden.npz (float64).  The e3nn sources are imported in
+Run where the reference tree is available:  python tests/golden/make_golden.py <reference-root>
+(or set FASTEQ_REFERENCE).  Writes tests/golden/e3nn_golden.npz (float64).  The e3nn sources are imported in
 place from the reference's model bundle; the one missing dependency
 (opt_einsum_fx, an einsum-order optimiser) is replaced by an identity stub.
 """
@@ -13,7 +13,9 @@ import types
 import numpy as np
 import torch
 
-REF = os.environ.get("FASTEQ_REFERENCE", "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FASTEQ_REFERENCE")
+if not REF:
+    raise SystemExit("usage: make_golden.py <reference-root>  (the FastEq source tree)")
 bundle = glob.glob(os.path.join(REF, "test/nequip_allegro_test/NequIP_OAM_R_4.5*nequip"))[0]
 sys.path.insert(0, bundle)
 stub = types.ModuleType("opt_einsum_fx")

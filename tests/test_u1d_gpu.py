@@ -76,7 +76,7 @@ def _tp(in1, lmax_sh, lmax_out):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 def test_config0_forward_backward(dtype):
-    """BASELINE config 0: 128x0e+128x1o+128x2e (x) SH l<=3 -> all paths l<=3, 512 nodes, 4096 dst-sorted edges."""
+    """benchmark configuration 0: 128x0e+128x1o+128x2e (x) SH l<=3 -> all paths l<=3, 512 nodes, 4096 dst-sorted edges."""
     d, paths = _tp("128x0e+128x1o+128x2e", 3, 3)
     _run_case(lambda dt: d.meta(dt, "cuda"), paths, d.coeff_list, (d.w_seg_num, d.x_seg_num, d.y_seg_num, d.out_seg_num),
               128, 512, 4096, dtype)
