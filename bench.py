@@ -226,6 +226,22 @@ def model_bench(args, dev, rank, dist, n_boxes: int):
     if dist is not None:
         tm = t.clone(); dist.all_reduce(tm, op=dist.ReduceOp.MAX); ms = float(tm[0])
         ts = t.clone(); dist.all_reduce(ts, op=dist.ReduceOp.SUM); atoms = float(ts[1])
+    # the same evaluation replayed from a CUDA graph (fixed neighbour list, new positions each step)
+    graphed_ms = None
+    try:
+        from fasteq_b200.nn.graphed import GraphedEnergyForces
+        ge = GraphedEnergyForces(model, d["pos"], d["species"], d["src"], d["dst"], d["shift"], d["graph"], b.n_graphs)
+        ge(d["pos"]); torch.cuda.synchronize()
+        ev0.record()
+        for _ in range(k):
+            ge(d["pos"])
+        ev1.record(); torch.cuda.synchronize()
+        tg = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        graphed_ms = float(tg[0]) / k
+    except Exception as exc:   # report, never fail the benchmark over the optional replay path
+        graphed_ms = f"capture failed: {type(exc).__name__}: {str(exc)[:120]}"
     # end to end through the model call: pinned host positions / species / edge lists in, energies and forces out
     hb = model_inputs(n_boxes, rank, torch.float32, "cpu")[1]
     hp = {kk: v.pin_memory() for kk, v in hb.items()}
@@ -248,6 +264,8 @@ def model_bench(args, dev, rank, dist, n_boxes: int):
     e2e = {"value": atoms * k / float(te[0]), "unit": "atom-steps/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": int(en.numel() * 4 + fo.numel() * 4)}
     return {"metric": "MACE atom-steps/s (energy + forces)", "value": atoms * k / (ms * 1e-3), "unit": "atom-steps/s", "e2e": e2e,
+            "cuda_graph_replay": ({"ms_per_step": graphed_ms, "value": atoms / (graphed_ms * 1e-3), "unit": "atom-steps/s"}
+                                  if isinstance(graphed_ms, float) else graphed_ms),
             "ms_per_step": ms / k, "steps": k, "atoms": int(atoms), "edges_per_gpu": b.n_edges,
             "config": "config 1: 2 layers, 128x0e+128x1o, SH l<=3, correlation 3, 8 Bessel x p=5 envelope, 64-64-64 SiLU radial MLP, FP32",
             "energy_finite": bool(torch.isfinite(out["energy"]).all()), "forces_finite": bool(torch.isfinite(out["forces"]).all())}
