@@ -41,7 +41,8 @@ template <int BN> struct Cfg {
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
   static constexpr int STAGES = (BN <= 64) ? 4 : 3;     // ring depth that fits the 227 KB of one CTA
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* barriers */ + 1024 /* alignment slack */;
+  static constexpr int STORE_BYTES = 4 * 2 * 4096;     // per epilogue warp: two 32 x 32 FP32 slabs for the TMA stores
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + 1024 /* barriers */ + 1024 /* alignment slack */;
 };
 
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
@@ -77,14 +78,15 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
 template <int BN>
 __global__ void __launch_bounds__(NT, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                   const __grid_constant__ TcTable tab, float* __restrict__ C, long long M, int c_rows_per_b, int N, int K,
+                   const __grid_constant__ CUtensorMap tmC, const __grid_constant__ TcTable tab, long long M, int N, int K,
                    int* status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using C_ = Cfg<BN>;
   constexpr int STAGES = C_::STAGES;
   unsigned char* stage_base = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C_::STAGE_BYTES);
+  unsigned char* store_base = smem + STAGES * C_::STAGE_BYTES;     // [4 warps][2 slabs][32 rows x 128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(store_base + C_::STORE_BYTES);
   uint64_t* full_raw = bars;                 // [STAGES] TMA landed
   uint64_t* full_split = bars + STAGES;      // [STAGES] hi / lo tiles ready
   uint64_t* empty = bars + 2 * STAGES;       // [STAGES] MMAs have consumed the stage
@@ -192,8 +194,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     mbar_wait(acc_full, 0u, status);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int quarter = warp & 3;
-    const long long row = m0 + quarter * 32 + lane;
-    float* crow = C + ((size_t)(row < M ? row : 0) * c_rows_per_b + tab.group_c_row[g] + t) * (size_t)N;
+    // registers -> swizzled staging slab of this warp -> one 32 x 32 TMA store per column chunk
+    unsigned char* slab = store_base + (size_t)quarter * 2 * 4096;
+    const int c_row = tab.group_c_row[g] + t;
 #pragma unroll 1
     for (int c = 0; c < BN / 32; ++c) {
       uint32_t r[32];
@@ -208,19 +211,27 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           : "r"(taddr)
           : "memory");
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (row < M) {
+      unsigned char* sl = slab + (size_t)(c & 1) * 4096;
+      if (lane == 0) bulk_wait_read<1>();
+      __syncwarp();
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const int n = n0 + c * 32 + j;
-          if (n + 3 < N) {
-            *reinterpret_cast<float4*>(crow + n) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                               __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-          } else {
-            for (int e = 0; e < 4; ++e) if (n + e < N) crow[n + e] = __uint_as_float(r[j + e]);
-          }
+      for (int j = 0; j < 8; ++j) {
+        *reinterpret_cast<float4*>(sl + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+            make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int col0 = n0 + c * 32;
+        const long long row0 = m0 + quarter * 32;
+        if (col0 < N && row0 < M) {
+          asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                       ::"l"(&tmC), "r"(col0), "r"(c_row), "r"((int)row0), "r"(smem_u32(sl)) : "memory");
         }
+        bulk_commit();
       }
     }
+    if (lane == 0) bulk_wait_read<0>();
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -461,7 +472,7 @@ bool supported(long long M, int a_rows, int K, int P, int N, int c_rows, const v
 }
 
 template <int BN>
-static int launch_bn(const TcTable& tab, const CUtensorMap& ma, const CUtensorMap& mb, float* C, long long M, int c_rows, int N,
+static int launch_bn(const TcTable& tab, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, long long M, int N,
                      int K, cudaStream_t s) {
   int* st = nullptr;
   cudaError_t e = cudaGetSymbolAddress((void**)&st, g_tc_status);
@@ -469,7 +480,7 @@ static int launch_bn(const TcTable& tab, const CUtensorMap& ma, const CUtensorMa
   e = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
   if (e != cudaSuccess) return cuda_fail(e);
   dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)((N + BN - 1) / BN), (unsigned)tab.n_items);
-  gemm_tf32x3_kernel<BN><<<grid, NT, Cfg<BN>::SMEM_BYTES, s>>>(ma, mb, tab, C, M, c_rows, N, K, st);
+  gemm_tf32x3_kernel<BN><<<grid, NT, Cfg<BN>::SMEM_BYTES, s>>>(ma, mb, mc, tab, M, N, K, st);
   e = cudaGetLastError();
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }
@@ -478,12 +489,14 @@ int launch(const TcTable& tab, const float* A, long long M, int a_rows, int K, c
            int c_rows, cudaStream_t s) {
   if (tab.n_items < 1 || tab.n_items > 65535) return FASTEQ_UNSUPPORTED;
   const int BN = N <= 64 ? 64 : 128;
-  alignas(64) CUtensorMap ma, mb;
+  alignas(64) CUtensorMap ma, mb, mc;
   int rc = make_map(&ma, A, (uint64_t)K, (uint64_t)a_rows, (uint64_t)M, (uint64_t)K, (uint64_t)a_rows * K, BK, 1, BM);
   if (rc != FASTEQ_OK) return rc;
   rc = make_map(&mb, Bt, (uint64_t)K, (uint64_t)N, (uint64_t)P, (uint64_t)K, (uint64_t)N * K, BK, (uint32_t)BN, 1);
   if (rc != FASTEQ_OK) return rc;
-  return BN == 64 ? launch_bn<64>(tab, ma, mb, C, M, c_rows, N, K, s) : launch_bn<128>(tab, ma, mb, C, M, c_rows, N, K, s);
+  rc = make_map(&mc, C, (uint64_t)N, (uint64_t)c_rows, (uint64_t)M, (uint64_t)N, (uint64_t)c_rows * N, 32, 1, 32);
+  if (rc != FASTEQ_OK) return rc;
+  return BN == 64 ? launch_bn<64>(tab, ma, mb, mc, M, N, K, s) : launch_bn<128>(tab, ma, mb, mc, M, N, K, s);
 }
 
 template <int KB>
