@@ -366,7 +366,7 @@ def config_dict(workload, inp, n_gpus):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="config1_cwtp", choices=sorted(WORKLOADS))
@@ -438,7 +438,7 @@ def main():
 
     # ---- per-kernel timing for the roofline (rank 0's kernels, CUDA events on the launch stream)
     call = u1d._Call(w, x, y, inp_idx, out_idx, meta)
-    k = max(3, args.steps)
+    k = min(max(3, args.steps), 10)     # each kernel timed alone, a short burst (the peak it is compared with is a burst figure)
     def timed(fn):
         fn(); torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
