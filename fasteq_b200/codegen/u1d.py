@@ -41,7 +41,9 @@ def default_tuning(spec: U1DSpec, direction: str) -> Tuning:
 
     With 128-channel FP32 tiles both directions use packed two-channel arithmetic; the forward keeps
     the receiver row in registers (two thread groups split the output segments when there are too
-    many for one thread), the backward runs two pipelines per CTA.  Other shapes: one channel per thread."""
+    many for one thread), the backward runs two pipelines per CTA.  Other shapes: one channel per
+    thread, as many pipelines per CTA as give four consumer warps, residency from the shared-memory
+    footprint."""
     f32 = spec.dtype == "f32"
     cap = 128 if f32 else 64
     ct = min((spec.u + 31) // 32 * 32, cap)
@@ -51,32 +53,29 @@ def default_tuning(spec: U1DSpec, direction: str) -> Tuning:
                 ct = cand
                 break
     big = spec.out_segs > 64
+    e = spec.elem_bytes
     if direction == "fwd":
         if f32 and spec.u % 128 == 0:
-            # packed arithmetic; a small row fits one thread group (two pipelines fill the four
-            # sub-partitions), a large row is split over two groups
             if big:
                 return Tuning(ct=128, groups=2, stages=6, min_blocks=1, vec=2, pipes=1)
             return Tuning(ct=128, groups=1, stages=6, min_blocks=2, vec=2, pipes=2)
-        if f32:
-            groups = 2 if big else 1
-            pipes = max(1, 4 // (groups * (ct // 32)))       # four consumer warps per CTA
-            stages = 6
-            per_pipe = 256 + stages * _stage_bytes(spec, ct, 0)
-            return Tuning(ct=ct, groups=groups, stages=stages, pipes=pipes,
-                          min_blocks=max(1, min(3 if not big else 2, _SMEM_BUDGET // (pipes * per_pipe))))
-        return Tuning(ct=ct, groups=1, stages=4, min_blocks=2)
+        groups = 2 if big else 1
+        pipes = max(1, 4 // (groups * (ct // 32)))           # four consumer warps per CTA
+        stages = 6 if f32 else 4
+        per_pipe = 256 + stages * _stage_bytes(spec, ct, 0)
+        fit = max(1, _SMEM_BUDGET // per_pipe)
+        if fit < 2 * pipes:
+            return Tuning(ct=ct, groups=groups, stages=stages, pipes=max(1, min(fit, pipes)), min_blocks=1)
+        return Tuning(ct=ct, groups=groups, stages=stages, pipes=pipes, min_blocks=max(1, min(2 if (big or not f32) else 3, fit // pipes)))
     if f32 and spec.u % 128 == 0:
         return Tuning(ct=128, groups=1, stages=3, min_blocks=1 if big else 2, vec=2, pipes=2)
-    if f32:
-        pipes = max(1, 4 // (ct // 32))
-        extra = (ct // 32) * spec.y_segs * 4
-        per_pipe = 256 + 3 * _stage_bytes(spec, ct, extra) + spec.out_segs * ct * 4
-        fit = max(1, _SMEM_BUDGET // per_pipe)                 # pipelines one SM can hold
-        if fit < 2 * pipes:                                    # not room for two CTAs: one CTA with all of them
-            return Tuning(ct=ct, groups=1, stages=3, pipes=min(fit, 4), min_blocks=1)
-        return Tuning(ct=ct, groups=1, stages=3, pipes=pipes, min_blocks=max(1, min(3, fit // pipes)))
-    return Tuning(ct=ct, groups=1, stages=3, min_blocks=2)
+    pipes = max(1, 4 // (ct // 32))
+    extra = (ct // 32) * spec.y_segs * e
+    per_pipe = 256 + 3 * _stage_bytes(spec, ct, extra) + (spec.out_segs * ct * e + 127) // 128 * 128
+    fit = max(1, _SMEM_BUDGET // per_pipe)                     # pipelines one SM can hold
+    if fit < 2 * pipes:                                        # no room for two CTAs: one CTA with all of them
+        return Tuning(ct=ct, groups=1, stages=3, pipes=min(fit, 4), min_blocks=1)
+    return Tuning(ct=ct, groups=1, stages=3, pipes=pipes, min_blocks=max(1, min(3 if f32 else 2, fit // pipes)))
 
 
 _SMEM_BUDGET = 220 * 1024
