@@ -45,37 +45,50 @@ def default_tuning(spec: U1DSpec, direction: str) -> Tuning:
     thread, as many pipelines per CTA as give four consumer warps, residency from the shared-memory
     footprint."""
     f32 = spec.dtype == "f32"
-    cap = 128 if f32 else 64
-    ct = min((spec.u + 31) // 32 * 32, cap)
-    if spec.u > ct and spec.u % ct != 0:
-        for cand in (128, 96, 64, 32):
-            if cand <= ct and spec.u % cand == 0:
-                ct = cand
-                break
-    big = spec.out_segs > 64
+    packed = f32 and spec.u % 64 == 0
     e = spec.elem_bytes
+    if packed:
+        ct = 128 if spec.u % 128 == 0 else 64
+        vec, wpg = 2, ct // 64                        # consumer warps per thread group
+    else:
+        cap = 128 if f32 else 64
+        ct = min((spec.u + 31) // 32 * 32, cap)
+        if spec.u > ct and spec.u % ct != 0:
+            for cand in (128, 96, 64, 32):
+                if cand <= ct and spec.u % cand == 0:
+                    ct = cand
+                    break
+        vec, wpg = 1, ct // 32
+    big = spec.out_segs > 64
     if direction == "fwd":
-        if f32 and spec.u % 128 == 0:
-            if big:
-                return Tuning(ct=128, groups=2, stages=6, min_blocks=1, vec=2, pipes=1)
-            return Tuning(ct=128, groups=1, stages=6, min_blocks=2, vec=2, pipes=2)
         groups = 2 if big else 1
-        pipes = max(1, 4 // (groups * (ct // 32)))           # four consumer warps per CTA
+        pipes = max(1, 4 // (groups * wpg))                    # four consumer warps per CTA
         stages = 6 if f32 else 4
         per_pipe = 256 + stages * _stage_bytes(spec, ct, 0)
-        fit = max(1, _SMEM_BUDGET // per_pipe)
-        if fit < 2 * pipes:
-            return Tuning(ct=ct, groups=groups, stages=stages, pipes=max(1, min(fit, pipes)), min_blocks=1)
-        return Tuning(ct=ct, groups=groups, stages=stages, pipes=pipes, min_blocks=max(1, min(2 if (big or not f32) else 3, fit // pipes)))
-    if f32 and spec.u % 128 == 0:
-        return Tuning(ct=128, groups=1, stages=3, min_blocks=1 if big else 2, vec=2, pipes=2)
-    pipes = max(1, 4 // (ct // 32))
-    extra = (ct // 32) * spec.y_segs * e
-    per_pipe = 256 + 3 * _stage_bytes(spec, ct, extra) + (spec.out_segs * ct * e + 127) // 128 * 128
-    fit = max(1, _SMEM_BUDGET // per_pipe)                     # pipelines one SM can hold
-    if fit < 2 * pipes:                                        # no room for two CTAs: one CTA with all of them
-        return Tuning(ct=ct, groups=1, stages=3, pipes=min(fit, 4), min_blocks=1)
-    return Tuning(ct=ct, groups=1, stages=3, pipes=pipes, min_blocks=max(1, min(3 if f32 else 2, fit // pipes)))
+        fit = max(1, _SMEM_BUDGET // per_pipe)                 # pipelines one SM can hold
+        if fit < pipes:
+            pipes = fit
+        if packed:
+            residency = 1 if big else 2
+        else:
+            residency = 2 if (big or not f32) else 3
+        return Tuning(ct=ct, groups=groups, stages=stages, pipes=pipes, vec=vec, min_blocks=max(1, min(residency, fit // pipes)))
+    pipes = max(1, 4 // wpg)
+    extra = wpg * spec.y_segs * e
+    go_bytes = (spec.out_segs * ct * e + 127) // 128 * 128
+    stages = 3
+    per_pipe = 256 + stages * _stage_bytes(spec, ct, extra) + go_bytes
+    if pipes * per_pipe > _SMEM_BUDGET:
+        stages = 2
+        per_pipe = 256 + stages * _stage_bytes(spec, ct, extra) + go_bytes
+    fit = max(1, _SMEM_BUDGET // per_pipe)
+    if fit < pipes:
+        pipes = fit
+    if packed:
+        residency = 1 if big else 2
+    else:
+        residency = 1 if big else (3 if f32 else 2)
+    return Tuning(ct=ct, groups=1, stages=stages, pipes=pipes, vec=vec, min_blocks=max(1, min(residency, fit // pipes)))
 
 
 _SMEM_BUDGET = 220 * 1024
