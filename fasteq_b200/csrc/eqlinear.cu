@@ -270,6 +270,138 @@ int launch_tensorcore(const fasteq_eqlinear_problem* p, bool dgrad, const void* 
   return rc;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Weight gradient: per path a [u, v] = X^T G product reduced over R = batch * rows GEMM rows.
+// grid = (u tiles * v tiles, paths, splits); a CTA reduces its share of R into a 64 x 64 tile
+// (chunks of BK rows summed on their own first, like the forward), writes it to partial[split] and
+// a second kernel adds the splits in a fixed order and applies the coefficient.
+struct WgradTable {
+  int in_row[kMaxPaths], out_row[kMaxPaths], rows[kMaxPaths];
+  double coeff[kMaxPaths];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(NT) eqlinear_wgrad_kernel(const __grid_constant__ WgradTable tab, const T* __restrict__ X,
+                                                            const T* __restrict__ G, T* __restrict__ partial, long long batch,
+                                                            int in_rows, int out_rows, int u, int v, int num_paths,
+                                                            long long rows_per_split) {
+  __shared__ T sX[BK][BM + 4];
+  __shared__ T sG[BK][BN + 4];
+  const int q = blockIdx.y;
+  const int v_tiles = (v + BN - 1) / BN;
+  const int m0 = (blockIdx.x / v_tiles) * BM, n0 = (blockIdx.x % v_tiles) * BN;
+  const int gi = tab.rows[q];
+  const long long R = batch * gi;
+  const long long r_begin = (long long)blockIdx.z * rows_per_split;
+  const long long r_end = r_begin + rows_per_split < R ? r_begin + rows_per_split : R;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  T acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = T(0);
+  const int lc = threadIdx.x % 64, lr0 = threadIdx.x / 64;    // 64 consecutive threads read 64 consecutive channels
+  for (long long r0 = r_begin; r0 < r_end; r0 += BK) {
+#pragma unroll
+    for (int e = 0; e < BK / 4; ++e) {
+      const int k = e * 4 + lr0;
+      const long long r = r0 + k;
+      T xv = T(0), gv = T(0);
+      if (r < r_end) {
+        const long long b = r / gi;
+        const int t = (int)(r % gi);
+        if (m0 + lc < u) xv = X[((size_t)b * in_rows + tab.in_row[q] + t) * (size_t)u + m0 + lc];
+        if (n0 + lc < v) gv = G[((size_t)b * out_rows + tab.out_row[q] + t) * (size_t)v + n0 + lc];
+      }
+      sX[k][lc] = xv; sG[k][lc] = gv;
+    }
+    __syncthreads();
+    T part[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) part[i][j] = T(0);
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      T a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = sX[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = sG[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) part[i][j] += a[i] * b[j];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] += part[i][j];
+    __syncthreads();
+  }
+  T* dst = partial + ((size_t)blockIdx.z * num_paths + q) * (size_t)u * v;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= u) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < v) dst[(size_t)m * v + n] = acc[i][j];
+    }
+  }
+}
+
+template <typename T>
+__global__ void eqlinear_wgrad_reduce_kernel(const __grid_constant__ WgradTable tab, const T* __restrict__ partial,
+                                             T* __restrict__ gw, int splits, int num_paths, long long uv) {
+  const long long total = (long long)num_paths * uv;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    T s = T(0);
+    for (int z = 0; z < splits; ++z) s += partial[(size_t)z * total + i];
+    gw[i] = (T)tab.coeff[i / uv] * s;
+  }
+}
+
+template <typename T>
+int launch_wgrad(const fasteq_eqlinear_problem* p, const void* x, const void* go, void* gw, cudaStream_t s) {
+  if (!p || p->num_paths < 1 || p->num_paths > kMaxPaths || p->u < 1 || p->v < 1 || p->batch < 0) return FASTEQ_INVALID;
+  if (!p->in_row || !p->out_row || !p->rows || !p->coeff || !gw) return FASTEQ_INVALID;
+  WgradTable tab;
+  int max_rows = 1;
+  for (int q = 0; q < p->num_paths; ++q) {
+    if (p->rows[q] < 1 || p->in_row[q] < 0 || p->in_row[q] + p->rows[q] > p->in_rows || p->out_row[q] < 0 ||
+        p->out_row[q] + p->rows[q] > p->out_rows)
+      return FASTEQ_INVALID;
+    tab.in_row[q] = p->in_row[q]; tab.out_row[q] = p->out_row[q]; tab.rows[q] = p->rows[q]; tab.coeff[q] = p->coeff[q];
+    max_rows = std::max(max_rows, p->rows[q]);
+  }
+  const long long uv = (long long)p->u * p->v, total = uv * p->num_paths;
+  if (p->batch == 0) {
+    cudaError_t e = cudaMemsetAsync(gw, 0, (size_t)total * sizeof(T), s);
+    return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
+  }
+  if (!x || !go) return FASTEQ_INVALID;
+  const int tiles = ((p->u + BM - 1) / BM) * ((p->v + BN - 1) / BN);
+  const long long R = p->batch * max_rows;
+  // enough CTAs for a few waves of the SMs, but no split shorter than 256 GEMM rows
+  long long splits = std::max<long long>(1, 1184 / ((long long)tiles * p->num_paths));
+  splits = std::min<long long>(splits, std::max<long long>(1, R / 256));
+  splits = std::min<long long>(splits, 1024);
+  const long long rows_per_split = ((R + splits - 1) / splits + BK - 1) / BK * BK;
+  T* partial = nullptr;
+  cudaError_t e = cudaMallocAsync((void**)&partial, (size_t)splits * total * sizeof(T), s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  dim3 grid((unsigned)tiles, (unsigned)p->num_paths, (unsigned)splits);
+  eqlinear_wgrad_kernel<T><<<grid, NT, 0, s>>>(tab, (const T*)x, (const T*)go, partial, p->batch, p->in_rows, p->out_rows,
+                                               p->u, p->v, p->num_paths, rows_per_split);
+  const unsigned rb = (unsigned)std::min<long long>((total + 255) / 256, 2048);
+  eqlinear_wgrad_reduce_kernel<T><<<rb, 256, 0, s>>>(tab, partial, (T*)gw, (int)splits, p->num_paths, uv);
+  e = cudaGetLastError();
+  cudaFreeAsync(partial, s);
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
+}
+
 int dispatch(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const void* a, void* c, fasteq_stream_t stream) {
   if (!p) return FASTEQ_INVALID;
   switch (p->precision) {
@@ -295,4 +427,13 @@ extern "C" int fasteq_eqlinear_forward(const fasteq_eqlinear_problem* p, const v
 extern "C" int fasteq_eqlinear_dgrad(const fasteq_eqlinear_problem* p, const void* w, const void* grad_out, void* grad_x,
                                      fasteq_stream_t stream) {
   return dispatch(p, true, w, grad_out, grad_x, stream);
+}
+
+extern "C" int fasteq_eqlinear_wgrad(const fasteq_eqlinear_problem* p, const void* x, const void* grad_out, void* grad_w,
+                                     fasteq_stream_t stream) {
+  if (!p) return FASTEQ_INVALID;
+  if (p->precision == FASTEQ_EQLIN_FP64) return launch_wgrad<double>(p, x, grad_out, grad_w, (cudaStream_t)stream);
+  if (p->precision == FASTEQ_EQLIN_TF32X3 || p->precision == FASTEQ_EQLIN_FP32)
+    return launch_wgrad<float>(p, x, grad_out, grad_w, (cudaStream_t)stream);
+  return FASTEQ_INVALID;
 }

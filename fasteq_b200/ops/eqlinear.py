@@ -5,7 +5,8 @@ uniform ``uv,iu,iv`` SO3Linear).
 elements (viewed ``[P, U, V]``), the result is ``[B, J*V]``.  Precision routing as in the reference
 (fasteq/ops/eqlinear.py:24-41): float64 -> FP64; float32 -> ``compute_precision`` ``None`` /
 ``"tf32"`` / ``"tf32x3"`` (error bound of 3xTF32) or ``"fp32"``; anything else raises ``ValueError``.
-``w`` receives no gradient (the reference returns ``None`` for it, eqlinear_runtime.py:104).
+The reference returns no gradient for ``w`` (eqlinear_runtime.py:104); here ``w`` gets one when it
+requires grad (``fasteq_eqlinear_wgrad``, FP32 / FP64 FMA arithmetic), so the mixing weights can be trained.
 Unsupported descriptors raise; there is no fallback path.
 """
 from __future__ import annotations
@@ -126,6 +127,7 @@ def _core():
     if not _core_ready:
         lib.fasteq_eqlinear_forward.argtypes = [C.POINTER(_Problem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         lib.fasteq_eqlinear_dgrad.argtypes = [C.POINTER(_Problem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        lib.fasteq_eqlinear_wgrad.argtypes = [C.POINTER(_Problem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         _core_ready = True
     return lib
 
@@ -170,26 +172,40 @@ class _EqLinearFn(torch.autograd.Function):
         with torch.cuda.device(x.device):
             _cabi.check(lib.fasteq_eqlinear_forward(C.byref(prob), w3.data_ptr(), x3.data_ptr(), out.data_ptr(),
                                                     torch.cuda.current_stream(x.device).cuda_stream), lib, "fasteq_eqlinear_forward")
-        ctx.save_for_backward(w3)
-        ctx.geom, ctx.precision, ctx.batch = geom, precision, batch
+        ctx.save_for_backward(w3, x3 if ctx.needs_input_grad[0] else None)
+        ctx.geom, ctx.precision, ctx.batch, ctx.w_shape = geom, precision, batch, w.shape
         return out.reshape(batch, J * v)
 
     @staticmethod
     def backward(ctx, grad_out):
-        (w3,) = ctx.saved_tensors
+        w3, x3 = ctx.saved_tensors
         mapping, coeff, u, v, I, J = ctx.geom
         g3 = grad_out.reshape(ctx.batch, J, v).contiguous()
-        dx = torch.empty((ctx.batch, I, u), dtype=g3.dtype, device=g3.device)
         lib = _core()
         prob = _make_problem([(m[0], m[1], q, m[3]) for q, m in enumerate(mapping)], coeff, u, v, I, J, ctx.batch, ctx.precision)
+        dx = dw = None
         with torch.cuda.device(g3.device):
-            _cabi.check(lib.fasteq_eqlinear_dgrad(C.byref(prob), w3.data_ptr(), g3.data_ptr(), dx.data_ptr(),
-                                                  torch.cuda.current_stream(g3.device).cuda_stream), lib, "fasteq_eqlinear_dgrad")
-        return None, dx.reshape(ctx.batch, I * u), None, None
+            stream = torch.cuda.current_stream(g3.device).cuda_stream
+            if ctx.needs_input_grad[1]:
+                dx = torch.empty((ctx.batch, I, u), dtype=g3.dtype, device=g3.device)
+                _cabi.check(lib.fasteq_eqlinear_dgrad(C.byref(prob), w3.data_ptr(), g3.data_ptr(), dx.data_ptr(), stream),
+                            lib, "fasteq_eqlinear_dgrad")
+                dx = dx.reshape(ctx.batch, I * u)
+            if ctx.needs_input_grad[0]:
+                dw = torch.empty((len(mapping), u, v), dtype=g3.dtype, device=g3.device)
+                _cabi.check(lib.fasteq_eqlinear_wgrad(C.byref(prob), x3.data_ptr(), g3.data_ptr(), dw.data_ptr(), stream),
+                            lib, "fasteq_eqlinear_wgrad")
+                wps = [m[2] for m in mapping]
+                if wps != list(range(len(wps))):      # block q of the table is block wps[q] of the caller's tensor
+                    full = torch.empty_like(dw)
+                    full[torch.tensor(wps, device=dw.device)] = dw
+                    dw = full
+                dw = dw.reshape(ctx.w_shape)
+        return dw, dx, None, None
 
 
 def fast_equi_linear(descriptor, w, x, *, compute_precision=None):
-    """Forward and grad_x for the uniform uv/iu/iv eqlinear operator."""
+    """Forward, grad_x and grad_w for the uniform uv/iu/iv eqlinear operator."""
     precision = _resolve_precision(x, w, compute_precision)
     geom = _descriptor_problem(descriptor)
     return _EqLinearFn.apply(w, x, geom, precision)

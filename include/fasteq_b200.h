@@ -202,6 +202,14 @@ int fasteq_eqlinear_forward(const fasteq_eqlinear_problem* p /* host */, const v
  * (the reference exposes grad_x only, eqlinear_runtime.py:86-104). grad_x is fully overwritten. */
 int fasteq_eqlinear_dgrad(const fasteq_eqlinear_problem* p /* host */, const void* w, const void* grad_out,
                           void* grad_x, fasteq_stream_t stream);
+/* grad_w[q] = coeff[q] * sum_b sum_{t < rows[q]} x[b, in_row[q]+t, :]^T grad_out[b, out_row[q]+t, :]   ([u, v] per path).
+ * Needed to train the mixing weights.  The reference's public operator returns no weight gradient
+ * (eqlinear_runtime.py:104); its FP32 back-end keeps a reduction kernel for one
+ * (fasteq/cuda/src/eqlinear/backends/fp32/reduce_dw.cu:12).  FP32 (also for FASTEQ_EQLIN_TF32X3) or FP64
+ * FMA arithmetic, two deterministic stages: per-chunk partial sums in a stream-ordered temporary, then
+ * their reduction.  grad_w [num_paths, u, v] is fully overwritten. */
+int fasteq_eqlinear_wgrad(const fasteq_eqlinear_problem* p /* host */, const void* x, const void* grad_out,
+                          void* grad_w, fasteq_stream_t stream);
 
 /* ------------------------------------------------------------------------- *
  * Gate non-linearity (e3nn nn.Gate) on ir_mul rows [segments, u]: input = scalar segments, one gate

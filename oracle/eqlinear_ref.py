@@ -56,3 +56,16 @@ def eqlinear_dgrad(grad_out, w, mapping, cg, in_rows_total):
     for (ir, orow, wp, rows), c in zip(mapping, cg):
         gx[:, ir:ir + rows, :] += float(c) * (grad_out[:, orow:orow + rows, :].astype(np.float64) @ w[wp].astype(np.float64).T)
     return gx.astype(grad_out.dtype)
+
+
+def eqlinear_wgrad(x, grad_out, mapping, cg, num_weight_blocks):
+    """grad_w[wp] = cg * sum_b sum_t x[b, in+t, :]^T grad_out[b, out+t, :] -> [P, U, V] (float64).
+    The adjoint of ``eqlinear_forward`` in ``w``; the reference's operator returns none
+    (fasteq/ops/auto_schedule/eqlinear_runtime.py:104), so this follows from the forward formula."""
+    U, V = x.shape[2], grad_out.shape[2]
+    gw = np.zeros((num_weight_blocks, U, V), dtype=np.float64)
+    for (ir, orow, wp, rows), c in zip(mapping, cg):
+        xs = x[:, ir:ir + rows, :].astype(np.float64).reshape(-1, U)
+        gs = grad_out[:, orow:orow + rows, :].astype(np.float64).reshape(-1, V)
+        gw[wp] += float(c) * (xs.T @ gs)
+    return gw

@@ -94,3 +94,19 @@ def test_front_end_geometry_and_errors():
         eq._descriptor_problem(d2)
     with pytest.raises(RuntimeError, match="no CPU path"):
         eq.fast_equi_linear(linear("4x0e", "4x0e"), torch.zeros(16), torch.zeros(3, 4))
+
+
+def test_oracle_weight_gradient_is_the_adjoint_of_the_forward():
+    """<r, forward(x, w + dw) - forward(x, w)> == <wgrad(x, r), dw> exactly (the forward is linear in w)."""
+    import numpy as np
+    from oracle import eqlinear_ref
+    rng = np.random.default_rng(3)
+    i_dims, u, v, B = [1, 1, 3, 3, 5], 6, 4, 9
+    m = eqlinear_ref.mapping_from_i_dims(i_dims)
+    cg = [0.3 + 0.1 * q for q in range(len(i_dims))]
+    J = eqlinear_ref.out_rows(i_dims)
+    x = rng.standard_normal((B, sum(i_dims), u)); dw = rng.standard_normal((len(i_dims), u, v))
+    r = rng.standard_normal((B, J, v))
+    lhs = float((r * eqlinear_ref.eqlinear_forward(x, dw, m, cg, J)).sum())
+    rhs = float((eqlinear_ref.eqlinear_wgrad(x, r, m, cg, len(i_dims)) * dw).sum())
+    assert abs(lhs - rhs) <= 1e-12 * max(1.0, abs(lhs))

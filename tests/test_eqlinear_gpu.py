@@ -95,3 +95,38 @@ def test_e3nn_style_descriptor_with_shared_outputs_and_odd_sizes():
         (gx,) = torch.autograd.grad(out.sum(), xd)
         ref_gx = eqlinear_ref.eqlinear_dgrad(np.ones_like(ref), w.numpy().reshape(-1, u, v), mapping, coeff, I)
         assert _rel_fro(gx.cpu().double().numpy().reshape(ref_gx.shape), ref_gx) <= tol
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float64, 1e-12), (torch.float32, 2e-6)])
+@pytest.mark.parametrize("shape,batch", [("MEDIUM_P2", 2944), ("SMALL_P1", 77), ("LARGE_P3", 700)])
+def test_weight_gradient(shape, batch, dtype, tol):
+    """grad_w against the float64 adjoint of the forward formula (two-stage deterministic reduction)."""
+    from fasteq_b200.ops.eqlinear import fast_equi_linear
+    x, w, cg, i_dims, u = _make(shape, batch, dtype)
+    m, x3, w3, ref = _ref(x, w, i_dims, cg, u)
+    wd = w.cuda().requires_grad_(True)
+    xd = x.cuda().requires_grad_(True)
+    out = fast_equi_linear(_FakeDescriptor(i_dims, u, u, cg), wd, xd, compute_precision="fp32" if dtype == torch.float32 else None)
+    r = torch.randn(out.shape, generator=torch.Generator().manual_seed(2), dtype=torch.float64).to(dtype)
+    gw, gx = torch.autograd.grad(out, (wd, xd), r.cuda())
+    ref_gw = eqlinear_ref.eqlinear_wgrad(x3, r.double().numpy().reshape(ref.shape), m, cg, len(i_dims))
+    assert gw.shape == w.shape
+    assert _rel_fro(gw.cpu().double().numpy().reshape(ref_gw.shape), ref_gw) <= tol
+    gw2, = torch.autograd.grad(fast_equi_linear(_FakeDescriptor(i_dims, u, u, cg), wd, xd.detach()), wd, r.cuda())
+    assert torch.equal(gw, gw2)          # fixed reduction order: bit-identical across calls
+
+
+def test_weight_gradient_with_permuted_weight_blocks():
+    from fasteq_b200.ops.eqlinear import fast_equi_linear, _descriptor_problem
+    d = linear("24x0e+24x0e+24x1o+24x2e", "40x0e+40x1o+40x1o+40x2e")
+    mapping, coeff, u, v, I, J = _descriptor_problem(d)
+    g = torch.Generator().manual_seed(6)
+    B = 201
+    x = torch.randn(B, I * u, generator=g, dtype=torch.float64)
+    w = torch.randn(len(d.paths) * u * v, generator=g, dtype=torch.float64)
+    r = torch.randn(B, J * v, generator=g, dtype=torch.float64)
+    wd = w.cuda().requires_grad_(True)
+    out = fast_equi_linear(d, wd, x.cuda())
+    (gw,) = torch.autograd.grad(out, wd, r.cuda())
+    ref = eqlinear_ref.eqlinear_wgrad(x.numpy().reshape(B, I, u), r.numpy().reshape(B, J, v), mapping, coeff, len(d.paths))
+    assert _rel_fro(gw.cpu().numpy().reshape(ref.shape), ref) <= 1e-12
