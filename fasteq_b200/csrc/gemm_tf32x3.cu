@@ -11,13 +11,16 @@
 // keeps the relative error near 2^-21 (the reference's tf32x3 scheme,
 // fasteq/cuda/src/eqlinear/backends/tf32/shape_plan.cu:109-113: three MMAs, no lo*lo term).
 //
-// Structure of one CTA (one 128 x BN output tile of one item):
+// Structure of one CTA (persistent: one CTA per SM walks 128 x BN output tiles round-robin, the stage ring
+// and two TMEM accumulators carry over from tile to tile so that loads, splits, MMAs and stores of
+// neighbouring tiles overlap):
 //   warp 0       : TMA producer -- 3-D tiled loads (SWIZZLE_128B) of the raw A and Bt k-blocks
 //   warp 1       : allocates TMEM, issues tcgen05.mma (kind::tf32, M = 128, N = BN, K = 8) from one lane,
 //                  releases ring stages and signals the epilogue with tcgen05.commit
 //   warps 2..5   : split each raw k-block into hi / lo tiles in place (the swizzle is position
-//                  preserving, so no layout knowledge is needed), then read the accumulator with
-//                  tcgen05.ld and store the tile
+//                  preserving, so no layout knowledge is needed)
+//   warps 6..9   : read a finished accumulator with tcgen05.ld and store the tile through swizzled
+//                  staging slabs and TMA stores
 // Every mbarrier wait is bounded (about two seconds), after which a status word is set and the
 // waiter falls through; TMEM is always released before the CTA ends.  No multicast, no clusters.
 #include <cstdio>
@@ -34,7 +37,8 @@ namespace fasteq {
 namespace tc {
 
 constexpr int BM = 128, BK = 32;
-constexpr int NT = 192;   // 6 warps
+constexpr int NT = 192;     // A-stationary kernel: 6 warps
+constexpr int NT_P = 320;   // persistent grouped kernel: 10 warps
 
 template <int BN> struct Cfg {
   static constexpr int A_BYTES = BM * BK * 4;          // 16 KB
@@ -75,11 +79,32 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// one output tile of the persistent loop
+struct Tile {
+  int g, t, seg0, n_kb, n0;
+  long long m0;
+};
+
+__device__ __forceinline__ Tile decode_tile(const TcTable& tab, long long tile, int m_tiles, int n_tiles, int kb_per_seg, int BN) {
+  Tile r;
+  const int mx = (int)(tile % m_tiles);
+  const long long rest = tile / m_tiles;
+  const int ny = (int)(rest % n_tiles);
+  const int z = (int)(rest / n_tiles);
+  int g = 0;
+  while (g + 1 < tab.n_groups && z >= tab.item_first[g + 1]) ++g;
+  r.g = g; r.t = z - tab.item_first[g];
+  r.seg0 = tab.group_first[g];
+  r.n_kb = (tab.group_first[g + 1] - r.seg0) * kb_per_seg;
+  r.m0 = (long long)mx * BM; r.n0 = ny * BN;
+  return r;
+}
+
 template <int BN>
-__global__ void __launch_bounds__(NT, 1)
+__global__ void __launch_bounds__(NT_P, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ TcTable tab, long long M, int N, int K,
-                   int* status) {
+                   long long n_tiles_total, int m_tiles, int n_tiles, int* status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using C_ = Cfg<BN>;
@@ -90,27 +115,20 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   uint64_t* full_raw = bars;                 // [STAGES] TMA landed
   uint64_t* full_split = bars + STAGES;      // [STAGES] hi / lo tiles ready
   uint64_t* empty = bars + 2 * STAGES;       // [STAGES] MMAs have consumed the stage
-  uint64_t* acc_full = bars + 3 * STAGES;    // accumulator complete
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
+  uint64_t* acc_full = bars + 3 * STAGES;    // [2] accumulator complete
+  uint64_t* acc_empty = acc_full + 2;        // [2] accumulator read back by the four epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // which (group, t) this CTA works on
-  int g = 0;
-  while (g + 1 < tab.n_groups && (int)blockIdx.z >= tab.item_first[g + 1]) ++g;
-  const int t = (int)blockIdx.z - tab.item_first[g];
-  const int seg0 = tab.group_first[g], nseg = tab.group_first[g + 1] - seg0;
   const int kb_per_seg = (K + BK - 1) / BK;
-  const int n_kb = nseg * kb_per_seg;
-  const long long m0 = (long long)blockIdx.x * BM;
-  const int n0 = blockIdx.y * BN;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_raw[s], 1); mbar_init(&full_split[s], 4); mbar_init(&empty[s], 1); }
-    mbar_init(acc_full, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     mbar_fence_init();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -121,16 +139,19 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      for (int kb = 0; kb < n_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1u;
-        mbar_wait(&empty[s], ph ^ 1u, status);
-        unsigned char* st = stage_base + (size_t)s * C_::STAGE_BYTES;
-        const int seg = seg0 + kb / kb_per_seg;
-        const int k0 = (kb % kb_per_seg) * BK;
-        mbar_arrive_expect_tx(&full_raw[s], (uint32_t)(C_::A_BYTES + C_::B_BYTES));
-        tma_load_3d(st, &tmA, k0, tab.path_a_row[seg] + t, (int)m0, &full_raw[s]);
-        tma_load_3d(st + 2 * C_::A_BYTES, &tmB, k0, n0, tab.path_w[seg], &full_raw[s]);
+      int it = 0;
+      for (long long tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x) {
+        const Tile tl = decode_tile(tab, tile, m_tiles, n_tiles, kb_per_seg, BN);
+        for (int kb = 0; kb < tl.n_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          mbar_wait(&empty[s], ((it / STAGES) & 1u) ^ 1u, status);
+          unsigned char* st = stage_base + (size_t)s * C_::STAGE_BYTES;
+          const int seg = tl.seg0 + kb / kb_per_seg;
+          const int k0 = (kb % kb_per_seg) * BK;
+          mbar_arrive_expect_tx(&full_raw[s], (uint32_t)(C_::A_BYTES + C_::B_BYTES));
+          tma_load_3d(st, &tmA, k0, tab.path_a_row[seg] + tl.t, (int)tl.m0, &full_raw[s]);
+          tma_load_3d(st + 2 * C_::A_BYTES, &tmB, k0, tl.n0, tab.path_w[seg], &full_raw[s]);
+        }
       }
     }
   } else if (warp == 1) {
@@ -138,98 +159,120 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     if (lane == 0) {
       // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-      for (int kb = 0; kb < n_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1u;
-        mbar_wait(&full_split[s], ph, status);
+      int it = 0;
+      uint32_t lt = 0;
+      for (long long tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++lt) {
+        const Tile tl = decode_tile(tab, tile, m_tiles, n_tiles, kb_per_seg, BN);
+        const uint32_t buf = lt & 1u;
+        mbar_wait(&acc_empty[buf], ((lt >> 1) & 1u) ^ 1u, status);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_hi = smem_u32(stage_base + (size_t)s * C_::STAGE_BYTES);
-        const uint32_t a_lo = a_hi + C_::A_BYTES;
-        const uint32_t b_hi = a_hi + 2 * C_::A_BYTES;
-        const uint32_t b_lo = b_hi + C_::B_BYTES;
+        const uint32_t tmem_d = tmem_base + buf * (uint32_t)BN;
+        for (int kb = 0; kb < tl.n_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          mbar_wait(&full_split[s], (it / STAGES) & 1u, status);
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_hi = smem_u32(stage_base + (size_t)s * C_::STAGE_BYTES);
+          const uint32_t a_lo = a_hi + C_::A_BYTES;
+          const uint32_t b_hi = a_hi + 2 * C_::A_BYTES;
+          const uint32_t b_lo = b_hi + C_::B_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < BK / 8; ++kk) {
-          const uint32_t off = kk * 32;   // 8 TF32 values = 32 bytes along K inside the 128-byte swizzle row
-          mma_tf32(tmem_base, make_desc(a_lo + off), make_desc(b_hi + off), idesc, (kb | kk) ? 1u : 0u);
-          mma_tf32(tmem_base, make_desc(a_hi + off), make_desc(b_lo + off), idesc, 1u);
-          mma_tf32(tmem_base, make_desc(a_hi + off), make_desc(b_hi + off), idesc, 1u);
+          for (int kk = 0; kk < BK / 8; ++kk) {
+            const uint32_t off = kk * 32;   // 8 TF32 values = 32 bytes along K inside the 128-byte swizzle row
+            mma_tf32(tmem_d, make_desc(a_lo + off), make_desc(b_hi + off), idesc, (kb | kk) ? 1u : 0u);
+            mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_lo + off), idesc, 1u);
+            mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_hi + off), idesc, 1u);
+          }
+          mma_commit(&empty[s]);            // the stage may be refilled once these MMAs have read it
         }
-        mma_commit(&empty[s]);            // the stage may be refilled once these MMAs have read it
+        mma_commit(&acc_full[buf]);
       }
-      mma_commit(acc_full);
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ split raw tiles into hi / lo
+    const int tid = threadIdx.x - 64;     // 0..127
+    int it = 0;
+    for (long long tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x) {
+      const Tile tl = decode_tile(tab, tile, m_tiles, n_tiles, kb_per_seg, BN);
+      for (int kb = 0; kb < tl.n_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        mbar_wait(&full_raw[s], (it / STAGES) & 1u, status);
+        unsigned char* st = stage_base + (size_t)s * C_::STAGE_BYTES;
+        float4* a_hi = reinterpret_cast<float4*>(st);
+        float4* a_lo = reinterpret_cast<float4*>(st + C_::A_BYTES);
+        float4* b_hi = reinterpret_cast<float4*>(st + 2 * C_::A_BYTES);
+        float4* b_lo = reinterpret_cast<float4*>(st + 2 * C_::A_BYTES + C_::B_BYTES);
+        auto split = [](float4 v, float4& hi, float4& lo) {
+          hi.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); lo.x = v.x - hi.x;
+          hi.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); lo.y = v.y - hi.y;
+          hi.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); lo.z = v.z - hi.z;
+          hi.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); lo.w = v.w - hi.w;
+        };
+#pragma unroll
+        for (int i = 0; i < C_::A_BYTES / 16 / 128; ++i) {
+          float4 hi, lo; split(a_hi[tid + i * 128], hi, lo);
+          a_hi[tid + i * 128] = hi; a_lo[tid + i * 128] = lo;
+        }
+#pragma unroll
+        for (int i = 0; i < C_::B_BYTES / 16 / 128; ++i) {
+          float4 hi, lo; split(b_hi[tid + i * 128], hi, lo);
+          b_hi[tid + i * 128] = hi; b_lo[tid + i * 128] = lo;
+        }
+        fence_async_smem();                 // generic-proxy writes -> visible to the tensor core's async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_split[s]);
+      }
     }
   } else {
-    // ------------------------------------------------------------------ split, then epilogue
-    const int tid = threadIdx.x - 64;     // 0..127
-    for (int kb = 0; kb < n_kb; ++kb) {
-      const int s = kb % STAGES;
-      const uint32_t ph = (kb / STAGES) & 1u;
-      mbar_wait(&full_raw[s], ph, status);
-      unsigned char* st = stage_base + (size_t)s * C_::STAGE_BYTES;
-      float4* a_hi = reinterpret_cast<float4*>(st);
-      float4* a_lo = reinterpret_cast<float4*>(st + C_::A_BYTES);
-      float4* b_hi = reinterpret_cast<float4*>(st + 2 * C_::A_BYTES);
-      float4* b_lo = reinterpret_cast<float4*>(st + 2 * C_::A_BYTES + C_::B_BYTES);
-      auto split = [](float4 v, float4& hi, float4& lo) {
-        hi.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); lo.x = v.x - hi.x;
-        hi.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); lo.y = v.y - hi.y;
-        hi.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); lo.z = v.z - hi.z;
-        hi.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); lo.w = v.w - hi.w;
-      };
-#pragma unroll
-      for (int i = 0; i < C_::A_BYTES / 16 / 128; ++i) {
-        float4 hi, lo; split(a_hi[tid + i * 128], hi, lo);
-        a_hi[tid + i * 128] = hi; a_lo[tid + i * 128] = lo;
-      }
-#pragma unroll
-      for (int i = 0; i < C_::B_BYTES / 16 / 128; ++i) {
-        float4 hi, lo; split(b_hi[tid + i * 128], hi, lo);
-        b_hi[tid + i * 128] = hi; b_lo[tid + i * 128] = lo;
-      }
-      fence_async_smem();                 // generic-proxy writes -> visible to the tensor core's async proxy
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&full_split[s]);
-    }
-    // epilogue: TMEM lane = tile row; warp w may touch lanes 32 * (w % 4) .. + 31
-    mbar_wait(acc_full, 0u, status);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // ------------------------------------------------------------------ epilogue (warps 6..9)
+    // TMEM lane = tile row; warp w may touch lanes 32 * (w % 4) .. + 31
     const int quarter = warp & 3;
     // registers -> swizzled staging slab of this warp -> one 32 x 32 TMA store per column chunk
     unsigned char* slab = store_base + (size_t)quarter * 2 * 4096;
-    const int c_row = tab.group_c_row[g] + t;
+    uint32_t lt = 0;
+    int chunk_no = 0;
+    for (long long tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++lt) {
+      const Tile tl = decode_tile(tab, tile, m_tiles, n_tiles, kb_per_seg, BN);
+      const uint32_t buf = lt & 1u;
+      mbar_wait(&acc_full[buf], (lt >> 1) & 1u, status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int c_row = tab.group_c_row[tl.g] + tl.t;
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
-      uint32_t r[32];
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32);
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-          : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-            "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-            "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-            "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-          : "r"(taddr)
-          : "memory");
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      unsigned char* sl = slab + (size_t)(c & 1) * 4096;
-      if (lane == 0) bulk_wait_read<1>();
-      __syncwarp();
+      for (int c = 0; c < BN / 32; ++c, ++chunk_no) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)BN + (uint32_t)(c * 32);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+              "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        unsigned char* sl = slab + (size_t)(chunk_no & 1) * 4096;
+        if (lane == 0) bulk_wait_read<1>();     // the slab used two chunks ago has been read by its store
+        __syncwarp();
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        *reinterpret_cast<float4*>(sl + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-            make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-      }
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        const int col0 = n0 + c * 32;
-        const long long row0 = m0 + quarter * 32;
-        if (col0 < N && row0 < M) {
-          asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
-                       ::"l"(&tmC), "r"(col0), "r"(c_row), "r"((int)row0), "r"(smem_u32(sl)) : "memory");
+        for (int j = 0; j < 8; ++j) {
+          *reinterpret_cast<float4*>(sl + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+              make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
         }
-        bulk_commit();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int col0 = tl.n0 + c * 32;
+          const long long row0 = tl.m0 + quarter * 32;
+          if (col0 < N && row0 < M) {
+            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                         ::"l"(&tmC), "r"(col0), "r"(c_row), "r"((int)row0), "r"(smem_u32(sl)) : "memory");
+          }
+          bulk_commit();
+        }
       }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
     if (lane == 0) bulk_wait_read<0>();
   }
@@ -237,7 +280,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
   }
 }
 
@@ -471,6 +514,13 @@ bool supported(long long M, int a_rows, int K, int P, int N, int c_rows, const v
   return true;
 }
 
+static int sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+  return n;
+}
+
 template <int BN>
 static int launch_bn(const TcTable& tab, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, long long M, int N,
                      int K, cudaStream_t s) {
@@ -479,8 +529,13 @@ static int launch_bn(const TcTable& tab, const CUtensorMap& ma, const CUtensorMa
   if (e != cudaSuccess) return cuda_fail(e);
   e = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
   if (e != cudaSuccess) return cuda_fail(e);
-  dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)((N + BN - 1) / BN), (unsigned)tab.n_items);
-  gemm_tf32x3_kernel<BN><<<grid, NT, Cfg<BN>::SMEM_BYTES, s>>>(ma, mb, mc, tab, M, N, K, st);
+  const long long m_tiles = (M + BM - 1) / BM;
+  const int n_tiles = (N + BN - 1) / BN;
+  const long long total = m_tiles * n_tiles * tab.n_items;
+  const int sms = sm_count();
+  if (sms < 1) return FASTEQ_CUDA_ERROR;
+  const unsigned grid = (unsigned)(total < sms ? total : sms);     // one persistent CTA per SM
+  gemm_tf32x3_kernel<BN><<<grid, NT_P, Cfg<BN>::SMEM_BYTES, s>>>(ma, mb, mc, tab, M, N, K, total, (int)m_tiles, n_tiles, st);
   e = cudaGetLastError();
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }

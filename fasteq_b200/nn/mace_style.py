@@ -53,12 +53,16 @@ class RadialMLP(torch.nn.Module):
 
 class InteractionLayer(torch.nn.Module):
     def __init__(self, irreps_in: Irreps, hidden: Irreps, sh_lmax: int, lmax_mid: int, num_species: int, num_basis: int,
-                 radial_hidden: List[int], correlation: int, avg_num_neighbors: float):
+                 radial_hidden: List[int], correlation: int, avg_num_neighbors: float, tp_parity: Optional[str] = "natural"):
         super().__init__()
         mul = irreps_in.uniform_mul()
         sh = Irreps.spherical_harmonics(sh_lmax)
         self.linear_up = SO3Linear(irreps_in, irreps_in)
-        irreps_tp, instr = full_channelwise_instructions(irreps_in, sh, lmax_mid)
+        # MACE keeps only the couplings whose output irrep is one of the target irreps, i.e. parity (-1)^l
+        # (mace/modules/irreps_tools.py tp_out_irreps_with_instructions; the reference's own operator bench
+        # applies the same filter, test/bench_tensor_product_uniform1d.py:64-68): 0e+1o x SH(l<=3) gives
+        # 10 weighted paths and 40 output rows instead of 13 / 55.
+        irreps_tp, instr = full_channelwise_instructions(irreps_in, sh, lmax_mid, parity_filter=tp_parity)
         self.conv_tp = ChannelwiseTensorProduct(irreps_in, sh, irreps_tp, instr)
         self.radial = RadialMLP(num_basis, radial_hidden, self.conv_tp.weight_numel)
         self.irreps_mid = Irreps([(mul, (l, (-1) ** l)) for l in range(lmax_mid + 1)])
@@ -82,7 +86,7 @@ class InteractionLayer(torch.nn.Module):
 class MACEStyleModel(torch.nn.Module):
     def __init__(self, num_species: int = 4, channels: int = 128, hidden_lmax: int = 1, sh_lmax: int = 3, lmax_mid: int = 3,
                  num_layers: int = 2, r_max: float = 5.0, num_basis: int = 8, radial_hidden=(64, 64, 64), correlation: int = 3,
-                 avg_num_neighbors: float = 52.0, envelope_p: int = 5):
+                 avg_num_neighbors: float = 52.0, envelope_p: int = 5, tp_parity: Optional[str] = "natural"):
         super().__init__()
         self.r_max, self.num_basis, self.envelope_p, self.channels = r_max, num_basis, envelope_p, channels
         hidden = Irreps([(channels, (l, (-1) ** l)) for l in range(hidden_lmax + 1)])
@@ -93,7 +97,7 @@ class MACEStyleModel(torch.nn.Module):
         irreps_in = Irreps([(channels, (0, 1))])
         for _ in range(num_layers):
             layers.append(InteractionLayer(irreps_in, hidden, sh_lmax, lmax_mid, num_species, num_basis, list(radial_hidden),
-                                           correlation, avg_num_neighbors))
+                                           correlation, avg_num_neighbors, tp_parity))
             irreps_in = hidden
         self.layers = torch.nn.ModuleList(layers)
         self.readouts = torch.nn.ParameterList(torch.nn.Parameter(torch.randn(channels) / math.sqrt(channels)) for _ in range(num_layers))

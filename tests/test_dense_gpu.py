@@ -1,0 +1,53 @@
+"""GPU parity of the 3xTF32 tensor-core dense layer (radial MLP) against float64 matmul: shapes of the
+config-1 radial MLP (8 -> 64 -> 64 -> 64 -> weight_numel), row counts that are not tile multiples,
+and enough row tiles that every persistent CTA walks several tiles."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a.double() - b).norm() / b.norm().clamp_min(1e-30))
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (1, 64, 8), (77, 64, 64), (128, 8, 64), (1000, 64, 1664), (513, 1664, 64), (300, 512, 64), (257, 128, 128),
+    (148 * 128 * 3 + 77, 64, 64), (148 * 128 * 2 + 5, 64, 8), (40000, 128, 128), (20000, 12, 20),
+])
+def test_dense_forward_matches_float64(M, N, K):
+    from fasteq_b200.ops.dense import dense, tensorcore_device_status
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g)
+    w = torch.randn(N, K, generator=g) / K ** 0.5
+    ref = x.double() @ w.double().t()
+    out = dense(x.cuda(), w.cuda())
+    assert out.shape == (M, N)
+    assert _rel(out.cpu(), ref) <= (2e-6 if K <= 128 else 2e-5), _rel(out.cpu(), ref)   # long K: the 3xTF32 bound of the reference (2e-5)
+    # element-wise too: a misplaced tile would hide in a norm
+    assert float((out.cpu().double() - ref).abs().max()) <= 2e-5 * float(ref.abs().max())
+    assert tensorcore_device_status() == 0
+
+
+def test_dense_gradients():
+    from fasteq_b200.ops.dense import dense
+    g = torch.Generator().manual_seed(3)
+    M, N, K = 148 * 128 + 300, 64, 64
+    x = torch.randn(M, K, generator=g)
+    w = torch.randn(N, K, generator=g) / 8
+    r = torch.randn(M, N, generator=g)
+    xd, wd = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+    gx, gw = torch.autograd.grad(dense(xd, wd), (xd, wd), r.cuda())
+    assert _rel(gx.cpu(), r.double() @ w.double()) <= 2e-6
+    assert _rel(gw.cpu(), r.double().t() @ x.double()) <= 1e-5
+
+
+def test_dense_leading_dimensions_and_fallback_dtypes():
+    from fasteq_b200.ops.dense import dense
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(5, 31, 8, generator=g, dtype=torch.float64)
+    w = torch.randn(64, 8, generator=g, dtype=torch.float64)
+    out = dense(x.cuda(), w.cuda())            # float64 goes through torch.matmul
+    assert out.shape == (5, 31, 64) and _rel(out.cpu(), x @ w.t()) <= 1e-14
+    out32 = dense(x.float().cuda(), w.float().cuda())
+    assert out32.shape == (5, 31, 64) and _rel(out32.cpu(), x @ w.t()) <= 2e-6
