@@ -32,6 +32,7 @@
 #include "core_common.h"
 #include "fasteq_device.cuh"
 #include "gemm_tf32x3.h"
+#include "tcgen05_util.cuh"
 
 namespace fasteq {
 namespace tc {
@@ -48,36 +49,6 @@ template <int BN> struct Cfg {
   static constexpr int STORE_BYTES = 4 * 2 * 4096;     // per epilogue warp: two 32 x 32 FP32 slabs for the TMA stores
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + 1024 /* barriers */ + 1024 /* alignment slack */;
 };
-
-__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
-      : "memory");
-}
-
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
-  // K-major, SWIZZLE_128B: rows of 128 bytes, 8-row groups 1024 bytes apart
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
-  d |= (uint64_t)1 << 16;                    // leading byte offset (unused for swizzled K-major), 16 B
-  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
-  d |= (uint64_t)1 << 46;                    // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
-  return d;
-}
-
-__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 // one output tile of the persistent loop
 struct Tile {
@@ -488,7 +459,7 @@ static PFN_cuTensorMapEncodeTiled get_encode() {
 }
 
 // 3-D FP32 tensor [d2][d1][d0] (d0 contiguous), box [b2][b1][b0], 128-byte swizzle, zero fill outside
-static int make_map(CUtensorMap* m, const float* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_elems,
+int make_map(CUtensorMap* m, const float* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_elems,
                     uint64_t stride2_elems, uint32_t b0, uint32_t b1, uint32_t b2) {
   PFN_cuTensorMapEncodeTiled enc = get_encode();
   if (!enc) return FASTEQ_INTERNAL;
@@ -618,5 +589,11 @@ extern "C" int fasteq_gemm_tf32x3(const void* A, const void* Bt, void* C, int64_
 
 extern "C" int fasteq_tensorcore_device_status(int32_t* code) {
   if (!code) return FASTEQ_INVALID;
-  return fasteq::tc::device_status(code);
+  int a = 0, b = 0;
+  int rc = fasteq::tc::device_status(&a);
+  if (rc != FASTEQ_OK) return rc;
+  rc = fasteq::chain::device_status(&b);
+  if (rc != FASTEQ_OK) return rc;
+  *code = a ? a : b;
+  return FASTEQ_OK;
 }

@@ -1,0 +1,432 @@
+// Hidden layers of the radial MLP (width 64, SiLU) as ONE kernel per direction, so that the per-edge
+// activations between the layers never leave the SM:
+//
+//   forward : b [E, nb] --W1 (CUDA cores)--> h1 = silu(z1) --W2 (tcgen05)--> h2 = silu(z2) --W3--> h3
+//             writes h_L [E, 64] and d_l = silu'(z_l) for the tensor-core layers (kept for the backward)
+//   backward: g = dE/dh_L;  g <- W_l^T (g * d_l) for l = L..2 (tcgen05);  gz1 = g * silu'(z1) with z1
+//             recomputed from b;  dE/db = W1^T gz1  [E, nb]
+//
+// The radial network of MACE / NequIP models is a small bias-free MLP on the radial basis
+// (.../nequip/nn/embedding/_edge.py:174-189 feeds it; the reference leaves the MLP to torch); here its
+// 64 x 64 layers run as 3xTF32 tensor-core products (same split as gemm_tf32x3.cu) chained through
+// shared memory and TMEM.
+//
+// One persistent CTA per SM walks tiles of 128 edges:
+//   warp 0    : loads the pre-split hidden weights once (TMA, SWIZZLE_128B), they stay resident
+//   warp 1    : issues the tcgen05.mma of a layer when the eight worker warps have written its operand
+//   warps 2-9 : workers; a thread owns half a row of the tile (TMEM lane = row, 32 of the 64 columns):
+//               it writes its part of the A operand (hi / lo, swizzled K-major) itself, reads the
+//               accumulator back with tcgen05.ld and applies SiLU / the stored derivative.  Rows of
+//               [E, 64] tensors enter and leave through per-warp 32 x 32 swizzled slabs and tiled TMA
+//               loads / stores, so that global traffic is made of full 128-byte lines.
+// Every mbarrier wait is bounded; a timeout sets a status word and the kernel drains.
+#include <cstdio>
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include "fasteq_b200.h"
+#include "core_common.h"
+#include "fasteq_device.cuh"
+#include "gemm_tf32x3.h"
+#include "tcgen05_util.cuh"
+
+namespace fasteq {
+namespace chain {
+
+using namespace fasteq::tc;
+
+constexpr int H = 64;                 // hidden width
+constexpr int BM = 128, BK = 32;
+constexpr int NT = 320;
+constexpr int N_WORKERS = 8;          // worker warps
+constexpr int MAX_TC = 2;             // tensor-core layers (hidden layers after the first)
+constexpr int W_LAYER_BYTES = 2 * 2 * H * BK * 4;    // [kb][hi | lo] of a 64 x 64 matrix: 32 KB
+constexpr int A_BYTES = 2 * 2 * BM * BK * 4;         // [kb][hi | lo] of a 128 x 64 tile: 64 KB
+constexpr int SLAB_BYTES = 32 * 128;                 // 32 rows x 32 FP32 columns
+constexpr int MAX_NB = 16;
+constexpr int SMEM_BYTES = MAX_TC * W_LAYER_BYTES + A_BYTES + N_WORKERS * 2 * SLAB_BYTES + H * MAX_NB * 4 + 1024 /* barriers */ +
+                           1024 /* alignment */;
+
+struct Args {
+  const float* basis;      // [M, nb]
+  const float* w1;         // [H, nb]
+  float* grad_basis;       // backward: dE/db [M, nb], zero-filled by the caller, accumulated with red.add
+  long long M;
+  int nb, n_tc;
+};
+
+__device__ __forceinline__ void silu_and_derivative(float z, float& h, float& d) {
+  const float s = __fdividef(1.0f, 1.0f + __expf(-z));
+  h = z * s;
+  d = s * (1.0f + z * (1.0f - s));
+}
+
+// 16-byte chunk c of row r of a 128-byte-row tile sits at chunk position c ^ (r & 7) (SWIZZLE_128B)
+__device__ __forceinline__ float4* swz(unsigned char* tile, int r, int c) {
+  return reinterpret_cast<float4*>(tile + r * 128 + ((c ^ (r & 7)) << 4));
+}
+
+// this thread's 32 values (columns 32 * half ..) -> row `row` of k-block `half` of the A operand
+__device__ __forceinline__ void write_operand(unsigned char* A, int half, int row, const float (&v)[32]) {
+  unsigned char* hi_tile = A + half * (2 * BM * BK * 4);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    float4 hi, lo;
+    split_tf32(v[4 * c + 0], hi.x, lo.x); split_tf32(v[4 * c + 1], hi.y, lo.y);
+    split_tf32(v[4 * c + 2], hi.z, lo.z); split_tf32(v[4 * c + 3], hi.w, lo.w);
+    *swz(hi_tile, row, c) = hi;
+    *swz(hi_tile + BM * BK * 4, row, c) = lo;
+  }
+}
+
+__device__ __forceinline__ void tma_store_block(const CUtensorMap* map, int col0, long long row0, int z, const void* slab) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+               ::"l"(map), "r"(col0), "r"((int)row0), "r"(z), "r"(smem_u32(slab)) : "memory");
+}
+
+// tmW: prepared weights; tmIO0 / tmIO1: forward = (h_L out, derivatives out), backward = (dE/dh_L in, derivatives in),
+// all [z][M][64] FP32 with 32 x 32 boxes
+template <int NB, bool BWD>
+__global__ void __launch_bounds__(NT, 1)
+radial_chain_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmIO0,
+                    const __grid_constant__ CUtensorMap tmIO1, const __grid_constant__ Args a, int* status) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* w_base = smem;                                   // [MAX_TC][kb][hi 8 KB | lo 8 KB]
+  unsigned char* a_base = smem + MAX_TC * W_LAYER_BYTES;          // [kb][hi 16 KB | lo 16 KB]
+  unsigned char* slab_base = a_base + A_BYTES;                    // [8 warps][2][4 KB]
+  float* w1s = reinterpret_cast<float*>(slab_base + N_WORKERS * 2 * SLAB_BYTES);   // [H][NB], zero padded
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(w1s) + H * MAX_NB * 4);
+  uint64_t* w_full = bars;            // 1
+  uint64_t* a_ready = bars + 1;       // the eight worker warps have written the operand
+  uint64_t* z_full = bars + 2;        // the accumulator is complete
+  uint64_t* slab_full = bars + 3;     // [8 warps][2] backward: a TMA load has landed in the slab
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 + 2 * N_WORKERS);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long n_tiles = (a.M + BM - 1) / BM;
+  const int n_tc = a.n_tc;
+
+  for (int i = threadIdx.x; i < H * NB; i += NT) {
+    const int j = i / NB, k = i % NB;
+    w1s[i] = k < a.nb ? a.w1[j * a.nb + k] : 0.f;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(w_full, 1);
+    mbar_init(a_ready, N_WORKERS);
+    mbar_init(z_full, 1);
+    for (int i = 0; i < 2 * N_WORKERS; ++i) mbar_init(&slab_full[i], 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, H);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0 && n_tc > 0) {
+      mbar_arrive_expect_tx(w_full, (uint32_t)(n_tc * W_LAYER_BYTES));
+      for (int l = 0; l < n_tc; ++l)
+        for (int kb = 0; kb < 2; ++kb)
+          for (int hl = 0; hl < 2; ++hl)
+            tma_load_3d(w_base + l * W_LAYER_BYTES + kb * (2 * H * BK * 4) + hl * (H * BK * 4), &tmW, kb * BK, 0, l * 2 + hl, w_full);
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_tc > 0) {
+      const uint32_t idesc = idesc_tf32_m128(H);
+      mbar_wait(w_full, 0u, status);
+      tc_fence_after();
+      uint32_t cnt = 0;
+      for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        for (int s = 0; s < n_tc; ++s) {
+          mbar_wait(a_ready, cnt & 1u, status);
+          ++cnt;
+          tc_fence_after();
+#pragma unroll
+          for (int kb = 0; kb < 2; ++kb) {
+            const uint32_t a_hi = smem_u32(a_base + kb * (2 * BM * BK * 4)), a_lo = a_hi + BM * BK * 4;
+            const uint32_t b_hi = smem_u32(w_base + s * W_LAYER_BYTES + kb * (2 * H * BK * 4)), b_lo = b_hi + H * BK * 4;
+#pragma unroll
+            for (int kk = 0; kk < BK / 8; ++kk) {
+              const uint32_t off = kk * 32;
+              mma_tf32(tmem_base, make_desc(a_lo + off), make_desc(b_hi + off), idesc, (kb | kk) ? 1u : 0u);
+              mma_tf32(tmem_base, make_desc(a_hi + off), make_desc(b_lo + off), idesc, 1u);
+              mma_tf32(tmem_base, make_desc(a_hi + off), make_desc(b_hi + off), idesc, 1u);
+            }
+          }
+          mma_commit(z_full);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ workers
+    const int wk = warp - 2;                          // 0..7
+    const int half = wk >> 2;                         // which 32 of the 64 columns
+    const int quarter = warp & 3;                     // the TMEM lanes this warp may read
+    const int trow = quarter * 32 + lane;             // row of the tile = TMEM lane
+    const uint32_t tmem_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 32);
+    unsigned char* slab0 = slab_base + wk * 2 * SLAB_BYTES;
+    unsigned char* slab1 = slab0 + SLAB_BYTES;
+    uint64_t* full0 = &slab_full[2 * wk];
+    uint64_t* full1 = full0 + 1;
+    uint32_t n_z = 0, n_f0 = 0, n_f1 = 0, n_store = 0;
+    const int col0 = half * 32;
+
+    if (BWD && lane == 0 && (long long)blockIdx.x < n_tiles) {
+      // first tile: dE/dh_L block into slab 0, the top derivative block into slab 1
+      const long long r0 = (long long)blockIdx.x * BM + quarter * 32;
+      mbar_arrive_expect_tx(full0, SLAB_BYTES);
+      tma_load_3d(slab0, &tmIO0, col0, (int)r0, 0, full0);
+      if (n_tc > 0) {
+        mbar_arrive_expect_tx(full1, SLAB_BYTES);
+        tma_load_3d(slab1, &tmIO1, col0, (int)r0, n_tc - 1, full1);
+      }
+    }
+    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      const long long row0 = tile * BM + quarter * 32;
+      const long long row = row0 + lane;
+      const bool valid = row < a.M;
+      const long long next_row0 = (tile + gridDim.x) * BM + quarter * 32;
+      const bool has_next = tile + gridDim.x < n_tiles;
+      float b[NB];
+#pragma unroll
+      for (int k = 0; k < NB; ++k) b[k] = (valid && k < a.nb) ? __ldg(a.basis + row * a.nb + k) : 0.f;
+      float v[32];
+      if (!BWD) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float z = 0.f;
+#pragma unroll
+          for (int k = 0; k < NB; ++k) z = fmaf(w1s[(col0 + j) * NB + k], b[k], z);
+          float d;
+          silu_and_derivative(z, v[j], d);
+        }
+      } else {
+        mbar_wait(full0, n_f0 & 1u, status); ++n_f0;
+        if (n_tc > 0) { mbar_wait(full1, n_f1 & 1u, status); ++n_f1; }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float4 gv = *swz(slab0, lane, c);
+          if (n_tc > 0) {
+            const float4 dv = *swz(slab1, lane, c);
+            gv.x *= dv.x; gv.y *= dv.y; gv.z *= dv.z; gv.w *= dv.w;
+          }
+          v[4 * c] = gv.x; v[4 * c + 1] = gv.y; v[4 * c + 2] = gv.z; v[4 * c + 3] = gv.w;
+        }
+        // both slabs are free again: fetch the next derivative of this tile, or the next tile's blocks
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (n_tc > 1) {
+            mbar_arrive_expect_tx(full0, SLAB_BYTES);
+            tma_load_3d(slab0, &tmIO1, col0, (int)row0, n_tc - 2, full0);
+          } else if (has_next) {
+            mbar_arrive_expect_tx(full0, SLAB_BYTES);
+            tma_load_3d(slab0, &tmIO0, col0, (int)next_row0, 0, full0);
+          }
+          if (has_next && n_tc > 0) {
+            mbar_arrive_expect_tx(full1, SLAB_BYTES);
+            tma_load_3d(slab1, &tmIO1, col0, (int)next_row0, n_tc - 1, full1);
+          }
+        }
+      }
+      for (int s = 0; s < n_tc; ++s) {
+        write_operand(a_base, half, trow, v);
+        fence_async_smem();              // generic-proxy writes -> visible to the tensor core's async proxy
+        tc_fence_before();               // this thread's earlier accumulator reads precede the next MMA
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_ready);
+        mbar_wait(z_full, n_z & 1u, status);
+        ++n_z;
+        tc_fence_after();
+        uint32_t r[32];
+        tmem_ld_32(tmem_acc, r);
+        if (!BWD) {
+          unsigned char* sl = (n_store & 1u) ? slab1 : slab0;
+          if (lane == 0) bulk_wait_read<1>();     // the slab used two stores ago has been read
+          __syncwarp();
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float d[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) silu_and_derivative(__uint_as_float(r[4 * c + e]), v[4 * c + e], d[e]);
+            *swz(sl, lane, c) = make_float4(d[0], d[1], d[2], d[3]);
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (row0 < a.M) tma_store_block(&tmIO1, col0, row0, s, sl);
+            bulk_commit();
+          }
+          ++n_store;
+        } else {
+          const bool more = s + 1 < n_tc;     // multiply by the derivative of the layer below
+          if (more) { mbar_wait(full0, n_f0 & 1u, status); ++n_f0; }
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float4 dv = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (more) dv = *swz(slab0, lane, c);
+            v[4 * c] = __uint_as_float(r[4 * c]) * dv.x; v[4 * c + 1] = __uint_as_float(r[4 * c + 1]) * dv.y;
+            v[4 * c + 2] = __uint_as_float(r[4 * c + 2]) * dv.z; v[4 * c + 3] = __uint_as_float(r[4 * c + 3]) * dv.w;
+          }
+          if (more) {
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (s + 2 < n_tc) {
+                mbar_arrive_expect_tx(full0, SLAB_BYTES);
+                tma_load_3d(slab0, &tmIO1, col0, (int)row0, n_tc - 3 - s, full0);
+              } else if (has_next) {
+                mbar_arrive_expect_tx(full0, SLAB_BYTES);
+                tma_load_3d(slab0, &tmIO0, col0, (int)next_row0, 0, full0);
+              }
+            }
+          }
+        }
+      }
+      if (!BWD) {
+        unsigned char* sl = (n_store & 1u) ? slab1 : slab0;
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 8; ++c) *swz(sl, lane, c) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (row0 < a.M) tma_store_block(&tmIO0, col0, row0, 0, sl);
+          bulk_commit();
+        }
+        ++n_store;
+      } else {
+        float gb[NB];
+#pragma unroll
+        for (int k = 0; k < NB; ++k) gb[k] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float z = 0.f;
+#pragma unroll
+          for (int k = 0; k < NB; ++k) z = fmaf(w1s[(col0 + j) * NB + k], b[k], z);
+          float h, d;
+          silu_and_derivative(z, h, d);
+          const float gz = v[j] * d;
+#pragma unroll
+          for (int k = 0; k < NB; ++k) gb[k] = fmaf(gz, w1s[(col0 + j) * NB + k], gb[k]);
+        }
+        if (valid) {
+          // the two half-row owners of an edge add into a zero-filled row: two addends, order-independent
+#pragma unroll
+          for (int k = 0; k < NB; ++k)
+            if (k < a.nb) red_add(a.grad_basis + row * a.nb + k, gb[k]);
+        }
+      }
+    }
+    if (!BWD && lane == 0) bulk_wait_read<0>();   // the slabs must outlive their stores
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, H);
+  }
+}
+
+// prepared[l][hi | lo][r][c] = split(transpose ? W_l[c][r] : W_l[r][c]) for up to MAX_TC 64 x 64 matrices
+__global__ void prepare_weights_kernel(const float* __restrict__ w0, const float* __restrict__ w1, int n, bool transpose,
+                                       float* __restrict__ prepared) {
+  const int total = n * H * H;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int l = i / (H * H), r = (i / H) % H, c = i % H;
+    const float* w = l == 0 ? w0 : w1;
+    const float v = transpose ? w[c * H + r] : w[r * H + c];
+    float hi, lo;
+    tc::split_tf32(v, hi, lo);
+    prepared[(size_t)(l * 2) * H * H + r * H + c] = hi;
+    prepared[(size_t)(l * 2 + 1) * H * H + r * H + c] = lo;
+  }
+}
+
+__device__ int g_chain_status;
+
+int device_status(int* code) {
+  int v = 0, zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_chain_status, sizeof(int));
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaMemcpyToSymbol(g_chain_status, &zero, sizeof(int));
+  if (e != cudaSuccess) return cuda_fail(e);
+  *code = v;
+  return FASTEQ_OK;
+}
+
+template <int NB, bool BWD>
+static int launch_nb(const CUtensorMap& tmw, const CUtensorMap& io0, const CUtensorMap& io1, const Args& a, cudaStream_t s) {
+  int* st = nullptr;
+  cudaError_t e = cudaGetSymbolAddress((void**)&st, g_chain_status);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaFuncSetAttribute(radial_chain_kernel<NB, BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return cuda_fail(e);
+  int dev = 0, sms = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return cuda_fail(e);
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return cuda_fail(e);
+  const long long n_tiles = (a.M + BM - 1) / BM;
+  const unsigned grid = (unsigned)(n_tiles < sms ? n_tiles : sms);
+  radial_chain_kernel<NB, BWD><<<grid, NT, SMEM_BYTES, s>>>(tmw, io0, io1, a, st);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
+}
+
+// io0: forward h_L out / backward dE/dh_L in, [M, 64]; io1: derivatives [n_tc, M, 64] (out / in)
+template <bool BWD>
+static int run(Args a, const float* const* w_hidden, const float* io0, const float* io1, cudaStream_t s) {
+  if (a.M < 0 || a.nb < 1) return FASTEQ_INVALID;
+  if (a.nb > MAX_NB || a.n_tc < 0 || a.n_tc > MAX_TC || a.M > 0x7fffffffLL - BM) return FASTEQ_UNSUPPORTED;
+  if (a.M == 0) return FASTEQ_OK;
+  if (!a.basis || !a.w1 || !io0 || (a.n_tc > 0 && (!w_hidden || !io1)) || (BWD && !a.grad_basis)) return FASTEQ_INVALID;
+  if ((reinterpret_cast<uintptr_t>(io0) | reinterpret_cast<uintptr_t>(io1)) & 15u) return FASTEQ_UNSUPPORTED;
+  for (int l = 0; l < a.n_tc; ++l)
+    if (!w_hidden[l]) return FASTEQ_INVALID;
+  cudaError_t e;
+  if (BWD) {
+    e = cudaMemsetAsync(a.grad_basis, 0, (size_t)a.M * a.nb * sizeof(float), s);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  float* prepared = nullptr;
+  alignas(64) CUtensorMap tmw, tm0, tm1;
+  const int n_alloc = a.n_tc > 0 ? a.n_tc : 1;
+  e = cudaMallocAsync((void**)&prepared, (size_t)n_alloc * 2 * H * H * sizeof(float), s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (a.n_tc > 0) {
+    // forward uses W_2, W_3 in order; backward uses W_L^T first
+    const float* first = BWD ? w_hidden[a.n_tc - 1] : w_hidden[0];
+    const float* second = a.n_tc > 1 ? (BWD ? w_hidden[0] : w_hidden[1]) : first;
+    prepare_weights_kernel<<<a.n_tc * 4, 256, 0, s>>>(first, second, a.n_tc, BWD, prepared);
+  }
+  int rc = tc::make_map(&tmw, prepared, (uint64_t)H, (uint64_t)H, (uint64_t)n_alloc * 2, (uint64_t)H, (uint64_t)H * H, BK, H, 1);
+  if (rc == FASTEQ_OK) rc = tc::make_map(&tm0, io0, (uint64_t)H, (uint64_t)a.M, 1, (uint64_t)H, (uint64_t)a.M * H, 32, 32, 1);
+  if (rc == FASTEQ_OK)
+    rc = tc::make_map(&tm1, a.n_tc > 0 ? io1 : io0, (uint64_t)H, (uint64_t)a.M, (uint64_t)n_alloc, (uint64_t)H, (uint64_t)a.M * H, 32, 32, 1);
+  if (rc == FASTEQ_OK) rc = a.nb <= 8 ? launch_nb<8, BWD>(tmw, tm0, tm1, a, s) : launch_nb<16, BWD>(tmw, tm0, tm1, a, s);
+  cudaFreeAsync(prepared, s);
+  return rc;
+}
+
+}  // namespace chain
+}  // namespace fasteq
+
+extern "C" int fasteq_radial_chain_forward(const float* basis, int64_t n_edges, int32_t n_basis, const float* w_first,
+                                           const float* const* w_hidden, int32_t n_hidden, float* out, float* deriv,
+                                           fasteq_stream_t stream) {
+  if (n_hidden < 1) return FASTEQ_INVALID;
+  fasteq::chain::Args a{};
+  a.basis = basis; a.w1 = w_first; a.M = n_edges; a.nb = n_basis; a.n_tc = n_hidden - 1;
+  return fasteq::chain::run<false>(a, w_hidden, out, deriv, (cudaStream_t)stream);
+}
+
+extern "C" int fasteq_radial_chain_backward(const float* grad_out, const float* deriv, const float* basis, int64_t n_edges,
+                                            int32_t n_basis, const float* w_first, const float* const* w_hidden,
+                                            int32_t n_hidden, float* grad_basis, fasteq_stream_t stream) {
+  if (n_hidden < 1) return FASTEQ_INVALID;
+  fasteq::chain::Args a{};
+  a.basis = basis; a.w1 = w_first; a.grad_basis = grad_basis; a.M = n_edges; a.nb = n_basis; a.n_tc = n_hidden - 1;
+  return fasteq::chain::run<true>(a, w_hidden, grad_out, deriv, (cudaStream_t)stream);
+}

@@ -20,6 +20,7 @@ import torch
 from ..descriptors import full_channelwise_instructions
 from ..irreps import Irreps
 from ..ops.dense import dense
+from ..ops.radial_chain import radial_chain
 from ..ops.spherical_harmonics import SphericalHarmonics
 from .modules import ChannelwiseTensorProduct, SO3Linear, SymmetricContraction
 
@@ -44,6 +45,10 @@ class RadialMLP(torch.nn.Module):
             torch.nn.init.normal_(lin.weight, std=1.0 / math.sqrt(lin.in_features))
 
     def forward(self, x):
+        # inference / forces: all hidden layers in one kernel, then the wide last layer
+        h = radial_chain(x, [lin.weight for lin in self.layers[:-1]]) if x.dim() == 2 else None
+        if h is not None:
+            return dense(h, self.layers[-1].weight)
         for i, lin in enumerate(self.layers):
             x = dense(x, lin.weight)
             if i + 1 < len(self.layers):

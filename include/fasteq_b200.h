@@ -236,6 +236,21 @@ int fasteq_gate_backward(const fasteq_gate_problem* p /* host */, const void* x,
  * pointers 16-byte aligned, else FASTEQ_UNSUPPORTED.  The reference leaves this MLP to the model
  * package (torch); it has no entry point of its own for it. */
 int fasteq_gemm_tf32x3(const void* A, const void* Bt, void* C, int64_t M, int32_t N, int32_t K, fasteq_stream_t stream);
+/* Hidden layers of the radial MLP (width 64, SiLU, no bias) fused into one kernel per direction:
+ *   forward : basis [n_edges, n_basis] -> h_1 = silu(W_1 basis) -> ... -> h_L = silu(W_L h_{L-1})
+ *   backward: dE/dh_L -> dE/dbasis (weights get no gradient here; train through the layered path)
+ * w_first is W_1 [64, n_basis] (n_basis <= 16); w_hidden is a HOST array of n_hidden - 1 device
+ * pointers to W_2.. [64, 64] (n_hidden in 1..3).  The first layer runs on the CUDA cores, the 64 x 64
+ * layers as 3xTF32 tcgen05 products chained through shared memory and TMEM.  The forward also writes
+ * deriv [n_hidden - 1, n_edges, 64] = silu'(z_l) of the tensor-core layers, which the backward reads.
+ * out / deriv / grad_out 16-byte aligned.  No counterpart in the reference, which leaves the radial
+ * MLP to torch modules of the model package. */
+int fasteq_radial_chain_forward(const float* basis, int64_t n_edges, int32_t n_basis, const float* w_first,
+                                const float* const* w_hidden /* host */, int32_t n_hidden, float* out, float* deriv,
+                                fasteq_stream_t stream);
+int fasteq_radial_chain_backward(const float* grad_out, const float* deriv, const float* basis, int64_t n_edges,
+                                 int32_t n_basis, const float* w_first, const float* const* w_hidden /* host */,
+                                 int32_t n_hidden, float* grad_basis, fasteq_stream_t stream);
 /* Reads and clears the status word of the tensor-core kernels (synchronises). */
 int fasteq_tensorcore_device_status(int32_t* code /* host */);
 
