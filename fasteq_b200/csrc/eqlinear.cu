@@ -223,16 +223,20 @@ int launch(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const vo
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }
 
-// Bt[q][n][k] = coeff[q] * op(W[q])[k][n]: the K-major, pre-scaled weight blocks the tensor-core GEMM multiplies with.
+// Bt[q][n][k] = coeff[q] * op(W[q])[k][n]: the K-major, pre-scaled weight blocks the tensor-core GEMM multiplies with,
+// written as their two TF32 parts (hi: 10 mantissa bits, lo: the exact remainder).
 // Forward: K = u, N = v (a transpose of W[q]); grad_x: K = v, N = u (W[q] as stored).
-__global__ void pack_weights_kernel(const float* __restrict__ W, float* __restrict__ Bt, const __grid_constant__ GroupTable tab,
-                                    int u, int v, bool dgrad) {
+__global__ void pack_weights_kernel(const float* __restrict__ W, float* __restrict__ Bt_hi, float* __restrict__ Bt_lo,
+                                    const __grid_constant__ GroupTable tab, int u, int v, bool dgrad) {
   const int K = dgrad ? v : u, N = dgrad ? u : v;
   const long long total = (long long)tab.n_paths * N * K;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int k = (int)(i % K), n = (int)((i / K) % N), q = (int)(i / ((long long)K * N));
     const float* wq = W + (size_t)tab.path_w[q] * u * v;
-    Bt[i] = tab.path_coeff_f[q] * (dgrad ? wq[(size_t)n * v + k] : wq[(size_t)k * v + n]);
+    const float val = tab.path_coeff_f[q] * (dgrad ? wq[(size_t)n * v + k] : wq[(size_t)k * v + n]);
+    const float hi = __uint_as_float(__float_as_uint(val) & 0xffffe000u);
+    Bt_hi[i] = hi;
+    Bt_lo[i] = val - hi;
   }
 }
 
@@ -256,15 +260,15 @@ int launch_tensorcore(const fasteq_eqlinear_problem* p, bool dgrad, const void* 
   t.item_first[tab.n_groups] = t.n_items;
   for (int q = 0; q < tab.n_paths; ++q) { t.path_a_row[q] = tab.path_a_row[q]; t.path_w[q] = q; }   // packed in table order
   float* bt = nullptr;
-  cudaError_t e = cudaMallocAsync((void**)&bt, (size_t)p->num_paths * N * K * sizeof(float), s);
-  if (e != cudaSuccess) return cuda_fail(e);
   const long long total = (long long)p->num_paths * N * K;
-  pack_weights_kernel<<<(unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096), 256, 0, s>>>((const float*)w, bt, tab, p->u, p->v, dgrad);
+  cudaError_t e = cudaMallocAsync((void**)&bt, (size_t)total * 2 * sizeof(float), s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  pack_weights_kernel<<<(unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096), 256, 0, s>>>((const float*)w, bt, bt + total, tab, p->u, p->v, dgrad);
   if (!covers) {
     const long long tot = p->batch * c_rows * N;
     zero_rows_kernel<float><<<(unsigned)((tot + 255) / 256), 256, 0, s>>>((float*)c, p->batch, c_rows, N, tab);
   }
-  rc = tc::launch(t, (const float*)a, p->batch, a_rows, K, bt, p->num_paths, N, (float*)c, c_rows, s);
+  rc = tc::launch(t, (const float*)a, p->batch, a_rows, K, bt, bt + total, p->num_paths, N, (float*)c, c_rows, s);
   cudaFreeAsync(bt, s);
   if (rc == FASTEQ_OK) *used = true;
   return rc;

@@ -73,9 +73,10 @@ __device__ __forceinline__ Tile decode_tile(const TcTable& tab, long long tile, 
 
 template <int BN>
 __global__ void __launch_bounds__(NT_P, 1)
-gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                   const __grid_constant__ CUtensorMap tmC, const __grid_constant__ TcTable tab, long long M, int N, int K,
-                   long long n_tiles_total, int m_tiles, int n_tiles, int* status) {
+gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBhi,
+                   const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmC,
+                   const __grid_constant__ TcTable tab, long long M, int N, int K, long long n_tiles_total, int m_tiles,
+                   int n_tiles, int* status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using C_ = Cfg<BN>;
@@ -99,7 +100,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     mbar_fence_init();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(4 * BN)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -119,17 +120,19 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           unsigned char* st = stage_base + (size_t)s * C_::STAGE_BYTES;
           const int seg = tl.seg0 + kb / kb_per_seg;
           const int k0 = (kb % kb_per_seg) * BK;
-          mbar_arrive_expect_tx(&full_raw[s], (uint32_t)(C_::A_BYTES + C_::B_BYTES));
+          mbar_arrive_expect_tx(&full_raw[s], (uint32_t)(C_::A_BYTES + 2 * C_::B_BYTES));
           tma_load_3d(st, &tmA, k0, tab.path_a_row[seg] + tl.t, (int)tl.m0, &full_raw[s]);
-          tma_load_3d(st + 2 * C_::A_BYTES, &tmB, k0, tl.n0, tab.path_w[seg], &full_raw[s]);
+          tma_load_3d(st + 2 * C_::A_BYTES, &tmBhi, k0, tl.n0, tab.path_w[seg], &full_raw[s]);
+          tma_load_3d(st + 2 * C_::A_BYTES + C_::B_BYTES, &tmBlo, k0, tl.n0, tab.path_w[seg], &full_raw[s]);
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128
-      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      // instruction descriptors: D = F32, A = B = TF32, both K-major, M = 128; N = 2 BN for the product of
+      // A_hi with the stacked [B_hi; B_lo] tile, N = BN for A_lo x B_hi
+      const uint32_t idesc2 = idesc_tf32_m128(2 * BN), idesc1 = idesc_tf32_m128(BN);
       int it = 0;
       uint32_t lt = 0;
       for (long long tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++lt) {
@@ -137,21 +140,21 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const uint32_t buf = lt & 1u;
         mbar_wait(&acc_empty[buf], ((lt >> 1) & 1u) ^ 1u, status);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t tmem_d = tmem_base + buf * (uint32_t)BN;
+        // columns [0, BN): hi x hi;  [BN, 2 BN): hi x lo + lo x hi (small terms, kept apart so that their
+        // sum is not absorbed one rounding at a time into the large accumulator)
+        const uint32_t tmem_d = tmem_base + buf * (uint32_t)(2 * BN);
         for (int kb = 0; kb < tl.n_kb; ++kb, ++it) {
           const int s = it % STAGES;
           mbar_wait(&full_split[s], (it / STAGES) & 1u, status);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_hi = smem_u32(stage_base + (size_t)s * C_::STAGE_BYTES);
           const uint32_t a_lo = a_hi + C_::A_BYTES;
-          const uint32_t b_hi = a_hi + 2 * C_::A_BYTES;
-          const uint32_t b_lo = b_hi + C_::B_BYTES;
+          const uint32_t b_hi = a_hi + 2 * C_::A_BYTES;    // B_hi tile, B_lo tile right behind it
 #pragma unroll
           for (int kk = 0; kk < BK / 8; ++kk) {
             const uint32_t off = kk * 32;   // 8 TF32 values = 32 bytes along K inside the 128-byte swizzle row
-            mma_tf32(tmem_d, make_desc(a_lo + off), make_desc(b_hi + off), idesc, (kb | kk) ? 1u : 0u);
-            mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_lo + off), idesc, 1u);
-            mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_hi + off), idesc, 1u);
+            mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_hi + off), idesc2, (kb | kk) ? 1u : 0u);
+            mma_tf32(tmem_d + (uint32_t)BN, make_desc(a_lo + off), make_desc(b_hi + off), idesc1, 1u);
           }
           mma_commit(&empty[s]);            // the stage may be refilled once these MMAs have read it
         }
@@ -170,8 +173,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         unsigned char* st = stage_base + (size_t)s * C_::STAGE_BYTES;
         float4* a_hi = reinterpret_cast<float4*>(st);
         float4* a_lo = reinterpret_cast<float4*>(st + C_::A_BYTES);
-        float4* b_hi = reinterpret_cast<float4*>(st + 2 * C_::A_BYTES);
-        float4* b_lo = reinterpret_cast<float4*>(st + 2 * C_::A_BYTES + C_::B_BYTES);
         auto split = [](float4 v, float4& hi, float4& lo) {
           hi.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); lo.x = v.x - hi.x;
           hi.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); lo.y = v.y - hi.y;
@@ -182,11 +183,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         for (int i = 0; i < C_::A_BYTES / 16 / 128; ++i) {
           float4 hi, lo; split(a_hi[tid + i * 128], hi, lo);
           a_hi[tid + i * 128] = hi; a_lo[tid + i * 128] = lo;
-        }
-#pragma unroll
-        for (int i = 0; i < C_::B_BYTES / 16 / 128; ++i) {
-          float4 hi, lo; split(b_hi[tid + i * 128], hi, lo);
-          b_hi[tid + i * 128] = hi; b_lo[tid + i * 128] = lo;
         }
         fence_async_smem();                 // generic-proxy writes -> visible to the tensor core's async proxy
         __syncwarp();
@@ -209,18 +205,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const int c_row = tab.group_c_row[tl.g] + tl.t;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c, ++chunk_no) {
-        uint32_t r[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)BN + (uint32_t)(c * 32);
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-              "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-            : "r"(taddr)
-            : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        uint32_t r[32], q[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * (uint32_t)(2 * BN) + (uint32_t)(c * 32);
+        tmem_ld_32(taddr, r);                      // hi x hi
+        tmem_ld_32(taddr + (uint32_t)BN, q);       // hi x lo + lo x hi
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(q[j]));
         unsigned char* sl = slab + (size_t)(chunk_no & 1) * 4096;
         if (lane == 0) bulk_wait_read<1>();     // the slab used two chunks ago has been read by its store
         __syncwarp();
@@ -251,7 +241,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(4 * BN)) : "memory");
   }
 }
 
@@ -493,8 +483,8 @@ static int sm_count() {
 }
 
 template <int BN>
-static int launch_bn(const TcTable& tab, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, long long M, int N,
-                     int K, cudaStream_t s) {
+static int launch_bn(const TcTable& tab, const CUtensorMap& ma, const CUtensorMap& mbh, const CUtensorMap& mbl, const CUtensorMap& mc,
+                     long long M, int N, int K, cudaStream_t s) {
   int* st = nullptr;
   cudaError_t e = cudaGetSymbolAddress((void**)&st, g_tc_status);
   if (e != cudaSuccess) return cuda_fail(e);
@@ -506,23 +496,34 @@ static int launch_bn(const TcTable& tab, const CUtensorMap& ma, const CUtensorMa
   const int sms = sm_count();
   if (sms < 1) return FASTEQ_CUDA_ERROR;
   const unsigned grid = (unsigned)(total < sms ? total : sms);     // one persistent CTA per SM
-  gemm_tf32x3_kernel<BN><<<grid, NT_P, Cfg<BN>::SMEM_BYTES, s>>>(ma, mb, mc, tab, M, N, K, total, (int)m_tiles, n_tiles, st);
+  gemm_tf32x3_kernel<BN><<<grid, NT_P, Cfg<BN>::SMEM_BYTES, s>>>(ma, mbh, mbl, mc, tab, M, N, K, total, (int)m_tiles, n_tiles, st);
   e = cudaGetLastError();
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }
 
-int launch(const TcTable& tab, const float* A, long long M, int a_rows, int K, const float* Bt, int P, int N, float* C,
-           int c_rows, cudaStream_t s) {
+// Bt_hi / Bt_lo: the [P, N, K] weight blocks already split into their TF32 parts (split_weights / the
+// SO3Linear packing kernel do it once per call; the blocks are tiny next to A)
+int launch(const TcTable& tab, const float* A, long long M, int a_rows, int K, const float* Bt_hi, const float* Bt_lo, int P, int N,
+           float* C, int c_rows, cudaStream_t s) {
   if (tab.n_items < 1 || tab.n_items > 65535) return FASTEQ_UNSUPPORTED;
   const int BN = N <= 64 ? 64 : 128;
-  alignas(64) CUtensorMap ma, mb, mc;
+  alignas(64) CUtensorMap ma, mbh, mbl, mc;
   int rc = make_map(&ma, A, (uint64_t)K, (uint64_t)a_rows, (uint64_t)M, (uint64_t)K, (uint64_t)a_rows * K, BK, 1, BM);
   if (rc != FASTEQ_OK) return rc;
-  rc = make_map(&mb, Bt, (uint64_t)K, (uint64_t)N, (uint64_t)P, (uint64_t)K, (uint64_t)N * K, BK, (uint32_t)BN, 1);
+  rc = make_map(&mbh, Bt_hi, (uint64_t)K, (uint64_t)N, (uint64_t)P, (uint64_t)K, (uint64_t)N * K, BK, (uint32_t)BN, 1);
+  if (rc != FASTEQ_OK) return rc;
+  rc = make_map(&mbl, Bt_lo, (uint64_t)K, (uint64_t)N, (uint64_t)P, (uint64_t)K, (uint64_t)N * K, BK, (uint32_t)BN, 1);
   if (rc != FASTEQ_OK) return rc;
   rc = make_map(&mc, C, (uint64_t)N, (uint64_t)c_rows, (uint64_t)M, (uint64_t)N, (uint64_t)c_rows * N, 32, 1, 32);
   if (rc != FASTEQ_OK) return rc;
-  return BN == 64 ? launch_bn<64>(tab, ma, mb, mc, M, N, K, s) : launch_bn<128>(tab, ma, mb, mc, M, N, K, s);
+  return BN == 64 ? launch_bn<64>(tab, ma, mbh, mbl, mc, M, N, K, s) : launch_bn<128>(tab, ma, mbh, mbl, mc, M, N, K, s);
+}
+
+// hi / lo parts of n contiguous FP32 values into split[0 .. n) and split[n .. 2n)
+int split_weights(const float* w, long long n, float* split, cudaStream_t s) {
+  split_weights_kernel<<<(unsigned)((n + 255) / 256 < 1024 ? (n + 255) / 256 : 1024), 256, 0, s>>>(w, split, split + n, n);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }
 
 template <int KB>
@@ -584,7 +585,15 @@ extern "C" int fasteq_gemm_tf32x3(const void* A, const void* Bt, void* C, int64_
   tc::TcTable tab{};
   tab.n_groups = 1; tab.n_items = 1; tab.group_c_row[0] = 0; tab.group_first[0] = 0; tab.group_first[1] = 1;
   tab.item_first[0] = 0; tab.item_first[1] = 1; tab.path_a_row[0] = 0; tab.path_w[0] = 0;
-  return tc::launch(tab, (const float*)A, M, 1, K, (const float*)Bt, 1, N, (float*)C, 1, (cudaStream_t)stream);
+  float* split = nullptr;
+  const long long nw = (long long)N * K;
+  cudaError_t e = cudaMallocAsync((void**)&split, (size_t)nw * 2 * sizeof(float), (cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_fail(e);
+  int rc = tc::split_weights((const float*)Bt, nw, split, (cudaStream_t)stream);
+  if (rc == FASTEQ_OK)
+    rc = tc::launch(tab, (const float*)A, M, 1, K, split, split + nw, 1, N, (float*)C, 1, (cudaStream_t)stream);
+  cudaFreeAsync(split, (cudaStream_t)stream);
+  return rc;
 }
 
 extern "C" int fasteq_tensorcore_device_status(int32_t* code) {

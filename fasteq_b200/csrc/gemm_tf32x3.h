@@ -14,8 +14,8 @@ struct TcTable {
   int path_w[64];              // block of Bt the segment multiplies with
 };
 bool supported(long long M, int a_rows, int K, int P, int N, int c_rows, const void* A, const void* Bt, const void* C);
-int launch(const TcTable& tab, const float* A, long long M, int a_rows, int K, const float* Bt, int P, int N, float* C,
-           int c_rows, cudaStream_t s);
+int launch(const TcTable& tab, const float* A, long long M, int a_rows, int K, const float* Bt_hi, const float* Bt_lo, int P, int N,
+           float* C, int c_rows, cudaStream_t s);
 int device_status(int* code);
 // 3-D FP32 tensor [d2][d1][d0] (d0 contiguous, strides in elements), box [b2][b1][b0], SWIZZLE_128B, zero fill
 int make_map(CUtensorMap* m, const float* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_elems,
