@@ -121,7 +121,7 @@ def build_inputs(workload: str, seed: int, n_boxes=None):
     g = torch.Generator().manual_seed(seed)
     N, E, U = batch.n_nodes, batch.n_edges, d.u_dim
     vec = torch.from_numpy(batch.edge_vec)
-    return dict(d=d, ins=ins, irreps=(in1, str(sh), str(io)), batch=batch, N=N, E=E, dtype=dtype, vec=vec,
+    return dict(d=d, ins=ins, irreps=(in1, str(sh), str(io)), batch=batch, N=N, E=E, dtype=dtype, vec=vec, n_boxes=n_boxes or boxes,
                 x=torch.randn(N, d.x_seg_num * U, generator=g, dtype=dtype),
                 w=torch.randn(E, d.w_seg_num * U, generator=g, dtype=dtype),
                 r=torch.randn(N, d.out_seg_num * U, generator=g, dtype=dtype),
@@ -355,6 +355,7 @@ def reference_arm(args):
 
 def config_dict(workload, inp, n_gpus):
     in1, lsh, lout, boxes, dtype = WORKLOADS[workload]
+    boxes = inp.get("n_boxes", boxes)
     d = inp["d"]
     return {"workload": workload, "irreps_in1": in1, "sh_lmax": lsh, "lmax_out": lout, "u": d.u_dim,
             "w_segs": d.w_seg_num, "out_segs": d.out_seg_num, "cg_paths": d.num_paths,
