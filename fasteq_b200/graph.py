@@ -34,12 +34,13 @@ class Batch:
         return int(self.edge_src.shape[0])
 
 
-def periodic_radius_graph(pos: np.ndarray, side: float, cutoff: float):
-    """All pairs (sender j, receiver i, image) with |r_j + shift - r_i| < cutoff in a cubic box."""
+def periodic_radius_graph(pos: np.ndarray, side, cutoff: float):
+    """All pairs (sender j, receiver i, image) with |r_j + shift - r_i| < cutoff in a periodic box
+    (``side``: one length for a cube, or three for an orthorhombic box)."""
     n = pos.shape[0]
-    reach = int(np.ceil(cutoff / side))
-    rng = np.arange(-reach, reach + 1)
-    images = np.stack(np.meshgrid(rng, rng, rng, indexing="ij"), -1).reshape(-1, 3).astype(np.float64) * side
+    side = np.broadcast_to(np.asarray(side, dtype=np.float64), (3,))
+    rngs = [np.arange(-int(np.ceil(cutoff / s)), int(np.ceil(cutoff / s)) + 1) for s in side]
+    images = np.stack(np.meshgrid(*rngs, indexing="ij"), -1).reshape(-1, 3).astype(np.float64) * side
     src_l, dst_l, vec_l, sh_l = [], [], [], []
     c2 = cutoff * cutoff
     for img in images:

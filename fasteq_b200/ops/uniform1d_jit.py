@@ -69,13 +69,22 @@ class GraphPlan:
     """Receiver-sorted CSR view of a scatter index: sortedness, permutation, segment offsets
     and per-grid partitions.  Built once per index tensor (one host sync) and cached."""
 
-    def __init__(self, dst: torch.Tensor, n_rows: int):
+    def __init__(self, dst: torch.Tensor, n_rows: int, seg_ptr: Optional[torch.Tensor] = None):
         if dst.dim() != 1:
             raise ValueError("scatter index must be 1-D")
         core = _cabi.core()
         self.n_rows = int(n_rows)
         self.n_edges = int(dst.numel())
         dev = dst.device
+        self._parts: Dict[int, torch.Tensor] = {}
+        self.device = dev
+        if seg_ptr is not None:
+            # the caller vouches for a receiver-sorted index and brings its CSR offsets (the GPU
+            # neighbour-list builder does): nothing to check, nothing to build, no host sync
+            if seg_ptr.numel() != self.n_rows + 1 or seg_ptr.dtype != torch.int32 or seg_ptr.device != dev:
+                raise ValueError("seg_ptr must be an int32 tensor of n_rows + 1 offsets on the index's device")
+            self.sorted, self.perm, self.seg_ptr = True, None, seg_ptr.contiguous()
+            return
         stream = torch.cuda.current_stream(dev).cuda_stream
         dst32 = dst.to(torch.int32).contiguous()
         flag = torch.empty(1, dtype=torch.int32, device=dev)
@@ -122,6 +131,17 @@ def graph_plan(dst: torch.Tensor, n_rows: int) -> GraphPlan:
         plan = GraphPlan(dst, n_rows)
         plan._keepalive = dst  # the key is the storage address: keep it from being recycled
         _PLANS[key] = plan
+    return plan
+
+
+def register_sorted_plan(dst: torch.Tensor, n_rows: int, seg_ptr: torch.Tensor) -> GraphPlan:
+    """Install the plan of a receiver-sorted index whose CSR offsets are already known."""
+    key = (dst.data_ptr(), dst.numel(), dst._version, str(dst.device), dst.dtype, int(n_rows))
+    if len(_PLANS) >= _PLAN_LIMIT:
+        _PLANS.pop(next(iter(_PLANS)))
+    plan = GraphPlan(dst, n_rows, seg_ptr)
+    plan._keepalive = dst
+    _PLANS[key] = plan
     return plan
 
 

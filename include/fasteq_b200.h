@@ -166,6 +166,35 @@ int fasteq_graph_partition(const int32_t* seg_ptr, int64_t n_rows, int64_t n_edg
                            int32_t* part_ptr, fasteq_stream_t stream);
 
 /* ------------------------------------------------------------------------- *
+ * Periodic radius graph on the GPU (a neighbour of the hot path; the reference's callers bring edge
+ * lists from ASE / matscipy and it has no counterpart).  Batches of orthorhombic periodic boxes;
+ * every pair (sender j, receiver i, image) with |r_j + shift - r_i| < cutoff, both directions, no
+ * self edge in the home image, ordered by (receiver, sender, shift_x, shift_y, shift_z).  The count
+ * step also yields the CSR offsets (seg_ptr) that fasteq_u1d_graph wants.
+ *
+ *   fasteq_neighbors_work_bytes(&p, &bytes);                          host only
+ *   fasteq_neighbors_count(&p, work, bytes, seg_ptr, max_deg, s);     seg_ptr[n_atoms] = number of edges
+ *   ... read seg_ptr[n_atoms] (and max_deg <= 1024), allocate the edge arrays ...
+ *   fasteq_neighbors_fill(&p, work, bytes, seg_ptr, src, dst, shift, s);
+ *
+ * Positions are FP64 and must lie inside [0, box); distances are formed as ((r_j + shift) - r_i) with
+ * individually rounded FP64 operations, so the edge set equals a numpy evaluation of the same formula.
+ * ------------------------------------------------------------------------- */
+typedef struct fasteq_nl_problem {
+  int64_t n_atoms;
+  int32_t n_structs;
+  double cutoff;
+  const double* pos;            /* device [n_atoms, 3] */
+  const int32_t* atom_struct;   /* device [n_atoms] structure id of each atom */
+  const double* box;            /* HOST [n_structs, 3] box lengths */
+} fasteq_nl_problem;
+int fasteq_neighbors_work_bytes(const fasteq_nl_problem* p /* host */, int64_t* bytes /* host */);
+int fasteq_neighbors_count(const fasteq_nl_problem* p /* host */, void* work, int64_t work_bytes, int32_t* seg_ptr /* [n_atoms+1] */,
+                           int32_t* max_degree /* device, may be NULL */, fasteq_stream_t stream);
+int fasteq_neighbors_fill(const fasteq_nl_problem* p /* host */, void* work, int64_t work_bytes, const int32_t* seg_ptr,
+                          int32_t* edge_src, int32_t* edge_dst, double* edge_shift /* [n_edges, 3] */, fasteq_stream_t stream);
+
+/* ------------------------------------------------------------------------- *
  * SO3Linear ("eqlinear", subscripts uv,iu,iv): per-irrep channel mix
  *
  *   out[b, out_row[q] + t, :] += coeff[q] * x[b, in_row[q] + t, :] @ W[q]      t < rows[q]
