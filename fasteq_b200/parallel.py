@@ -139,3 +139,45 @@ class HaloExchange:
         if self.local.world == 1:
             return x
         return _Halo.apply(x, self.export_idx, self.ghost_slot, self.local.max_export, self.group)
+
+
+class _EngineExchange(torch.autograd.Function):
+    """Ghost rows filled by an MD engine's communication, differentiable: the forward hands the engine a
+    buffer of ``ntotal`` rows whose first ``nlocal`` hold the owned values and lets it fill the rest; the
+    backward hands it the gradient of all rows and gets back the owners' sums.  The engine object follows the
+    protocol of LAMMPS ML-IAP data as the reference's models use it
+    (.../nequip/nn/_ghost_exchange_lmp_mliap.py:11-31): ``nlocal``, ``ntotal``,
+    ``forward_exchange(src [ntotal, w], dst [ntotal, w], w)``, ``reverse_exchange(grad [ntotal, w], dst [ntotal, w], w)``."""
+
+    @staticmethod
+    def forward(ctx, x_owned, engine):
+        nlocal, ntotal = int(engine.nlocal), int(engine.ntotal)
+        if x_owned.shape[0] != nlocal:
+            raise ValueError(f"engine exchange: {x_owned.shape[0]} owned rows given, the engine owns {nlocal}")
+        flat = x_owned.reshape(nlocal, -1)
+        src = torch.zeros((ntotal, flat.shape[1]), dtype=flat.dtype, device=flat.device)
+        src[:nlocal] = flat
+        out = torch.empty_like(src)
+        engine.forward_exchange(src, out, out.shape[1])
+        ctx.engine, ctx.nlocal, ctx.tail = engine, nlocal, x_owned.shape[1:]
+        return out.reshape((ntotal,) + tuple(x_owned.shape[1:]))
+
+    @staticmethod
+    def backward(ctx, grad_ext):
+        g = grad_ext.reshape(grad_ext.shape[0], -1).contiguous()
+        out = torch.empty_like(g)
+        ctx.engine.reverse_exchange(g, out, out.shape[1])
+        return out[: ctx.nlocal].reshape((ctx.nlocal,) + tuple(ctx.tail)), None
+
+
+class EngineGhostExchange:
+    """``ext = halo(x_owned)`` with the ghost rows supplied by an MD engine (same calling convention as
+    ``HaloExchange``, so the models' ``halo=`` hook takes either)."""
+
+    def __init__(self, engine):
+        self.engine = engine
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if int(self.engine.ntotal) == int(self.engine.nlocal):
+            return x
+        return _EngineExchange.apply(x, self.engine)
