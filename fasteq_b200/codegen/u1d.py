@@ -22,6 +22,7 @@ from dataclasses import dataclass
 from typing import Dict, List, Tuple
 
 from .u1d_common import U1DSpec, Block, build_blocks, lit, split_out_segments
+from .sh import SH_DEVICE_STUB, emit_sh_device
 
 
 @dataclass(frozen=True)
@@ -120,8 +121,9 @@ constexpr int U = {spec.u}, CT = {tun.ct}, WSEG = {spec.w_segs}, XSEG = {spec.x_
 constexpr int STAGES = {tun.stages}, GROUPS = {tun.groups}, PIPES = {tun.pipes}, NCONS_WARPS = {ncons_warps}, STAGE_EXTRA_BYTES = {extra_bytes};
 constexpr bool EMIT_EMPTY_ROWS = {b(emit_empty)}, BEGIN_PER_SEGMENT = {b(not emit_empty)};
 constexpr bool Y_VEC = {b(spec.y_vec)}, W_SHARED = {b(spec.w_shared)}, X_INDEXED = {b(spec.x_indexed)}, Y_INDEXED = {b(spec.y_indexed)}, SCATTERED = {b(spec.scattered)};
+constexpr bool Y_SH = {b(bool(spec.y_sh))};   // the y operand holds edge vectors [rows, 3]; the producer evaluates their harmonics
 }}  // namespace cfg
-"""
+""" + (emit_sh_device(spec.y_sh[0], spec.dtype, spec.y_sh[1], spec.y_sh[2]) if spec.y_sh else SH_DEVICE_STUB)
 
 
 _HOST_COMMON = r"""
@@ -608,6 +610,23 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
         const Meta pm = *reinterpret_cast<const Meta*>(st + OFF_META);
         if (pm.flags & F_DATA) {{
           const T* part = reinterpret_cast<const T*>(st + OFF_EXTRA);
+          if (cfg::Y_SH) {{
+            // the y operand is the edge vector: chain the harmonics' Jacobian and write d/d(vector)
+            T gk[YSEG];
+#pragma unroll
+            for (int k = 0; k < YSEG; ++k) {{
+              T s = T(0);
+#pragma unroll
+              for (int wp = 0; wp < cfg::NCONS_WARPS; ++wp) s += part[wp * YSEG + k];
+              gk[k] = s;
+            }}
+            const T* vsrc = y + (size_t)pm.yr * 3;
+            T gv[3];
+            fasteq_sh::vjp(vsrc[0], vsrc[1], vsrc[2], gk, gv);
+            T* dst = gy + (size_t)pm.yr * 3;
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {{ if (GY_ATOMIC) red_add(dst + k, gv[k]); else dst[k] = gv[k]; }}
+          }} else {{
           T* dst = gy + (size_t)pm.yr * YSEG;
 #pragma unroll
           for (int k = 0; k < YSEG; ++k) {{
@@ -615,6 +634,7 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
 #pragma unroll
             for (int wp = 0; wp < cfg::NCONS_WARPS; ++wp) s += part[wp * YSEG + k];
             if (GY_ATOMIC) red_add(dst + k, s); else dst[k] = s;
+          }}
           }}
         }}
       }}
@@ -804,7 +824,7 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
     if need_gx and spec.x_indexed:
         zero.append("if (gx) { e = cudaMemsetAsync(gx, 0, (size_t)gh->x_rows * XSEG * U * sizeof(T), s); if (e != cudaSuccess) return cuda_fail(e); }")
     if need_gy:
-        ycols = "YSEG * U" if spec.y_vec else "YSEG"
+        ycols = "YSEG * U" if spec.y_vec else ("3" if spec.y_sh else "YSEG")
         if spec.y_indexed:
             zero.append(f"if (gy) {{ e = cudaMemsetAsync(gy, 0, (size_t)gh->y_rows * {ycols} * sizeof(T), s); if (e != cudaSuccess) return cuda_fail(e); }}")
         elif not spec.y_vec:

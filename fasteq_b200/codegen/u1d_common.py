@@ -37,6 +37,8 @@ class U1DSpec:
     x_indexed: bool = True      # x rows gathered through an index
     y_indexed: bool = False     # y rows gathered through an index
     scattered: bool = True      # output rows summed over the edges of a receiver segment
+    y_sh: tuple = ()            # (degrees, normalize, normalization): y rows are edge vectors [rows, 3] and the
+                                # kernel evaluates their spherical harmonics itself (scalar-y mode only)
 
     @property
     def ctype(self) -> str:
@@ -49,12 +51,12 @@ class U1DSpec:
     def key(self, extra: str = "") -> str:
         h = hashlib.sha256()
         h.update(repr((self.paths, self.w_segs, self.x_segs, self.y_segs, self.out_segs, self.u, self.dtype,
-                       self.y_vec, self.w_shared, self.x_indexed, self.y_indexed, self.scattered, extra)).encode())
+                       self.y_vec, self.w_shared, self.x_indexed, self.y_indexed, self.scattered, self.y_sh, extra)).encode())
         return h.hexdigest()[:16]
 
 
 def make_spec(i_list, j_list, k_list, v_list, coeff_list, *, w_segs, x_segs, y_segs, out_segs, u, dtype,
-              y_vec=False, w_shared=False, x_indexed=True, y_indexed=False, scattered=True) -> U1DSpec:
+              y_vec=False, w_shared=False, x_indexed=True, y_indexed=False, scattered=True, y_sh=()) -> U1DSpec:
     cs = np.asarray(coeff_list, dtype=np.float64)
     if dtype == "f32":
         cs = cs.astype(np.float32).astype(np.float64)  # the literal the kernel will hold
@@ -62,8 +64,15 @@ def make_spec(i_list, j_list, k_list, v_list, coeff_list, *, w_segs, x_segs, y_s
     for (i, j, k, v, _) in paths:
         if not (0 <= i < w_segs and 0 <= j < x_segs and 0 <= k < y_segs and 0 <= v < out_segs):
             raise ValueError("path index outside its operand's segment count")
+    if y_sh:
+        ls, normalize, normalization = y_sh
+        y_sh = (tuple(int(l) for l in ls), bool(normalize), str(normalization))
+        if y_vec or y_indexed:
+            raise ValueError("in-kernel spherical harmonics need a per-edge scalar y operand (no channel axis, no gather)")
+        if sum(2 * l + 1 for l in y_sh[0]) != int(y_segs):
+            raise ValueError("the spherical-harmonic degrees do not add up to the y segment count")
     return U1DSpec(paths, int(w_segs), int(x_segs), int(y_segs), int(out_segs), int(u), dtype,
-                   bool(y_vec), bool(w_shared), bool(x_indexed), bool(y_indexed), bool(scattered))
+                   bool(y_vec), bool(w_shared), bool(x_indexed), bool(y_indexed), bool(scattered), tuple(y_sh))
 
 
 @dataclass

@@ -8,8 +8,9 @@
 // shared memory.
 //
 // The including file must define namespace cfg { T, U, CT, WSEG, XSEG, YSEG,
-// OSEG, STAGES, PIPES, Y_VEC, W_SHARED, X_INDEXED, Y_INDEXED, SCATTERED, NCONS_WARPS,
-// STAGE_EXTRA_BYTES, EMIT_EMPTY_ROWS, BEGIN_PER_SEGMENT }.
+// OSEG, STAGES, PIPES, Y_VEC, W_SHARED, X_INDEXED, Y_INDEXED, SCATTERED, Y_SH, NCONS_WARPS,
+// STAGE_EXTRA_BYTES, EMIT_EMPTY_ROWS, BEGIN_PER_SEGMENT } and namespace fasteq_sh { eval, vjp }
+// (spherical harmonics of an edge vector and their vector-Jacobian product; stubs unless Y_SH).
 #pragma once
 #include "fasteq_device.cuh"
 
@@ -103,6 +104,7 @@ struct Producer {
     Meta m; m.row = row; m.flags = flags; m.ct = ct; m.e = e; m.xr = xr; m.yr = yr; m.pad0 = 0; m.pad1 = 0;
     *reinterpret_cast<Meta*>(st + OFF_META) = m;
     const bool data = (flags & F_DATA) != 0;
+    if (cfg::Y_SH && data) sh_row(st, yr);     // plain stores, published by the arrive below
     mbar_arrive_expect_tx(&full[stage], data ? tx_bytes(valid) : 0u);
     if (data) {
       const uint32_t piece = (uint32_t)(valid * sizeof(T));
@@ -120,13 +122,23 @@ struct Producer {
         const T* src = y + (size_t)yr * YSEG * U;
         if (FULL_ROW) bulk_g2s(st + OFF_Y, src, (uint32_t)(YSEG * U * sizeof(T)), &full[stage]);
         else for (int s = 0; s < YSEG; ++s) bulk_g2s(st + OFF_Y + (size_t)s * CT * sizeof(T), src + (size_t)s * U + ct * CT, piece, &full[stage]);
-      } else {
+      } else if (!cfg::Y_SH) {
         const T* src = y + (size_t)yr * YSEG;
 #pragma unroll
         for (int k = 0; k < YSEG; ++k) cp_async_elem(st + OFF_Y + k * sizeof(T), src + k);
       }
     }
     cp_async_arrive_noinc(&full[stage]);
+  }
+
+  // Y_SH: the y operand is the edge vector; its harmonics are evaluated here, into the stage's y row
+  __device__ __forceinline__ void sh_row(unsigned char* st, int yr) {
+    const T* v = y + (size_t)yr * 3;
+    T sh[YSEG];
+    fasteq_sh::eval(v[0], v[1], v[2], sh);
+    T* dst = reinterpret_cast<T*>(st + OFF_Y);
+#pragma unroll
+    for (int k = 0; k < YSEG; ++k) dst[k] = sh[k];
   }
 
   // Fallback path (operands not 16-byte aligned): the whole warp copies one edge with 4/8-byte cp.async.
@@ -140,6 +152,7 @@ struct Producer {
       if (it >= (uint32_t)STAGES) flush(st);
       Meta m; m.row = row; m.flags = flags; m.ct = ct; m.e = e; m.xr = xr; m.yr = yr; m.pad0 = 0; m.pad1 = 0;
       *reinterpret_cast<Meta*>(st + OFF_META) = m;
+      if (cfg::Y_SH && (flags & F_DATA)) sh_row(st, yr);
       mbar_arrive_expect_tx(&full[stage], 0u);
     }
     __syncwarp();
@@ -148,7 +161,7 @@ struct Producer {
       if (!cfg::W_SHARED) copy_tile(st + OFF_W, w + (size_t)e * WSEG * U, WSEG, ct, valid, false, &full[stage], lane);
       copy_tile(st + OFF_X, x + (size_t)xr * XSEG * U, XSEG, ct, valid, false, &full[stage], lane);
       if (cfg::Y_VEC) copy_tile(st + OFF_Y, y + (size_t)yr * YSEG * U, YSEG, ct, valid, false, &full[stage], lane);
-      else for (int k = lane; k < YSEG; k += 32) cp_async_elem(st + OFF_Y + k * sizeof(T), y + (size_t)yr * YSEG + k);
+      else if (!cfg::Y_SH) for (int k = lane; k < YSEG; k += 32) cp_async_elem(st + OFF_Y + k * sizeof(T), y + (size_t)yr * YSEG + k);
     }
     cp_async_arrive_noinc(&full[stage]);
     ++it;

@@ -76,13 +76,14 @@ class InteractionLayer(torch.nn.Module):
         self.linear_out = SO3Linear(hidden, hidden)
         self.inv_neighbors = 1.0 / avg_num_neighbors
 
-    def forward(self, h, species, edge_sh, edge_radial, edge_dst, edge_src, halo=None):
+    def forward(self, h, species, edge_sh, edge_radial, edge_dst, edge_src, halo=None, edge_vec=None):
         up = self.linear_up(h)
         n_owned = up.shape[0]
         if halo is not None:
             up = halo(up)                    # owned rows, then ghost rows of the senders other ranks own
         w = self.radial(edge_radial)
-        msg = self.conv_tp(up, edge_sh, w, edge_dst, edge_src)[:n_owned]
+        # edge_vec given: the tensor-product kernel evaluates the spherical harmonics of the edge itself
+        msg = self.conv_tp(up, edge_sh, w, edge_dst, edge_src, edge_vec=edge_vec)[:n_owned]
         mid = self.linear_mid(msg) * self.inv_neighbors
         prod = self.product(mid, species)
         return self.linear_out(prod)
@@ -91,8 +92,9 @@ class InteractionLayer(torch.nn.Module):
 class MACEStyleModel(torch.nn.Module):
     def __init__(self, num_species: int = 4, channels: int = 128, hidden_lmax: int = 1, sh_lmax: int = 3, lmax_mid: int = 3,
                  num_layers: int = 2, r_max: float = 5.0, num_basis: int = 8, radial_hidden=(64, 64, 64), correlation: int = 3,
-                 avg_num_neighbors: float = 52.0, envelope_p: int = 5, tp_parity: Optional[str] = "natural"):
+                 avg_num_neighbors: float = 52.0, envelope_p: int = 5, tp_parity: Optional[str] = "natural", fuse_sh: bool = True):
         super().__init__()
+        self.fuse_sh = fuse_sh                # edge harmonics inside the tensor-product kernels (no [E, 16] tensor)
         self.r_max, self.num_basis, self.envelope_p, self.channels = r_max, num_basis, envelope_p, channels
         hidden = Irreps([(channels, (l, (-1) ** l)) for l in range(hidden_lmax + 1)])
         self.hidden = hidden
@@ -108,20 +110,23 @@ class MACEStyleModel(torch.nn.Module):
         self.readouts = torch.nn.ParameterList(torch.nn.Parameter(torch.randn(channels) / math.sqrt(channels)) for _ in range(num_layers))
 
     def edge_features(self, pos, edge_src, edge_dst, edge_shift):
+        """(harmonics or None, radial basis, edge vectors or None): with ``fuse_sh`` the vectors go to the layers."""
         vec = pos[edge_src] + edge_shift - pos[edge_dst]
         r = vec.norm(dim=-1)
         radial = bessel_basis(r, self.r_max, self.num_basis) * polynomial_cutoff(r, self.r_max, self.envelope_p).unsqueeze(-1)
-        return self.sh(vec), radial
+        if self.fuse_sh and vec.is_cuda:
+            return None, radial, vec
+        return self.sh(vec), radial, None
 
     def node_energies(self, pos, species, edge_src, edge_dst, edge_shift, halo=None):
         """``halo`` (a ``parallel.HaloExchange``) extends per-node tensors with ghost rows; ``pos`` and
         ``species`` then hold the owned nodes only and the edge indices are local ids."""
         pos_ext = pos if halo is None else halo(pos)
-        edge_sh, edge_radial = self.edge_features(pos_ext, edge_src, edge_dst, edge_shift)
+        edge_sh, edge_radial, edge_vec = self.edge_features(pos_ext, edge_src, edge_dst, edge_shift)
         h = self.embedding[species]
         e = pos.new_zeros(pos.shape[0])
         for layer, ro in zip(self.layers, self.readouts):
-            h = layer(h, species, edge_sh, edge_radial, edge_dst, edge_src, halo)
+            h = layer(h, species, edge_sh, edge_radial, edge_dst, edge_src, halo, edge_vec)
             e = e + h[:, : self.channels] @ ro          # scalars are the first segment of the ir_mul row
         return e
 

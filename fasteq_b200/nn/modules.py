@@ -41,17 +41,39 @@ class ChannelwiseTensorProduct(torch.nn.Module):
         self.layout = layout
         self._meta = {}
 
-    def meta(self, dtype, device):
-        key = (dtype, str(device))
+    def meta(self, dtype, device, y_sh=()):
+        key = (dtype, str(device), tuple(y_sh))
         if key not in self._meta:
-            self._meta[key] = self.descriptor.meta(dtype, device)
+            m = self.descriptor.meta(dtype, device)
+            if y_sh:
+                m["y_sh"] = tuple(y_sh)
+            self._meta[key] = m
         return self._meta[key]
 
-    def forward(self, x, edge_attr, edge_weight, edge_dst, edge_src):
+    def sh_degrees(self):
+        """Degrees of ``irreps_in2`` when it is a set of spherical harmonics (one copy of each ``l`` with
+        parity ``(-1)^l``), which is what the in-kernel evaluation from edge vectors needs."""
+        ls = []
+        for b in self.irreps_in2:
+            if b.mul != 1 or b.ir.p != (-1) ** b.ir.l:
+                raise ValueError(f"irreps_in2 = {self.irreps_in2} is not a set of spherical harmonics")
+            ls.append(b.ir.l)
+        return tuple(ls)
+
+    def forward(self, x, edge_attr, edge_weight, edge_dst, edge_src, edge_vec=None, sh_normalize: bool = True,
+                sh_normalization: str = "component"):
+        """``edge_attr`` are the spherical harmonics of the edges; alternatively pass ``edge_attr=None`` and the
+        edge vectors ``edge_vec [E, 3]``: the kernel then evaluates the harmonics itself (and the backward
+        returns the gradient with respect to the vectors)."""
         if self.layout == "mul_ir":
             x = mul_ir_to_ir_mul(x, self.irreps_in1)
-        out = fast_uniform1d_jit(edge_weight.contiguous(), x.contiguous(), edge_attr.contiguous(), {1: edge_src}, {0: edge_dst},
-                                 self.meta(x.dtype, x.device))
+        if edge_vec is not None:
+            if edge_attr is not None:
+                raise ValueError("pass either edge_attr or edge_vec")
+            y, meta = edge_vec, self.meta(x.dtype, x.device, (self.sh_degrees(), sh_normalize, sh_normalization))
+        else:
+            y, meta = edge_attr, self.meta(x.dtype, x.device)
+        out = fast_uniform1d_jit(edge_weight.contiguous(), x.contiguous(), y.contiguous(), {1: edge_src}, {0: edge_dst}, meta)
         if self.layout == "mul_ir":
             out = ir_mul_to_mul_ir(out, self.irreps_out)
         return out

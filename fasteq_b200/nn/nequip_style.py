@@ -45,20 +45,22 @@ class NequIPStyleLayer(torch.nn.Module):
         self.inv_neighbors = 1.0 / avg_num_neighbors
         self.irreps_out = hid
 
-    def forward(self, h, edge_sh, edge_radial, edge_dst, edge_src, halo=None):
+    def forward(self, h, edge_sh, edge_radial, edge_dst, edge_src, halo=None, edge_vec=None):
         up = self.linear_1(h)
         n_owned = up.shape[0]
         if halo is not None:
             up = halo(up)
-        msg = self.conv_tp(up, edge_sh, self.radial(edge_radial), edge_dst, edge_src)[:n_owned]
+        msg = self.conv_tp(up, edge_sh, self.radial(edge_radial), edge_dst, edge_src, edge_vec=edge_vec)[:n_owned]
         pre = self.linear_2(msg) * self.inv_neighbors + self.self_connection(h)
         return gate(pre, self.gate_spec)
 
 
 class NequIPStyleModel(torch.nn.Module):
     def __init__(self, num_species: int = 2, channels: int = 64, lmax: int = 2, sh_lmax: int = 2, num_layers: int = 4,
-                 r_max: float = 4.0, num_basis: int = 8, radial_hidden=(64, 64), avg_num_neighbors: float = 27.0, envelope_p: int = 5):
+                 r_max: float = 4.0, num_basis: int = 8, radial_hidden=(64, 64), avg_num_neighbors: float = 27.0, envelope_p: int = 5,
+                 fuse_sh: bool = True):
         super().__init__()
+        self.fuse_sh = fuse_sh                # edge harmonics inside the tensor-product kernels
         self.r_max, self.num_basis, self.envelope_p, self.channels = r_max, num_basis, envelope_p, channels
         self.embedding = torch.nn.Parameter(torch.randn(num_species, channels))
         self.sh = SphericalHarmonics(list(range(sh_lmax + 1)), True, "component")
@@ -75,10 +77,11 @@ class NequIPStyleModel(torch.nn.Module):
         vec = pos_ext[edge_src] + edge_shift - pos_ext[edge_dst]
         r = vec.norm(dim=-1)
         radial = bessel_basis(r, self.r_max, self.num_basis) * polynomial_cutoff(r, self.r_max, self.envelope_p).unsqueeze(-1)
-        edge_sh = self.sh(vec)
+        fused = self.fuse_sh and vec.is_cuda
+        edge_sh = None if fused else self.sh(vec)
         h = self.embedding[species]
         for layer in self.layers:
-            h = layer(h, edge_sh, radial, edge_dst, edge_src, halo)
+            h = layer(h, edge_sh, radial, edge_dst, edge_src, halo, vec if fused else None)
         return h[:, : self.channels] @ self.readout
 
     def forward(self, pos, species, edge_src, edge_dst, edge_shift, forces: bool = True, halo=None):

@@ -187,14 +187,20 @@ class _Call:
         self.w_segs, self.x_segs = int(meta["w_seg_num"]), int(meta["x_seg_num"])
         self.y_segs, self.out_segs = int(meta["y_seg_num"]), int(meta["out_seg_num"])
         size_list = meta["size_list"]
+        # extension of the reference's meta: "y_sh" = (degrees, normalize, normalization) says that the y
+        # operand holds edge vectors [rows, 3] whose spherical harmonics the kernel evaluates itself
+        self.y_sh = tuple(meta["y_sh"]) if meta.get("y_sh") else ()
         y_cols = int(size_list[2]) // self.y_segs
         if y_cols not in (1, self.u):
             raise ValueError("y must carry 1 or u_dim values per segment")
         self.y_vec = y_cols != 1
-        for name, t, cols in (("w", w, self.w_segs * self.u), ("x", x, self.x_segs * self.u), ("y", y, self.y_segs * y_cols)):
+        y_row = 3 if self.y_sh else self.y_segs * y_cols
+        if self.y_sh and (self.y_vec or y.shape[-1] != 3):
+            raise ValueError("with in-kernel spherical harmonics y must be the edge vectors [rows, 3]")
+        for name, t, cols in (("w", w, self.w_segs * self.u), ("x", x, self.x_segs * self.u), ("y", y, y_row)):
             if t.dim() < 2 or t.numel() % cols != 0:
                 raise ValueError(f"{name} has {t.numel()} elements, not a multiple of {cols}")
-        self.w_rows, self.x_rows, self.y_rows = w.numel() // (self.w_segs * self.u), x.numel() // (self.x_segs * self.u), y.numel() // (self.y_segs * y_cols)
+        self.w_rows, self.x_rows, self.y_rows = w.numel() // (self.w_segs * self.u), x.numel() // (self.x_segs * self.u), y.numel() // y_row
         self.x_indexed, self.y_indexed = 1 in input_indices, 2 in input_indices
         self.scattered = 0 in output_indices
         src = input_indices.get(1, input_indices.get(2))
@@ -220,14 +226,14 @@ class _Call:
         self.dtype = _dtype_str(w)
         skey = tuple((id(meta[k]), getattr(meta[k], "_version", 0)) for k in ("i_list", "j_list", "k_list", "v_list", "coeff_list")) + (
             self.w_segs, self.x_segs, self.y_segs, self.out_segs, self.u, self.dtype, self.y_vec, self.w_shared,
-            self.x_indexed, self.y_indexed, self.scattered)
+            self.x_indexed, self.y_indexed, self.scattered, self.y_sh)
         hit = _SPEC_CACHE.get(skey)
         if hit is None:
             spec = make_spec(
                 _np(meta["i_list"]), _np(meta["j_list"]), _np(meta["k_list"]), _np(meta["v_list"]), _np(meta["coeff_list"], True),
                 w_segs=self.w_segs, x_segs=self.x_segs, y_segs=self.y_segs, out_segs=self.out_segs, u=self.u,
                 dtype=self.dtype, y_vec=self.y_vec, w_shared=self.w_shared, x_indexed=self.x_indexed,
-                y_indexed=self.y_indexed, scattered=self.scattered)
+                y_indexed=self.y_indexed, scattered=self.scattered, y_sh=self.y_sh)
             if len(_SPEC_CACHE) > 256:
                 _SPEC_CACHE.clear()
             # the entry holds the table objects so their ids stay unique while it exists
@@ -382,7 +388,14 @@ class FastUniform1dJITFunction(torch.autograd.Function):
         needs = tuple(bool(n) for n in ctx.needs_input_grad[:3])
         if not any(needs):
             return None, None, None, None, None, None
-        gw, gx, gy = FastUniform1dBackwardFunction.apply(grad_out.contiguous(), w, x, y, ctx.call, needs)
+        if ctx.call.y_sh:
+            # not trilinear in the edge vector: the composed second backward does not apply
+            if torch.is_grad_enabled() and any(t.requires_grad for t in (grad_out, w, x, y)):
+                raise RuntimeError("fast_uniform1d_jit: no second-order gradient with in-kernel spherical harmonics; "
+                                   "pass the harmonics as the y operand instead")
+            gw, gx, gy = _run_bwd(ctx.call, grad_out.contiguous(), w, x, y, needs)
+        else:
+            gw, gx, gy = FastUniform1dBackwardFunction.apply(grad_out.contiguous(), w, x, y, ctx.call, needs)
         return (gw if needs[0] else None), (gx if needs[1] else None), (gy if needs[2] else None), None, None, None
 
 

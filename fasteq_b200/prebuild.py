@@ -52,6 +52,10 @@ def model_jobs(dtype: str = "f32", kind: str = "mace", **model_kwargs):
         spec = make_spec(d.i_list, d.j_list, d.k_list, d.v_list, d.coeff_list, w_segs=d.w_seg_num, x_segs=d.x_seg_num,
                          y_segs=d.y_seg_num, out_segs=d.out_seg_num, u=d.u_dim, dtype=dtype)
         u1d += [(spec, "fwd", (False, False, False)), (spec, "bwd", (True, True, True)), (spec, "bwd", (True, False, True))]
+        if getattr(model, "fuse_sh", False):      # the variants that evaluate the edge harmonics in the kernel
+            import dataclasses
+            fused = dataclasses.replace(spec, y_sh=(layer.conv_tp.sh_degrees(), True, "component"))
+            u1d += [(fused, "fwd", (False, False, False)), (fused, "bwd", (True, True, True)), (fused, "bwd", (True, False, True))]
         if hasattr(layer, "product"):
             s = layer.product.descriptor
             sp = make_stc_spec(s.paths, s.coeffs, x1_segs=s.x1_segs, x0_segs=s.x0_segs, out_segs=s.out_segs, u=s.u_dim, dtype=dtype)

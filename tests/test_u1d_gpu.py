@@ -193,3 +193,36 @@ def test_double_backward_matches_torch_autograd():
     ref = loss(lambda a, b, c: u1d_scatter(a, b, c, d, src, dst, N), "cpu")
     for name, a, b in zip(("w", "x", "y"), got, ref):
         _close(a, b.numpy(), torch.float64, f"second-order gradient wrt {name}")
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float64, 1e-11)])
+@pytest.mark.parametrize("in1,lmax", [("32x0e+32x1o", 2), ("128x0e+128x1o", 3)])
+def test_in_kernel_spherical_harmonics_match_the_two_step_path(in1, lmax, dtype, tol):
+    """y = edge vectors, harmonics evaluated by the producer: same output and same gradients (w, x and the
+    vectors) as harmonics computed first and passed as the y operand."""
+    from fasteq_b200.nn.modules import ChannelwiseTensorProduct
+    from fasteq_b200.ops.spherical_harmonics import SphericalHarmonics
+    sh_ir = Irreps.spherical_harmonics(lmax)
+    io, ins = full_channelwise_instructions(in1, sh_ir, lmax)
+    tp = ChannelwiseTensorProduct(in1, sh_ir, io, ins)
+    d = tp.descriptor
+    g = torch.Generator().manual_seed(11)
+    N, E = 57, 700
+    dst = torch.sort(torch.randint(0, N, (E,), generator=g)).values.int().cuda()
+    src = torch.randint(0, N, (E,), generator=g).int().cuda()
+    w = torch.randn(E, d.w_seg_num * d.u_dim, generator=g, dtype=torch.float64).to(dtype).cuda().requires_grad_(True)
+    x = torch.randn(N, d.x_seg_num * d.u_dim, generator=g, dtype=torch.float64).to(dtype).cuda().requires_grad_(True)
+    vec = (torch.randn(E, 3, generator=g, dtype=torch.float64) * 2.0).to(dtype).cuda().requires_grad_(True)
+    r = torch.randn(N, d.out_seg_num * d.u_dim, generator=g, dtype=torch.float64).to(dtype).cuda()
+    sh = SphericalHarmonics(list(range(lmax + 1)), True, "component")
+    out_ref = tp(x, sh(vec), w, dst, src)
+    ref = torch.autograd.grad(out_ref, (w, x, vec), r)
+    out = tp(x, None, w, dst, src, edge_vec=vec)
+    got = torch.autograd.grad(out, (w, x, vec), r)
+    scale = lambda t: float(t.abs().max())
+    assert float((out - out_ref).abs().max()) <= tol * scale(out_ref)
+    for a, b in zip(got, ref):
+        assert a.shape == b.shape and float((a - b).abs().max()) <= tol * scale(b)
+    with pytest.raises(RuntimeError):
+        o = tp(x, None, w, dst, src, edge_vec=vec)
+        (gv,) = torch.autograd.grad(o, vec, r, create_graph=True)
