@@ -20,6 +20,7 @@ import torch
 from ..descriptors import full_channelwise_instructions
 from ..irreps import Irreps
 from ..ops.dense import dense
+from ..ops.edge_geometry import edge_geometry, edge_geometry_usable
 from ..ops.radial_chain import radial_chain
 from ..ops.spherical_harmonics import SphericalHarmonics
 from .modules import ChannelwiseTensorProduct, SO3Linear, SymmetricContraction
@@ -92,8 +93,10 @@ class InteractionLayer(torch.nn.Module):
 class MACEStyleModel(torch.nn.Module):
     def __init__(self, num_species: int = 4, channels: int = 128, hidden_lmax: int = 1, sh_lmax: int = 3, lmax_mid: int = 3,
                  num_layers: int = 2, r_max: float = 5.0, num_basis: int = 8, radial_hidden=(64, 64, 64), correlation: int = 3,
-                 avg_num_neighbors: float = 52.0, envelope_p: int = 5, tp_parity: Optional[str] = "natural", fuse_sh: bool = True):
+                 avg_num_neighbors: float = 52.0, envelope_p: int = 5, tp_parity: Optional[str] = "natural", fuse_sh: bool = True,
+                 fuse_geometry: bool = True):
         super().__init__()
+        self.fuse_geometry = fuse_geometry    # edge vectors + radial basis (and their force-pass gradient) as one kernel each
         self.fuse_sh = fuse_sh                # edge harmonics inside the tensor-product kernels (no [E, 16] tensor)
         self.r_max, self.num_basis, self.envelope_p, self.channels = r_max, num_basis, envelope_p, channels
         hidden = Irreps([(channels, (l, (-1) ** l)) for l in range(hidden_lmax + 1)])
@@ -111,9 +114,12 @@ class MACEStyleModel(torch.nn.Module):
 
     def edge_features(self, pos, edge_src, edge_dst, edge_shift):
         """(harmonics or None, radial basis, edge vectors or None): with ``fuse_sh`` the vectors go to the layers."""
-        vec = pos[edge_src] + edge_shift - pos[edge_dst]
-        r = vec.norm(dim=-1)
-        radial = bessel_basis(r, self.r_max, self.num_basis) * polynomial_cutoff(r, self.r_max, self.envelope_p).unsqueeze(-1)
+        if self.fuse_geometry and edge_geometry_usable(pos, self.num_basis):
+            vec, radial = edge_geometry(pos, edge_src, edge_dst, edge_shift, self.r_max, self.num_basis, self.envelope_p)
+        else:
+            vec = pos[edge_src] + edge_shift - pos[edge_dst]
+            r = vec.norm(dim=-1)
+            radial = bessel_basis(r, self.r_max, self.num_basis) * polynomial_cutoff(r, self.r_max, self.envelope_p).unsqueeze(-1)
         if self.fuse_sh and vec.is_cuda:
             return None, radial, vec
         return self.sh(vec), radial, None

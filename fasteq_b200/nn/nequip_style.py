@@ -19,6 +19,7 @@ from ..descriptors import full_channelwise_instructions
 from ..irreps import Irreps
 from ..ops.gate import GateSpec, gate
 from ..ops.spherical_harmonics import SphericalHarmonics
+from ..ops.edge_geometry import edge_geometry, edge_geometry_usable
 from .mace_style import RadialMLP, bessel_basis, polynomial_cutoff
 from .modules import ChannelwiseTensorProduct, SO3Linear
 
@@ -58,8 +59,9 @@ class NequIPStyleLayer(torch.nn.Module):
 class NequIPStyleModel(torch.nn.Module):
     def __init__(self, num_species: int = 2, channels: int = 64, lmax: int = 2, sh_lmax: int = 2, num_layers: int = 4,
                  r_max: float = 4.0, num_basis: int = 8, radial_hidden=(64, 64), avg_num_neighbors: float = 27.0, envelope_p: int = 5,
-                 fuse_sh: bool = True):
+                 fuse_sh: bool = True, fuse_geometry: bool = True):
         super().__init__()
+        self.fuse_geometry = fuse_geometry    # edge vectors + radial basis as one kernel per direction
         self.fuse_sh = fuse_sh                # edge harmonics inside the tensor-product kernels
         self.r_max, self.num_basis, self.envelope_p, self.channels = r_max, num_basis, envelope_p, channels
         self.embedding = torch.nn.Parameter(torch.randn(num_species, channels))
@@ -74,9 +76,12 @@ class NequIPStyleModel(torch.nn.Module):
 
     def node_energies(self, pos, species, edge_src, edge_dst, edge_shift, halo=None):
         pos_ext = pos if halo is None else halo(pos)
-        vec = pos_ext[edge_src] + edge_shift - pos_ext[edge_dst]
-        r = vec.norm(dim=-1)
-        radial = bessel_basis(r, self.r_max, self.num_basis) * polynomial_cutoff(r, self.r_max, self.envelope_p).unsqueeze(-1)
+        if self.fuse_geometry and edge_geometry_usable(pos_ext, self.num_basis):
+            vec, radial = edge_geometry(pos_ext, edge_src, edge_dst, edge_shift, self.r_max, self.num_basis, self.envelope_p)
+        else:
+            vec = pos_ext[edge_src] + edge_shift - pos_ext[edge_dst]
+            r = vec.norm(dim=-1)
+            radial = bessel_basis(r, self.r_max, self.num_basis) * polynomial_cutoff(r, self.r_max, self.envelope_p).unsqueeze(-1)
         fused = self.fuse_sh and vec.is_cuda
         edge_sh = None if fused else self.sh(vec)
         h = self.embedding[species]

@@ -280,6 +280,18 @@ int fasteq_radial_chain_forward(const float* basis, int64_t n_edges, int32_t n_b
 int fasteq_radial_chain_backward(const float* grad_out, const float* deriv, const float* basis, int64_t n_edges,
                                  int32_t n_basis, const float* w_first, const float* const* w_hidden /* host */,
                                  int32_t n_hidden, float* grad_basis, fasteq_stream_t stream);
+/* Edge geometry of a radius graph: vec[e] = (pos[src[e]] + shift[e]) - pos[dst[e]] and the radial basis
+ * basis[e, n] = sqrt(2 / r_max) sin((n+1) pi r / r_max) / r * env(r / r_max), env the degree-p polynomial cutoff
+ * (the embedding of NequIP / MACE models, .../nequip/nn/embedding/_edge.py:174-189, cutoffs.py:17-27; the
+ * reference leaves it to torch modules).  The backward takes dE/dvec and / or dE/dbasis (either may be NULL),
+ * and overwrites grad_pos [n_nodes, 3] (accumulated with red.global.add over senders and receivers).
+ * dtype: fasteq_dtype of pos / shift / vec / basis; n_basis <= 16. */
+int fasteq_edge_geometry_forward(int32_t dtype, const void* pos, const int32_t* src, const int32_t* dst, const void* shift,
+                                 int64_t n_edges, double r_max, int32_t n_basis, int32_t envelope_p, void* vec, void* basis,
+                                 fasteq_stream_t stream);
+int fasteq_edge_geometry_backward(int32_t dtype, const void* pos, const int32_t* src, const int32_t* dst, const void* shift,
+                                  const void* grad_vec, const void* grad_basis, int64_t n_edges, int64_t n_nodes, double r_max,
+                                  int32_t n_basis, int32_t envelope_p, void* grad_pos, fasteq_stream_t stream);
 /* Reads and clears the status word of the tensor-core kernels (synchronises). */
 int fasteq_tensorcore_device_status(int32_t* code /* host */);
 
