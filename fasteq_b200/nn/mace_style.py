@@ -84,8 +84,10 @@ class InteractionLayer(torch.nn.Module):
             up = halo(up)                    # owned rows, then ghost rows of the senders other ranks own
         w = self.radial(edge_radial)
         # edge_vec given: the tensor-product kernel evaluates the spherical harmonics of the edge itself
-        msg = self.conv_tp(up, edge_sh, w, edge_dst, edge_src, edge_vec=edge_vec)[:n_owned]
-        mid = self.linear_mid(msg) * self.inv_neighbors
+        msg = self.conv_tp(up, edge_sh, w, edge_dst, edge_src, edge_vec=edge_vec)
+        if msg.shape[0] != n_owned:
+            msg = msg[:n_owned]              # rows of ghost receivers (no edges end there)
+        mid = self.linear_mid(msg, self.linear_mid.weight * self.inv_neighbors)   # 1 / <neighbours> folded into the small weight
         prod = self.product(mid, species)
         return self.linear_out(prod)
 

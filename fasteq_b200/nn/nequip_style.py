@@ -51,8 +51,10 @@ class NequIPStyleLayer(torch.nn.Module):
         n_owned = up.shape[0]
         if halo is not None:
             up = halo(up)
-        msg = self.conv_tp(up, edge_sh, self.radial(edge_radial), edge_dst, edge_src, edge_vec=edge_vec)[:n_owned]
-        pre = self.linear_2(msg) * self.inv_neighbors + self.self_connection(h)
+        msg = self.conv_tp(up, edge_sh, self.radial(edge_radial), edge_dst, edge_src, edge_vec=edge_vec)
+        if msg.shape[0] != n_owned:
+            msg = msg[:n_owned]
+        pre = self.linear_2(msg, self.linear_2.weight * self.inv_neighbors) + self.self_connection(h)
         return gate(pre, self.gate_spec)
 
 
