@@ -372,7 +372,8 @@ def reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": eps, "unit": "edges/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32" if dtype == torch.float32 else "f64", "data": "synthetic",
-        "config": config_dict(args.workload, inp, args.gpus),
+        # the arm's config is the GPU arm's (same workload); what was actually timed is described in `sample`
+        "config": config_dict(args.workload, dict(inp, n_boxes=args.boxes or boxes), args.gpus),
         "cpu_baseline": {"value": eps, "unit": "edges/s", "cores": threads, "kind": "port", "sample": sample,
                          "torch_threads": torch.get_num_threads(), "os_cpu_count": os.cpu_count()},
         "e2e": {"value": eps, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

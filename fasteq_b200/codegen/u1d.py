@@ -73,6 +73,8 @@ def default_tuning(spec: U1DSpec, direction: str) -> Tuning:
             pipes = 4
             if small:                                          # few bytes per stage: deeper rings, two such CTAs
                 stages = 10
+        elif packed and big and ct == 128:                     # two thread groups per pipeline: two pipelines, shorter rings
+            pipes, stages = 2, 5
         per_pipe = 256 + stages * _stage_bytes(spec, ct, 0)
         fit = max(1, _SMEM_BUDGET // per_pipe)                 # pipelines one SM can hold
         if fit < pipes:
