@@ -240,16 +240,18 @@ __global__ void pack_weights_kernel(const float* __restrict__ W, float* __restri
   }
 }
 
-int launch_tensorcore(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const void* a, void* c, cudaStream_t s,
-                      bool* used) {
+// `packed` (optional): the output of pack_weights_kernel for this problem and direction, prepared earlier by
+// fasteq_eqlinear_pack; when NULL the weights are packed into a stream-ordered temporary first.
+int launch_tensorcore(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const void* packed, const void* a, void* c,
+                      cudaStream_t s, bool* used) {
   *used = false;
   GroupTable tab; bool covers = true;
   int rc = build_table(p, dgrad, &tab, &covers);
   if (rc != FASTEQ_OK) return rc;
   const int K = dgrad ? p->v : p->u, N = dgrad ? p->u : p->v;
   const int a_rows = dgrad ? p->out_rows : p->in_rows, c_rows = dgrad ? p->in_rows : p->out_rows;
-  if (p->batch == 0 || !w || !a || !c) return FASTEQ_OK;   // the FMA path reports the error / no-op
-  if (!tc::supported(p->batch, a_rows, K, p->num_paths, N, c_rows, a, w, c)) return FASTEQ_OK;
+  if (p->batch == 0 || (!w && !packed) || !a || !c) return FASTEQ_OK;   // the FMA path reports the error / no-op
+  if (!tc::supported(p->batch, a_rows, K, p->num_paths, N, c_rows, a, packed ? packed : w, c)) return FASTEQ_OK;
   tc::TcTable t{};
   t.n_groups = tab.n_groups; t.n_items = 0;
   for (int g = 0; g < tab.n_groups; ++g) {
@@ -261,17 +263,44 @@ int launch_tensorcore(const fasteq_eqlinear_problem* p, bool dgrad, const void* 
   for (int q = 0; q < tab.n_paths; ++q) { t.path_a_row[q] = tab.path_a_row[q]; t.path_w[q] = q; }   // packed in table order
   float* bt = nullptr;
   const long long total = (long long)p->num_paths * N * K;
-  cudaError_t e = cudaMallocAsync((void**)&bt, (size_t)total * 2 * sizeof(float), s);
-  if (e != cudaSuccess) return cuda_fail(e);
-  pack_weights_kernel<<<(unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096), 256, 0, s>>>((const float*)w, bt, bt + total, tab, p->u, p->v, dgrad);
+  if (!packed) {
+    cudaError_t e = cudaMallocAsync((void**)&bt, (size_t)total * 2 * sizeof(float), s);
+    if (e != cudaSuccess) return cuda_fail(e);
+    pack_weights_kernel<<<(unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096), 256, 0, s>>>((const float*)w, bt, bt + total, tab, p->u, p->v, dgrad);
+  }
+  const float* hi = packed ? (const float*)packed : bt;
   if (!covers) {
     const long long tot = p->batch * c_rows * N;
     zero_rows_kernel<float><<<(unsigned)((tot + 255) / 256), 256, 0, s>>>((float*)c, p->batch, c_rows, N, tab);
   }
-  rc = tc::launch(t, (const float*)a, p->batch, a_rows, K, bt, bt + total, p->num_paths, N, (float*)c, c_rows, s);
-  cudaFreeAsync(bt, s);
+  rc = tc::launch(t, (const float*)a, p->batch, a_rows, K, hi, hi + total, p->num_paths, N, (float*)c, c_rows, s);
+  if (bt) cudaFreeAsync(bt, s);
   if (rc == FASTEQ_OK) *used = true;
   return rc;
+}
+
+int pack_only(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, void* packed, cudaStream_t s) {
+  GroupTable tab; bool covers = true;
+  int rc = build_table(p, dgrad, &tab, &covers);
+  if (rc != FASTEQ_OK) return rc;
+  if (!w || !packed) return FASTEQ_INVALID;
+  if (p->precision != FASTEQ_EQLIN_TF32X3) return FASTEQ_UNSUPPORTED;
+  const int K = dgrad ? p->v : p->u, N = dgrad ? p->u : p->v;
+  const long long total = (long long)p->num_paths * N * K;
+  pack_weights_kernel<<<(unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096), 256, 0, s>>>((const float*)w, (float*)packed, (float*)packed + total, tab, p->u, p->v, dgrad);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
+}
+
+int run_packed(const fasteq_eqlinear_problem* p, bool dgrad, const void* packed, const void* a, void* c, cudaStream_t s) {
+  if (!p || !packed) return FASTEQ_INVALID;
+  if (p->precision != FASTEQ_EQLIN_TF32X3) return FASTEQ_UNSUPPORTED;
+  if (p->batch == 0) return FASTEQ_OK;
+  if (!a || !c) return FASTEQ_INVALID;
+  bool used = false;
+  int rc = launch_tensorcore(p, dgrad, nullptr, packed, a, c, s, &used);
+  if (rc != FASTEQ_OK) return rc;
+  return used ? FASTEQ_OK : FASTEQ_UNSUPPORTED;      // shapes the tensor-core kernel does not take need the raw weights
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -412,7 +441,7 @@ int dispatch(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const 
     case FASTEQ_EQLIN_FP64: return launch<double>(p, dgrad, w, a, c, (cudaStream_t)stream);
     case FASTEQ_EQLIN_TF32X3: {
       bool used = false;
-      int rc = launch_tensorcore(p, dgrad, w, a, c, (cudaStream_t)stream, &used);
+      int rc = launch_tensorcore(p, dgrad, w, nullptr, a, c, (cudaStream_t)stream, &used);
       if (rc != FASTEQ_OK || used) return rc;
       return launch<float>(p, dgrad, w, a, c, (cudaStream_t)stream);   // shapes the tensor-core kernel does not take
     }
@@ -440,4 +469,19 @@ extern "C" int fasteq_eqlinear_wgrad(const fasteq_eqlinear_problem* p, const voi
   if (p->precision == FASTEQ_EQLIN_TF32X3 || p->precision == FASTEQ_EQLIN_FP32)
     return launch_wgrad<float>(p, x, grad_out, grad_w, (cudaStream_t)stream);
   return FASTEQ_INVALID;
+}
+
+extern "C" int fasteq_eqlinear_pack(const fasteq_eqlinear_problem* p, int32_t dgrad, const void* w, void* packed,
+                                    fasteq_stream_t stream) {
+  return pack_only(p, dgrad != 0, w, packed, (cudaStream_t)stream);
+}
+
+extern "C" int fasteq_eqlinear_forward_packed(const fasteq_eqlinear_problem* p, const void* packed, const void* x, void* out,
+                                              fasteq_stream_t stream) {
+  return run_packed(p, false, packed, x, out, (cudaStream_t)stream);
+}
+
+extern "C" int fasteq_eqlinear_dgrad_packed(const fasteq_eqlinear_problem* p, const void* packed, const void* grad_out,
+                                            void* grad_x, fasteq_stream_t stream) {
+  return run_packed(p, true, packed, grad_out, grad_x, (cudaStream_t)stream);
 }

@@ -540,12 +540,9 @@ static int launch_as_kb(const CUtensorMap& ma, const CUtensorMap& mbh, const CUt
 }
 
 // plain C[M, N] = A[M, K] @ Bt[N, K]^T with K <= 128 and several N tiles
-int launch_a_stationary(const float* A, long long M, int K, const float* Bt, int N, float* C, cudaStream_t s) {
-  float* split = nullptr;
+// `split`: hi / lo parts of Bt (2 * N * K floats)
+int launch_a_stationary(const float* A, long long M, int K, const float* split, int N, float* C, cudaStream_t s) {
   const long long nw = (long long)N * K;
-  cudaError_t e = cudaMallocAsync((void**)&split, (size_t)nw * 2 * sizeof(float), s);
-  if (e != cudaSuccess) return cuda_fail(e);
-  split_weights_kernel<<<(unsigned)((nw + 255) / 256 < 1024 ? (nw + 255) / 256 : 1024), 256, 0, s>>>(Bt, split, split + nw, nw);
   alignas(64) CUtensorMap ma, mbh, mbl, mc;
   int rc = make_map(&ma, A, (uint64_t)K, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, BK, 1, BM);
   if (rc == FASTEQ_OK) rc = make_map(&mc, C, (uint64_t)N, (uint64_t)M, 1, (uint64_t)N, (uint64_t)N * M, 32, 32, 1);
@@ -555,7 +552,35 @@ int launch_a_stationary(const float* A, long long M, int K, const float* Bt, int
     const int kb = (K + BK - 1) / BK;
     rc = kb <= 2 ? launch_as_kb<2>(ma, mbh, mbl, mc, M, N, K, s) : launch_as_kb<4>(ma, mbh, mbl, mc, M, N, K, s);
   }
-  cudaFreeAsync(split, s);
+  return rc;
+}
+
+// C = A @ Bt^T with Bt given raw (split into a temporary) or already split
+int dense(const float* A, const float* Bt, const float* split_in, float* C, long long M, int N, int K, cudaStream_t s) {
+  if (M < 0 || N < 1 || K < 1) return FASTEQ_INVALID;
+  if (M == 0) return FASTEQ_OK;
+  if (!A || (!Bt && !split_in) || !C) return FASTEQ_INVALID;
+  if (!supported(M, 1, K, 1, N, 1, A, split_in ? split_in : Bt, C)) return FASTEQ_UNSUPPORTED;
+  const long long nw = (long long)N * K;
+  float* tmp = nullptr;
+  int rc = FASTEQ_OK;
+  if (!split_in) {
+    cudaError_t e = cudaMallocAsync((void**)&tmp, (size_t)nw * 2 * sizeof(float), s);
+    if (e != cudaSuccess) return cuda_fail(e);
+    rc = split_weights(Bt, nw, tmp, s);
+  }
+  const float* split = split_in ? split_in : tmp;
+  if (rc == FASTEQ_OK) {
+    if (K <= 128 && N >= 256) {
+      rc = launch_a_stationary(A, M, K, split, N, C, s);
+    } else {
+      TcTable tab{};
+      tab.n_groups = 1; tab.n_items = 1; tab.group_c_row[0] = 0; tab.group_first[0] = 0; tab.group_first[1] = 1;
+      tab.item_first[0] = 0; tab.item_first[1] = 1; tab.path_a_row[0] = 0; tab.path_w[0] = 0;
+      rc = launch(tab, A, M, 1, K, split, split + nw, 1, N, C, 1, s);
+    }
+  }
+  if (tmp) cudaFreeAsync(tmp, s);
   return rc;
 }
 
@@ -576,24 +601,20 @@ int device_status(int* code) {
 // Bt is torch's [out_features, in_features] weight).  K and N multiples of 4, 16-byte aligned pointers.
 extern "C" int fasteq_gemm_tf32x3(const void* A, const void* Bt, void* C, int64_t M, int32_t N, int32_t K,
                                   fasteq_stream_t stream) {
-  using namespace fasteq;
-  if (M < 0 || N < 1 || K < 1) return FASTEQ_INVALID;
-  if (M == 0) return FASTEQ_OK;
-  if (!A || !Bt || !C) return FASTEQ_INVALID;
-  if (!tc::supported(M, 1, K, 1, N, 1, A, Bt, C)) return FASTEQ_UNSUPPORTED;
-  if (K <= 128 && N >= 256) return tc::launch_a_stationary((const float*)A, M, K, (const float*)Bt, N, (float*)C, (cudaStream_t)stream);
-  tc::TcTable tab{};
-  tab.n_groups = 1; tab.n_items = 1; tab.group_c_row[0] = 0; tab.group_first[0] = 0; tab.group_first[1] = 1;
-  tab.item_first[0] = 0; tab.item_first[1] = 1; tab.path_a_row[0] = 0; tab.path_w[0] = 0;
-  float* split = nullptr;
-  const long long nw = (long long)N * K;
-  cudaError_t e = cudaMallocAsync((void**)&split, (size_t)nw * 2 * sizeof(float), (cudaStream_t)stream);
-  if (e != cudaSuccess) return cuda_fail(e);
-  int rc = tc::split_weights((const float*)Bt, nw, split, (cudaStream_t)stream);
-  if (rc == FASTEQ_OK)
-    rc = tc::launch(tab, (const float*)A, M, 1, K, split, split + nw, 1, N, (float*)C, 1, (cudaStream_t)stream);
-  cudaFreeAsync(split, (cudaStream_t)stream);
-  return rc;
+  return fasteq::tc::dense((const float*)A, (const float*)Bt, nullptr, (float*)C, M, N, K, (cudaStream_t)stream);
+}
+
+// The two TF32 parts of a weight matrix, prepared once for many fasteq_gemm_tf32x3_presplit calls.
+extern "C" int fasteq_gemm_tf32x3_split(const void* Bt, int64_t n_elems, void* split, fasteq_stream_t stream) {
+  if (n_elems < 0 || (n_elems > 0 && (!Bt || !split))) return FASTEQ_INVALID;
+  if (n_elems == 0) return FASTEQ_OK;
+  return fasteq::tc::split_weights((const float*)Bt, n_elems, (float*)split, (cudaStream_t)stream);
+}
+
+extern "C" int fasteq_gemm_tf32x3_presplit(const void* A, const void* split, void* C, int64_t M, int32_t N, int32_t K,
+                                           fasteq_stream_t stream) {
+  if (!split && M > 0) return FASTEQ_INVALID;
+  return fasteq::tc::dense((const float*)A, nullptr, (const float*)split, (float*)C, M, N, K, (cudaStream_t)stream);
 }
 
 extern "C" int fasteq_tensorcore_device_status(int32_t* code) {

@@ -375,38 +375,51 @@ static int launch_nb(const CUtensorMap& tmw, const CUtensorMap& io0, const CUten
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }
 
+static int prepare(const float* const* w_hidden, int n_tc, bool bwd, float* prepared, cudaStream_t s) {
+  if (n_tc < 1) return FASTEQ_OK;
+  if (n_tc > MAX_TC) return FASTEQ_UNSUPPORTED;
+  if (!w_hidden || !prepared) return FASTEQ_INVALID;
+  for (int l = 0; l < n_tc; ++l)
+    if (!w_hidden[l]) return FASTEQ_INVALID;
+  // forward uses W_2, W_3 in order; backward uses W_L^T first
+  const float* first = bwd ? w_hidden[n_tc - 1] : w_hidden[0];
+  const float* second = n_tc > 1 ? (bwd ? w_hidden[0] : w_hidden[1]) : first;
+  prepare_weights_kernel<<<n_tc * 4, 256, 0, s>>>(first, second, n_tc, bwd, prepared);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
+}
+
 // io0: forward h_L out / backward dE/dh_L in, [M, 64]; io1: derivatives [n_tc, M, 64] (out / in)
 template <bool BWD>
-static int run(Args a, const float* const* w_hidden, const float* io0, const float* io1, cudaStream_t s) {
+static int run(Args a, const float* const* w_hidden, const float* prepared_in, const float* io0, const float* io1, cudaStream_t s) {
   if (a.M < 0 || a.nb < 1) return FASTEQ_INVALID;
   if (a.nb > MAX_NB || a.n_tc < 0 || a.n_tc > MAX_TC || a.M > 0x7fffffffLL - BM) return FASTEQ_UNSUPPORTED;
   if (a.M == 0) return FASTEQ_OK;
-  if (!a.basis || !a.w1 || !io0 || (a.n_tc > 0 && (!w_hidden || !io1)) || (BWD && !a.grad_basis)) return FASTEQ_INVALID;
-  if ((reinterpret_cast<uintptr_t>(io0) | reinterpret_cast<uintptr_t>(io1)) & 15u) return FASTEQ_UNSUPPORTED;
-  for (int l = 0; l < a.n_tc; ++l)
-    if (!w_hidden[l]) return FASTEQ_INVALID;
+  if (!a.basis || !a.w1 || !io0 || (a.n_tc > 0 && ((!w_hidden && !prepared_in) || !io1)) || (BWD && !a.grad_basis)) return FASTEQ_INVALID;
+  if ((reinterpret_cast<uintptr_t>(io0) | reinterpret_cast<uintptr_t>(io1) | reinterpret_cast<uintptr_t>(prepared_in)) & 15u)
+    return FASTEQ_UNSUPPORTED;
   cudaError_t e;
   if (BWD) {
     e = cudaMemsetAsync(a.grad_basis, 0, (size_t)a.M * a.nb * sizeof(float), s);
     if (e != cudaSuccess) return cuda_fail(e);
   }
-  float* prepared = nullptr;
+  float* tmp = nullptr;
   alignas(64) CUtensorMap tmw, tm0, tm1;
   const int n_alloc = a.n_tc > 0 ? a.n_tc : 1;
-  e = cudaMallocAsync((void**)&prepared, (size_t)n_alloc * 2 * H * H * sizeof(float), s);
-  if (e != cudaSuccess) return cuda_fail(e);
-  if (a.n_tc > 0) {
-    // forward uses W_2, W_3 in order; backward uses W_L^T first
-    const float* first = BWD ? w_hidden[a.n_tc - 1] : w_hidden[0];
-    const float* second = a.n_tc > 1 ? (BWD ? w_hidden[0] : w_hidden[1]) : first;
-    prepare_weights_kernel<<<a.n_tc * 4, 256, 0, s>>>(first, second, a.n_tc, BWD, prepared);
+  int rc = FASTEQ_OK;
+  if (!prepared_in || a.n_tc == 0) {
+    e = cudaMallocAsync((void**)&tmp, (size_t)n_alloc * 2 * H * H * sizeof(float), s);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (a.n_tc > 0) rc = prepare(w_hidden, a.n_tc, BWD, tmp, s);
   }
-  int rc = tc::make_map(&tmw, prepared, (uint64_t)H, (uint64_t)H, (uint64_t)n_alloc * 2, (uint64_t)H, (uint64_t)H * H, BK, H, 1);
+  const float* prepared = tmp ? tmp : prepared_in;
+  if (rc == FASTEQ_OK)
+    rc = tc::make_map(&tmw, prepared, (uint64_t)H, (uint64_t)H, (uint64_t)n_alloc * 2, (uint64_t)H, (uint64_t)H * H, BK, H, 1);
   if (rc == FASTEQ_OK) rc = tc::make_map(&tm0, io0, (uint64_t)H, (uint64_t)a.M, 1, (uint64_t)H, (uint64_t)a.M * H, 32, 32, 1);
   if (rc == FASTEQ_OK)
     rc = tc::make_map(&tm1, a.n_tc > 0 ? io1 : io0, (uint64_t)H, (uint64_t)a.M, (uint64_t)n_alloc, (uint64_t)H, (uint64_t)a.M * H, 32, 32, 1);
   if (rc == FASTEQ_OK) rc = a.nb <= 8 ? launch_nb<8, BWD>(tmw, tm0, tm1, a, s) : launch_nb<16, BWD>(tmw, tm0, tm1, a, s);
-  cudaFreeAsync(prepared, s);
+  if (tmp) cudaFreeAsync(tmp, s);
   return rc;
 }
 
@@ -414,19 +427,25 @@ static int run(Args a, const float* const* w_hidden, const float* io0, const flo
 }  // namespace fasteq
 
 extern "C" int fasteq_radial_chain_forward(const float* basis, int64_t n_edges, int32_t n_basis, const float* w_first,
-                                           const float* const* w_hidden, int32_t n_hidden, float* out, float* deriv,
-                                           fasteq_stream_t stream) {
+                                           const float* const* w_hidden, const float* prepared, int32_t n_hidden, float* out,
+                                           float* deriv, fasteq_stream_t stream) {
   if (n_hidden < 1) return FASTEQ_INVALID;
   fasteq::chain::Args a{};
   a.basis = basis; a.w1 = w_first; a.M = n_edges; a.nb = n_basis; a.n_tc = n_hidden - 1;
-  return fasteq::chain::run<false>(a, w_hidden, out, deriv, (cudaStream_t)stream);
+  return fasteq::chain::run<false>(a, w_hidden, prepared, out, deriv, (cudaStream_t)stream);
 }
 
 extern "C" int fasteq_radial_chain_backward(const float* grad_out, const float* deriv, const float* basis, int64_t n_edges,
                                             int32_t n_basis, const float* w_first, const float* const* w_hidden,
-                                            int32_t n_hidden, float* grad_basis, fasteq_stream_t stream) {
+                                            const float* prepared, int32_t n_hidden, float* grad_basis, fasteq_stream_t stream) {
   if (n_hidden < 1) return FASTEQ_INVALID;
   fasteq::chain::Args a{};
   a.basis = basis; a.w1 = w_first; a.grad_basis = grad_basis; a.M = n_edges; a.nb = n_basis; a.n_tc = n_hidden - 1;
-  return fasteq::chain::run<true>(a, w_hidden, grad_out, deriv, (cudaStream_t)stream);
+  return fasteq::chain::run<true>(a, w_hidden, prepared, grad_out, deriv, (cudaStream_t)stream);
+}
+
+extern "C" int fasteq_radial_chain_prepare(const float* const* w_hidden, int32_t n_hidden, int32_t backward, float* prepared,
+                                           fasteq_stream_t stream) {
+  if (n_hidden < 1) return FASTEQ_INVALID;
+  return fasteq::chain::prepare(w_hidden, n_hidden - 1, backward != 0, prepared, (cudaStream_t)stream);
 }

@@ -192,8 +192,8 @@ class LinearDescriptor:
         return len(self.paths) * self.u * self.v
 
 
-def linear(irreps_in, irreps_out, path_normalization: str = "element") -> LinearDescriptor:
-    """e3nn ``o3.Linear(irreps_in, irreps_out)`` as a uv,iu,iv descriptor.
+def linear(irreps_in, irreps_out, path_normalization: str = "element", scale: float = 1.0) -> LinearDescriptor:
+    """e3nn ``o3.Linear(irreps_in, irreps_out)`` as a uv,iu,iv descriptor (all path coefficients times ``scale``).
 
     One path per (input block, output block) pair of equal irrep, in e3nn's instruction order
     (input-major); coefficient ``sqrt(1 / fan_in)`` with ``fan_in`` the summed input multiplicity
@@ -210,7 +210,7 @@ def linear(irreps_in, irreps_out, path_normalization: str = "element") -> Linear
             fan = irreps_in[a].mul * len([1 for a2, b2 in pairs if b2 == b])
         else:
             fan = 1
-        paths.append(LinearPath((q, a, b), sqrt(1.0 / fan)))
+        paths.append(LinearPath((q, a, b), scale * sqrt(1.0 / fan)))
     return LinearDescriptor([b.ir.dim for b in irreps_in], [b.ir.dim for b in irreps_out], u, v, paths)
 
 

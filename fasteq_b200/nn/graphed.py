@@ -5,13 +5,16 @@ positions.  ``GraphedEnergyForces`` captures one evaluation (forward and the aut
 backward, a few hundred kernel launches) into a CUDA graph and replays it, so the per-step host
 cost is one copy of the positions and one graph launch instead of the Python / launch overhead of
 every operator.  Capture needs the operator plans and generated modules to exist already, which the
-warm-up evaluations ensure.
+warm-up evaluations ensure.  The model's weights are taken as frozen for the life of the graph: the
+prepared (TF32-split) weight forms cached during the warm-up are captured as they are.
 """
 from __future__ import annotations
 
 from typing import Dict, Optional
 
 import torch
+
+from ..ops import _prepared
 
 
 class GraphedEnergyForces:
@@ -29,8 +32,9 @@ class GraphedEnergyForces:
         torch.cuda.current_stream(pos.device).wait_stream(side)
         torch.cuda.synchronize(pos.device)
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with _prepared.frozen_weights(), torch.cuda.graph(self.graph):
             self.static_out = model(self.static_pos, *static_args, **static_kwargs)
+        self._prepared = _prepared.snapshot()      # the captured kernels read these buffers
 
     def __call__(self, pos: torch.Tensor) -> Dict[str, torch.Tensor]:
         """Results live in static buffers that the next call overwrites; clone what must be kept."""

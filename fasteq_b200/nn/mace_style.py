@@ -72,7 +72,7 @@ class InteractionLayer(torch.nn.Module):
         self.conv_tp = ChannelwiseTensorProduct(irreps_in, sh, irreps_tp, instr)
         self.radial = RadialMLP(num_basis, radial_hidden, self.conv_tp.weight_numel)
         self.irreps_mid = Irreps([(mul, (l, (-1) ** l)) for l in range(lmax_mid + 1)])
-        self.linear_mid = SO3Linear(irreps_tp, self.irreps_mid)
+        self.linear_mid = SO3Linear(irreps_tp, self.irreps_mid, output_scale=1.0 / avg_num_neighbors)
         self.product = SymmetricContraction(self.irreps_mid, hidden, num_species, correlation)
         self.linear_out = SO3Linear(hidden, hidden)
         self.inv_neighbors = 1.0 / avg_num_neighbors
@@ -87,7 +87,7 @@ class InteractionLayer(torch.nn.Module):
         msg = self.conv_tp(up, edge_sh, w, edge_dst, edge_src, edge_vec=edge_vec)
         if msg.shape[0] != n_owned:
             msg = msg[:n_owned]              # rows of ghost receivers (no edges end there)
-        mid = self.linear_mid(msg, self.linear_mid.weight * self.inv_neighbors)   # 1 / <neighbours> folded into the small weight
+        mid = self.linear_mid(msg)           # 1 / <neighbours> is folded into its path coefficients
         prod = self.product(mid, species)
         return self.linear_out(prod)
 

@@ -83,10 +83,13 @@ class SO3Linear(torch.nn.Module):
     """e3nn ``o3.Linear`` for uniform multiplicities: one ``[mul_in, mul_out]`` matrix per pair of equal
     irreps, normalised by the fan-in (e3nn/o3/_linear.py:148-159)."""
 
-    def __init__(self, irreps_in, irreps_out, layout: str = "ir_mul", compute_precision: Optional[str] = None):
+    def __init__(self, irreps_in, irreps_out, layout: str = "ir_mul", compute_precision: Optional[str] = None,
+                 output_scale: float = 1.0):
+        """``output_scale`` multiplies the result (folded into the path coefficients, e.g. 1 / <neighbours>)."""
         super().__init__()
         self.irreps_in, self.irreps_out = Irreps(irreps_in), Irreps(irreps_out)
-        self.descriptor = descriptors.linear(self.irreps_in, self.irreps_out)
+        self.output_scale = float(output_scale)
+        self.descriptor = descriptors.linear(self.irreps_in, self.irreps_out, scale=self.output_scale)
         self.weight = torch.nn.Parameter(torch.randn(self.descriptor.num_weights))
         self.layout, self.compute_precision = layout, compute_precision
 

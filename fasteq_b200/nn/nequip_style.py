@@ -41,7 +41,7 @@ class NequIPStyleLayer(torch.nn.Module):
         irreps_tp, instr = full_channelwise_instructions(irreps_in, sh, lmax)
         self.conv_tp = ChannelwiseTensorProduct(irreps_in, sh, irreps_tp, instr)
         self.radial = RadialMLP(num_basis, radial_hidden, self.conv_tp.weight_numel)
-        self.linear_2 = SO3Linear(irreps_tp, self.gate_in)
+        self.linear_2 = SO3Linear(irreps_tp, self.gate_in, output_scale=1.0 / avg_num_neighbors)
         self.self_connection = SO3Linear(irreps_in, self.gate_in)
         self.inv_neighbors = 1.0 / avg_num_neighbors
         self.irreps_out = hid
@@ -54,7 +54,7 @@ class NequIPStyleLayer(torch.nn.Module):
         msg = self.conv_tp(up, edge_sh, self.radial(edge_radial), edge_dst, edge_src, edge_vec=edge_vec)
         if msg.shape[0] != n_owned:
             msg = msg[:n_owned]
-        pre = self.linear_2(msg, self.linear_2.weight * self.inv_neighbors) + self.self_connection(h)
+        pre = self.linear_2(msg) + self.self_connection(h)      # 1 / <neighbours> is folded into linear_2's coefficients
         return gate(pre, self.gate_spec)
 
 

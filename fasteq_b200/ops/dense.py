@@ -11,6 +11,7 @@ import ctypes as C
 import torch
 
 from .. import _cabi
+from . import _prepared
 
 _ready = False
 
@@ -21,6 +22,8 @@ def _lib():
     if not _ready:
         lib.fasteq_gemm_tf32x3.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]
         lib.fasteq_tensorcore_device_status.argtypes = [C.POINTER(C.c_int32)]
+        lib.fasteq_gemm_tf32x3_split.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
+        lib.fasteq_gemm_tf32x3_presplit.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]
         _ready = True
     return lib
 
@@ -36,15 +39,29 @@ def _usable(x: torch.Tensor, n: int, k: int) -> bool:
     return x.is_cuda and x.dtype == torch.float32 and k % 4 == 0 and n % 4 == 0 and k >= 4 and n >= 4 and x.shape[0] > 0
 
 
-def _gemm(a: torch.Tensor, bt: torch.Tensor) -> torch.Tensor:
-    """a [M, K] @ bt[N, K]^T -> [M, N]."""
-    a, bt = a.contiguous(), bt.contiguous()
+def _gemm(a: torch.Tensor, bt: torch.Tensor, weight: torch.Tensor = None, transposed: bool = False) -> torch.Tensor:
+    """a [M, K] @ bt[N, K]^T -> [M, N].  ``weight`` (optional) is the parameter ``bt`` derives from: its TF32 parts
+    are then prepared once per weight version instead of once per call."""
+    a = a.contiguous()
     M, K = a.shape
     N = bt.shape[0]
     out = torch.empty((M, N), dtype=a.dtype, device=a.device)
     lib = _lib()
     with torch.cuda.device(a.device):
-        rc = lib.fasteq_gemm_tf32x3(a.data_ptr(), bt.data_ptr(), out.data_ptr(), M, N, K, torch.cuda.current_stream(a.device).cuda_stream)
+        stream = torch.cuda.current_stream(a.device).cuda_stream
+        split = None
+        if weight is not None:
+            def build():
+                b = bt.contiguous()
+                sp = torch.empty(2 * b.numel(), dtype=torch.float32, device=b.device)
+                _cabi.check(lib.fasteq_gemm_tf32x3_split(b.data_ptr(), b.numel(), sp.data_ptr(), stream), lib, "fasteq_gemm_tf32x3_split")
+                return sp
+            split = _prepared.get((weight,), ("dense", transposed), build)
+        if split is not None:
+            rc = lib.fasteq_gemm_tf32x3_presplit(a.data_ptr(), split.data_ptr(), out.data_ptr(), M, N, K, stream)
+        else:
+            bt = bt.contiguous()
+            rc = lib.fasteq_gemm_tf32x3(a.data_ptr(), bt.data_ptr(), out.data_ptr(), M, N, K, stream)
     if rc == 1:   # FASTEQ_UNSUPPORTED: alignment
         return a @ bt.t()
     _cabi.check(rc, lib, "fasteq_gemm_tf32x3")
@@ -55,14 +72,14 @@ class _Dense(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight):
         ctx.save_for_backward(x, weight)
-        return _gemm(x, weight)
+        return _gemm(x, weight, weight, False)
 
     @staticmethod
     def backward(ctx, grad_out):
         x, weight = ctx.saved_tensors
         gx = gw = None
         if ctx.needs_input_grad[0]:
-            gx = _gemm(grad_out, weight.t().contiguous())       # [M, N] @ [N, K] with Bt = weight^T [K, N]
+            gx = _gemm(grad_out, weight.t(), weight, True)      # [M, N] @ [N, K] with Bt = weight^T [K, N]
         if ctx.needs_input_grad[1]:
             gw = grad_out.t() @ x
         return gx, gw

@@ -18,6 +18,7 @@ from typing import Dict, List, Tuple
 import torch
 
 from .. import _cabi
+from . import _prepared
 
 __all__ = ["fast_equi_linear", "eqlinear_clear_plan_cache", "eqlinear_set_plan_cache", "eqlinear_debug_info"]
 
@@ -128,6 +129,9 @@ def _core():
         lib.fasteq_eqlinear_forward.argtypes = [C.POINTER(_Problem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         lib.fasteq_eqlinear_dgrad.argtypes = [C.POINTER(_Problem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         lib.fasteq_eqlinear_wgrad.argtypes = [C.POINTER(_Problem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        lib.fasteq_eqlinear_pack.argtypes = [C.POINTER(_Problem), C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
+        lib.fasteq_eqlinear_forward_packed.argtypes = [C.POINTER(_Problem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        lib.fasteq_eqlinear_dgrad_packed.argtypes = [C.POINTER(_Problem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         _core_ready = True
     return lib
 
@@ -157,6 +161,33 @@ def _order_weights(w3d, mapping):
     return w3d[torch.tensor(wps, device=w3d.device)].contiguous()
 
 
+def _packed_weights(w, w3, geom_key, prob, dgrad: bool, lib, stream):
+    """Pre-scaled, K-major, TF32-split weight blocks of this problem and direction (cached per weight version)."""
+    def build():
+        packed = torch.empty(2 * w3.numel(), dtype=torch.float32, device=w3.device)
+        rc = lib.fasteq_eqlinear_pack(C.byref(prob), 1 if dgrad else 0, w3.data_ptr(), packed.data_ptr(), stream)
+        if rc == 1:      # FASTEQ_UNSUPPORTED
+            return None
+        _cabi.check(rc, lib, "fasteq_eqlinear_pack")
+        return packed
+    return _prepared.get((w,), ("eqlinear", geom_key, dgrad), build)
+
+
+def _run(lib, prob, w, w3, a, c, geom_key, precision, dgrad: bool, stream):
+    """One forward / grad_x launch: through prepared weights when the tensor-core path takes the problem."""
+    if precision == _TF32:
+        packed = _packed_weights(w, w3, geom_key, prob, dgrad, lib, stream)
+        if packed is not None:
+            fn = lib.fasteq_eqlinear_dgrad_packed if dgrad else lib.fasteq_eqlinear_forward_packed
+            rc = fn(C.byref(prob), packed.data_ptr(), a.data_ptr(), c.data_ptr(), stream)
+            if rc != 1:
+                _cabi.check(rc, lib, "fasteq_eqlinear_dgrad_packed" if dgrad else "fasteq_eqlinear_forward_packed")
+                return
+    fn = lib.fasteq_eqlinear_dgrad if dgrad else lib.fasteq_eqlinear_forward
+    _cabi.check(fn(C.byref(prob), w3.data_ptr(), a.data_ptr(), c.data_ptr(), stream), lib,
+                "fasteq_eqlinear_dgrad" if dgrad else "fasteq_eqlinear_forward")
+
+
 class _EqLinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, w, x, geom, precision):
@@ -169,11 +200,12 @@ class _EqLinearFn(torch.autograd.Function):
         out = torch.empty((batch, J, v), dtype=x.dtype, device=x.device)
         lib = _core()
         prob = _make_problem([(m[0], m[1], q, m[3]) for q, m in enumerate(mapping)], coeff, u, v, I, J, batch, precision)
+        geom_key = (tuple(mapping), tuple(coeff), u, v, I, J)
         with torch.cuda.device(x.device):
-            _cabi.check(lib.fasteq_eqlinear_forward(C.byref(prob), w3.data_ptr(), x3.data_ptr(), out.data_ptr(),
-                                                    torch.cuda.current_stream(x.device).cuda_stream), lib, "fasteq_eqlinear_forward")
+            _run(lib, prob, w, w3, x3, out, geom_key, precision, False, torch.cuda.current_stream(x.device).cuda_stream)
         ctx.save_for_backward(w3, x3 if ctx.needs_input_grad[0] else None)
         ctx.geom, ctx.precision, ctx.batch, ctx.w_shape = geom, precision, batch, w.shape
+        ctx.w_ref, ctx.geom_key = w, geom_key
         return out.reshape(batch, J * v)
 
     @staticmethod
@@ -188,8 +220,7 @@ class _EqLinearFn(torch.autograd.Function):
             stream = torch.cuda.current_stream(g3.device).cuda_stream
             if ctx.needs_input_grad[1]:
                 dx = torch.empty((ctx.batch, I, u), dtype=g3.dtype, device=g3.device)
-                _cabi.check(lib.fasteq_eqlinear_dgrad(C.byref(prob), w3.data_ptr(), g3.data_ptr(), dx.data_ptr(), stream),
-                            lib, "fasteq_eqlinear_dgrad")
+                _run(lib, prob, ctx.w_ref, w3, g3, dx, ctx.geom_key, ctx.precision, True, stream)
                 dx = dx.reshape(ctx.batch, I * u)
             if ctx.needs_input_grad[0]:
                 dw = torch.empty((len(mapping), u, v), dtype=g3.dtype, device=g3.device)
@@ -212,11 +243,13 @@ def fast_equi_linear(descriptor, w, x, *, compute_precision=None):
 
 
 def eqlinear_clear_plan_cache() -> None:
-    """Kept for API compatibility: this implementation is stateless (no prepared plans)."""
+    """Drop the prepared weights (same name as the reference's call, fasteq/ops/eqlinear.py)."""
+    _prepared.clear()
 
 
 def eqlinear_set_plan_cache(max_bytes=None) -> None:
-    """Kept for API compatibility: there is no plan cache to size."""
+    """Byte budget of the prepared-weight cache; ``0`` disables it, ``None`` restores the default (256 MiB)."""
+    _prepared.set_budget(max_bytes)
 
 
 def eqlinear_debug_info(descriptor, w, x, *, compute_precision=None) -> dict:

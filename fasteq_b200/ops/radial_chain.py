@@ -13,6 +13,7 @@ from typing import List, Optional, Sequence
 import torch
 
 from .. import _cabi
+from . import _prepared
 
 _ready = False
 WIDTH = 64
@@ -25,10 +26,11 @@ def _lib():
     lib = _cabi.core()
     if not _ready:
         pp = C.POINTER(C.c_void_p)
-        lib.fasteq_radial_chain_forward.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, pp, C.c_int32, C.c_void_p,
+        lib.fasteq_radial_chain_forward.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, pp, C.c_void_p, C.c_int32, C.c_void_p,
                                                     C.c_void_p, C.c_void_p]
         lib.fasteq_radial_chain_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, pp,
-                                                     C.c_int32, C.c_void_p, C.c_void_p]
+                                                     C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
+        lib.fasteq_radial_chain_prepare.argtypes = [pp, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
         _ready = True
     return lib
 
@@ -38,6 +40,19 @@ def _hidden_array(ws: Sequence[torch.Tensor]):
     for i, w in enumerate(ws):
         arr[i] = w.data_ptr()
     return arr
+
+
+def _prepared_hidden(ws, backward: bool, lib, stream):
+    """TF32 parts of the 64 x 64 layers in the order (and orientation) the kernel of this direction multiplies with."""
+    hidden = ws[1:]
+    if not hidden:
+        return None
+    def build():
+        prep = torch.empty(len(hidden) * 2 * WIDTH * WIDTH, dtype=torch.float32, device=hidden[0].device)
+        _cabi.check(lib.fasteq_radial_chain_prepare(_hidden_array(hidden), len(ws), 1 if backward else 0, prep.data_ptr(), stream),
+                    lib, "fasteq_radial_chain_prepare")
+        return prep
+    return _prepared.get(tuple(hidden), ("radial_chain", backward), build)
 
 
 class _RadialChain(torch.autograd.Function):
@@ -50,8 +65,11 @@ class _RadialChain(torch.autograd.Function):
         deriv = torch.empty((max(n_hidden - 1, 1), E, WIDTH), dtype=torch.float32, device=basis.device)
         lib = _lib()
         with torch.cuda.device(basis.device):
-            rc = lib.fasteq_radial_chain_forward(basis.data_ptr(), E, nb, ws[0].data_ptr(), _hidden_array(ws[1:]), n_hidden,
-                                                 out.data_ptr(), deriv.data_ptr(), torch.cuda.current_stream(basis.device).cuda_stream)
+            stream = torch.cuda.current_stream(basis.device).cuda_stream
+            prep = _prepared_hidden(ws, False, lib, stream)
+            rc = lib.fasteq_radial_chain_forward(basis.data_ptr(), E, nb, ws[0].data_ptr(), _hidden_array(ws[1:]),
+                                                 prep.data_ptr() if prep is not None else None, n_hidden,
+                                                 out.data_ptr(), deriv.data_ptr(), stream)
         _cabi.check(rc, lib, "fasteq_radial_chain_forward")
         ctx.save_for_backward(basis, deriv, *ws)
         return out
@@ -66,9 +84,11 @@ class _RadialChain(torch.autograd.Function):
         gb = torch.empty((E, nb), dtype=torch.float32, device=basis.device)
         lib = _lib()
         with torch.cuda.device(basis.device):
+            stream = torch.cuda.current_stream(basis.device).cuda_stream
+            prep = _prepared_hidden(ws, True, lib, stream)
             rc = lib.fasteq_radial_chain_backward(g.data_ptr(), deriv.data_ptr(), basis.data_ptr(), E, nb, ws[0].data_ptr(),
-                                                  _hidden_array(ws[1:]), len(ws), gb.data_ptr(),
-                                                  torch.cuda.current_stream(basis.device).cuda_stream)
+                                                  _hidden_array(ws[1:]), prep.data_ptr() if prep is not None else None, len(ws),
+                                                  gb.data_ptr(), stream)
         _cabi.check(rc, lib, "fasteq_radial_chain_backward")
         return (gb,) + (None,) * len(ws)
 

@@ -231,6 +231,18 @@ int fasteq_eqlinear_forward(const fasteq_eqlinear_problem* p /* host */, const v
  * (the reference exposes grad_x only, eqlinear_runtime.py:86-104). grad_x is fully overwritten. */
 int fasteq_eqlinear_dgrad(const fasteq_eqlinear_problem* p /* host */, const void* w, const void* grad_out,
                           void* grad_x, fasteq_stream_t stream);
+/* Weights prepared once for many calls of the tensor-core path (FASTEQ_EQLIN_TF32X3): pre-scaled, K-major,
+ * split into their two TF32 parts; packed holds 2 * num_paths * u * v floats; dgrad != 0 prepares the
+ * grad_x layout.  The packed forms depend on the paths and coefficients but not on batch.  The _packed
+ * calls return FASTEQ_UNSUPPORTED for shapes the tensor-core kernel does not take (use the plain calls).
+ * Plays the part of the reference's forward_create / dgrad_create plan objects
+ * (fasteq/cuda/src/eqlinear/common/eqlinear_backend_api.h:12-27), owned by the caller. */
+int fasteq_eqlinear_pack(const fasteq_eqlinear_problem* p /* host */, int32_t dgrad, const void* w, void* packed,
+                         fasteq_stream_t stream);
+int fasteq_eqlinear_forward_packed(const fasteq_eqlinear_problem* p /* host */, const void* packed, const void* x, void* out,
+                                   fasteq_stream_t stream);
+int fasteq_eqlinear_dgrad_packed(const fasteq_eqlinear_problem* p /* host */, const void* packed, const void* grad_out,
+                                 void* grad_x, fasteq_stream_t stream);
 /* grad_w[q] = coeff[q] * sum_b sum_{t < rows[q]} x[b, in_row[q]+t, :]^T grad_out[b, out_row[q]+t, :]   ([u, v] per path).
  * Needed to train the mixing weights.  The reference's public operator returns no weight gradient
  * (eqlinear_runtime.py:104); its FP32 back-end keeps a reduction kernel for one
@@ -265,6 +277,10 @@ int fasteq_gate_backward(const fasteq_gate_problem* p /* host */, const void* x,
  * pointers 16-byte aligned, else FASTEQ_UNSUPPORTED.  The reference leaves this MLP to the model
  * package (torch); it has no entry point of its own for it. */
 int fasteq_gemm_tf32x3(const void* A, const void* Bt, void* C, int64_t M, int32_t N, int32_t K, fasteq_stream_t stream);
+/* The same product with the weight's two TF32 parts prepared beforehand (split holds 2 * N * K floats: hi parts,
+ * then lo parts), for weights that stay fixed over many calls. */
+int fasteq_gemm_tf32x3_split(const void* Bt, int64_t n_elems, void* split, fasteq_stream_t stream);
+int fasteq_gemm_tf32x3_presplit(const void* A, const void* split, void* C, int64_t M, int32_t N, int32_t K, fasteq_stream_t stream);
 /* Hidden layers of the radial MLP (width 64, SiLU, no bias) fused into one kernel per direction:
  *   forward : basis [n_edges, n_basis] -> h_1 = silu(W_1 basis) -> ... -> h_L = silu(W_L h_{L-1})
  *   backward: dE/dh_L -> dE/dbasis (weights get no gradient here; train through the layered path)
@@ -275,11 +291,16 @@ int fasteq_gemm_tf32x3(const void* A, const void* Bt, void* C, int64_t M, int32_
  * out / deriv / grad_out 16-byte aligned.  No counterpart in the reference, which leaves the radial
  * MLP to torch modules of the model package. */
 int fasteq_radial_chain_forward(const float* basis, int64_t n_edges, int32_t n_basis, const float* w_first,
-                                const float* const* w_hidden /* host */, int32_t n_hidden, float* out, float* deriv,
-                                fasteq_stream_t stream);
+                                const float* const* w_hidden /* host */, const float* prepared /* or NULL */, int32_t n_hidden,
+                                float* out, float* deriv, fasteq_stream_t stream);
 int fasteq_radial_chain_backward(const float* grad_out, const float* deriv, const float* basis, int64_t n_edges,
                                  int32_t n_basis, const float* w_first, const float* const* w_hidden /* host */,
-                                 int32_t n_hidden, float* grad_basis, fasteq_stream_t stream);
+                                 const float* prepared /* or NULL */, int32_t n_hidden, float* grad_basis, fasteq_stream_t stream);
+/* The 64 x 64 layers in the form the kernels multiply with (TF32 parts; transposed and in reverse order for the
+ * backward): prepared holds (n_hidden - 1) * 2 * 64 * 64 floats and may be passed to the calls above in place
+ * of w_hidden while the weights stay unchanged. */
+int fasteq_radial_chain_prepare(const float* const* w_hidden /* host */, int32_t n_hidden, int32_t backward, float* prepared,
+                                fasteq_stream_t stream);
 /* Edge geometry of a radius graph: vec[e] = (pos[src[e]] + shift[e]) - pos[dst[e]] and the radial basis
  * basis[e, n] = sqrt(2 / r_max) sin((n+1) pi r / r_max) / r * env(r / r_max), env the degree-p polynomial cutoff
  * (the embedding of NequIP / MACE models, .../nequip/nn/embedding/_edge.py:174-189, cutoffs.py:17-27; the

@@ -78,7 +78,7 @@ def energy_and_forces(model, pos, species, edge_src, edge_dst, edge_shift):
             if k + 1 < n_lin:
                 w = torch.nn.functional.silu(w)
         msg = u1d_scatter(w, up, ysh, layer.conv_tp.descriptor, edge_src, edge_dst, pos.shape[0])
-        mid = eqlinear(msg, p[pre + "linear_mid.weight"], layer.linear_mid.descriptor) * layer.inv_neighbors
+        mid = eqlinear(msg, p[pre + "linear_mid.weight"], layer.linear_mid.descriptor)   # its coefficients carry 1 / <neighbours>
         prod = stc(mid, p[pre + "product.weight"], species, layer.product.descriptor)
         h = eqlinear(prod, p[pre + "linear_out.weight"], layer.linear_out.descriptor)
         e = e + h[:, : model.channels] @ p[f"readouts.{li}"]
@@ -123,8 +123,8 @@ def nequip_energy_and_forces(model, pos, species, edge_src, edge_dst, edge_shift
             if k + 1 < n_lin:
                 w = torch.nn.functional.silu(w)
         msg = u1d_scatter(w, up, ysh, layer.conv_tp.descriptor, edge_src, edge_dst, pos.shape[0])
-        x = eqlinear(msg, p[pre + "linear_2.weight"], layer.linear_2.descriptor) * layer.inv_neighbors \
-            + eqlinear(h, p[pre + "self_connection.weight"], layer.self_connection.descriptor)
+        x = eqlinear(msg, p[pre + "linear_2.weight"], layer.linear_2.descriptor) \
+            + eqlinear(h, p[pre + "self_connection.weight"], layer.self_connection.descriptor)   # linear_2's coefficients carry 1 / <neighbours>
         h = gate_ref(x, layer.gate_spec)
     e = h[:, : model.channels] @ p["readout"]
     (g,) = torch.autograd.grad(e.sum(), pos)
