@@ -203,7 +203,7 @@ int fasteq_neighbors_fill(const fasteq_nl_problem* p /* host */, void* work, int
  * Replaces the forward_create / forward_run / dgrad_* entries of the reference's
  * EqLinearBackendApi (fasteq/cuda/src/eqlinear/common/eqlinear_backend_api.h:12-27; problem layout
  * eqlinear_common.h:30-62; path mapping (input_row, output_row, weight_path, rows) :32-37).
- * Stateless: the small path tables are host arrays read during the call; there is no plan object
+ * The small path tables are host arrays read during the call; there is no plan object
  * to create or destroy and no weight repacking.
  * ------------------------------------------------------------------------- */
 typedef enum fasteq_eqlinear_precision {
