@@ -203,8 +203,8 @@ int fasteq_neighbors_fill(const fasteq_nl_problem* p /* host */, void* work, int
  * Replaces the forward_create / forward_run / dgrad_* entries of the reference's
  * EqLinearBackendApi (fasteq/cuda/src/eqlinear/common/eqlinear_backend_api.h:12-27; problem layout
  * eqlinear_common.h:30-62; path mapping (input_row, output_row, weight_path, rows) :32-37).
- * The small path tables are host arrays read during the call; there is no plan object
- * to create or destroy and no weight repacking.
+ * The small path tables are host arrays read during the call.  The plain calls prepare the weights on the
+ * fly; fasteq_eqlinear_pack + the _packed calls below let a caller keep the prepared form instead.
  * ------------------------------------------------------------------------- */
 typedef enum fasteq_eqlinear_precision {
   FASTEQ_EQLIN_TF32X3 = 0,   /* FP32 data, 3xTF32 split on tensor cores (error < 2e-5 rel. Frobenius) */
