@@ -65,6 +65,58 @@ def _poly_expr(p: Poly, dt: str) -> str:
     return " + ".join(terms) if terms else ("0.0f" if dt == "f32" else "0.0")
 
 
+def _emit_double_backward(ls, comps, grads, load: str, dt: str) -> str:
+    """Second-order kernel.  With ``t = ggvec`` (cotangent of the vector gradient) and ``g = grad_out``:
+
+        d_grad_out[i] = <dY_i/dv, t>            d_vec = sum_i g_i (d^2 Y_i / dv dv) t
+
+    For normalised input ``Y_i(v) = P_i(v) |v|^-l`` (``P_i`` homogeneous of degree ``l``), so with ``u = v/|v|``:
+
+        dY/dv_a        = (dP/da - l u_a P) / |v|
+        d2Y/dv_a dv_b  = (d2P/da db - l (u_b dP/da + u_a dP/db + delta_ab P) + l (l + 2) u_a u_b P) / |v|^2
+
+    all evaluated at ``u`` (the reference keeps an analytic Hessian-vector product for the same purpose,
+    fasteq/triton/spherical_harmonics.py:368-383)."""
+    n = len(comps)
+    degs = [l for l in ls for _ in range(2 * l + 1)]
+    hess = [[[derivative(grads[a][i], b) for b in range(3)] for a in range(3)] for i in range(n)]
+    polys = list(comps) + [grads[a][i] for a in range(3) for i in range(n)] + [hess[i][a][b] for i in range(n) for a in range(3) for b in range(3)]
+    L = [f"""
+__global__ void __launch_bounds__(256) fasteq_sh_dbwd_kernel(const T* __restrict__ v, const T* __restrict__ gout,
+                                                            const T* __restrict__ ggv, long long n, T* __restrict__ d_gout,
+                                                            T* __restrict__ d_v) {{
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (long long)gridDim.x * blockDim.x) {{
+{load}
+    const T tx = ggv[3 * e], ty = ggv[3 * e + 1], tz = ggv[3 * e + 2];
+    const bool proj = NORMALIZE && (x * x + y * y + z * z) > T(0.5);    // above the clamp: true unit vector
+    const T ut = x * tx + y * ty + z * tz;
+    const T* g = gout + e * NOUT;
+    T* dg = d_gout + e * NOUT;
+    T dvx = T(0), dvy = T(0), dvz = T(0);"""]
+    L += _emit_monomials(_collect(polys), "    ")
+    zero = "T(0)"
+    for i in range(n):
+        l = degs[i]
+        ex = lambda p: _poly_expr(p, dt) if p else zero
+        L.append("    {")
+        L.append(f"      const T P = {ex(comps[i])}, gx_ = {ex(grads[0][i])}, gy_ = {ex(grads[1][i])}, gz_ = {ex(grads[2][i])};")
+        for b, nm in enumerate(("hx", "hy", "hz")):
+            L.append(f"      const T {nm} = tx * ({ex(hess[i][0][b])}) + ty * ({ex(hess[i][1][b])}) + tz * ({ex(hess[i][2][b])});")
+        L.append("      const T gt = gx_ * tx + gy_ * ty + gz_ * tz, gi = g[%d];" % i)
+        L.append(f"      T dgi = gt, ax = hx, ay = hy, az = hz;")
+        if l > 0:
+            L.append(f"      if (proj) {{ dgi -= T({l}) * ut * P;")
+            L.append(f"        ax += -T({l}) * (x * gt + ut * gx_ + tx * P) + T({l * (l + 2)}) * x * ut * P;")
+            L.append(f"        ay += -T({l}) * (y * gt + ut * gy_ + ty * P) + T({l * (l + 2)}) * y * ut * P;")
+            L.append(f"        az += -T({l}) * (z * gt + ut * gz_ + tz * P) + T({l * (l + 2)}) * z * ut * P; }}")
+        L.append(f"      dg[{i}] = dgi * inv; dvx += gi * ax; dvy += gi * ay; dvz += gi * az;")
+        L.append("    }")
+    L.append("    const T inv2 = inv * inv;")
+    L.append("    d_v[3 * e] = dvx * inv2; d_v[3 * e + 1] = dvy * inv2; d_v[3 * e + 2] = dvz * inv2;")
+    L.append("  }\n}")
+    return "\n".join(L)
+
+
 def emit_sh(ls: Tuple[int, ...], dtype: str, normalize: bool, normalization: str) -> str:
     dt = dtype
     ctype = "float" if dt == "f32" else "double"
@@ -120,6 +172,7 @@ __global__ void __launch_bounds__(256) fasteq_sh_bwd_kernel(const T* __restrict_
                 parts.append(f"{name} += gi * ({_poly_expr(grads[ax][i], dt)});")
         if parts:
             src.append(f"    {{ const T gi = g[{i}]; " + " ".join(parts) + " }")
+    dbwd = _emit_double_backward(ls, comps, grads, load, dt)
     src.append("""    if (NORMALIZE) {
       // d(r/|r|)/dr = (I - u u^T) / |r| ; below the clamp the map is linear with slope 1/eps
       const T dot = gx * x + gy * y + gz * z;
@@ -129,6 +182,18 @@ __global__ void __launch_bounds__(256) fasteq_sh_bwd_kernel(const T* __restrict_
     }
     gv[3 * e] = gx; gv[3 * e + 1] = gy; gv[3 * e + 2] = gz;
   }
+}
+""" + dbwd + """
+extern "C" int fasteq_sh_double_backward(const void* vec, const void* grad_out, const void* ggvec, int64_t n, void* d_grad_out,
+                                         void* d_vec, fasteq_stream_t stream) {
+  if (n < 0) return FASTEQ_INVALID;
+  if (n == 0) return FASTEQ_OK;
+  if (!vec || !grad_out || !ggvec || !d_grad_out || !d_vec) return FASTEQ_INVALID;
+  long long blocks = (n + 255) / 256; if (blocks > 148 * 32) blocks = 148 * 32;
+  fasteq_sh_dbwd_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const T*)vec, (const T*)grad_out, (const T*)ggvec, n,
+                                                                          (T*)d_grad_out, (T*)d_vec);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }
 
 extern "C" int fasteq_sh_forward(const void* vec, int64_t n, void* out, fasteq_stream_t stream) {

@@ -141,6 +141,94 @@ extern "C" int fasteq_stc_device_status(int32_t* code) {
 """
 
 
+def _emit_double_backward(spec: STCSpec, groups, dt: str) -> List[str]:
+    """Second-order kernel: with ``t = ggx1`` and ``tw = ggx0`` (per node) the cotangents of the first
+    backward's outputs, and ``m = prod x[a_i] * w`` one monomial,
+
+        D     = d/d eps  m(x + eps t, w + eps tw)            d_go[v] += c D
+        d_w  += c go[v] * dP                                 (dP = sum_i t[a_i] prod_{j != i} x[a_j])
+        d_x[a_k] += c go[v] * (w * d(dP)/dx[a_k] + tw * dP/dx[a_k])
+
+    Factors are handled by position, so repeated indices need no special case.  Straight-line code per
+    monomial (no nesting): this kernel serves force-loss training, not the benchmarked inference path.
+    Counterpart of fasteq/ops/stc_uniform1d_jit.py:964-968 (double-backward ``run(go, x1, x0, i0, ggx0, ggx1, V)``)."""
+    L: List[str] = [f"""
+__global__ void __launch_bounds__(NT) fasteq_stc_dbwd_kernel(const T* __restrict__ go, const T* __restrict__ x1,
+    const T* __restrict__ x0, const int* __restrict__ i0, const T* __restrict__ ggx1, const T* __restrict__ ggx0n,
+    long long batch, long long n_species, T* __restrict__ d_go, T* __restrict__ d_x1, T* __restrict__ d_x0n, int* status) {{
+  for (long long b = blockIdx.x; b < batch; b += gridDim.x) {{
+    int sp = i0[b];
+    if (sp < 0 || sp >= n_species) {{ atomicExch(status, 2); sp = 0; }}
+    for (int u = threadIdx.x; u < U; u += NT) {{
+      const T* xp = x1 + (size_t)b * A * U + u;
+      const T* tp = ggx1 + (size_t)b * A * U + u;
+      const T* wp = x0 + (size_t)sp * D * U + u;
+      const T* twp = ggx0n + (size_t)b * D * U + u;
+      const T* gp = go + (size_t)b * V * U + u;"""]
+    L += [f"      const T x{a} = xp[{a} * U], t{a} = tp[{a} * U];" for a in range(spec.x1_segs)]
+    L += [f"      const T go{v} = gp[{v} * U];" for v in range(spec.out_segs)]
+    L += [f"      T dx{a} = T(0);" for a in range(spec.x1_segs)]
+    L += [f"      T dg{v} = T(0);" for v in range(spec.out_segs)]
+    by_d: Dict[int, List[int]] = {}
+    for (d, v) in groups:
+        by_d.setdefault(d, []).append(v)
+    for d, vs in by_d.items():
+        L.append(f"      {{ const T w = wp[{d} * U], tw = twp[{d} * U]; T dw = T(0);")
+        for v in vs:
+            for a, c in sorted(groups[(d, v)].items()):
+                cl = lit(c, dt)
+                n = len(a)
+                L.append(f"        {{ const T cg = {cl} * go{v};")
+                if n == 1:
+                    (p,) = a
+                    L.append(f"          dg{v} = fma({cl}, fma(t{p}, w, x{p} * tw), dg{v}); dw = fma(cg, t{p}, dw); dx{p} = fma(cg, tw, dx{p}); }}")
+                elif n == 2:
+                    p, q = a
+                    L.append(f"          const T P = x{p} * x{q}, dP = fma(t{p}, x{q}, x{p} * t{q});")
+                    L.append(f"          dg{v} = fma({cl}, fma(dP, w, P * tw), dg{v}); dw = fma(cg, dP, dw);")
+                    L.append(f"          dx{p} = fma(cg, fma(w, t{q}, tw * x{q}), dx{p}); dx{q} = fma(cg, fma(w, t{p}, tw * x{p}), dx{q}); }}")
+                else:
+                    p, q, r = a
+                    L.append(f"          const T pq = x{p} * x{q}, pr = x{p} * x{r}, qr = x{q} * x{r};")
+                    L.append(f"          const T P = pq * x{r}, dP = fma(t{p}, qr, fma(t{q}, pr, t{r} * pq));")
+                    L.append(f"          dg{v} = fma({cl}, fma(dP, w, P * tw), dg{v}); dw = fma(cg, dP, dw);")
+                    L.append(f"          dx{p} = fma(cg, fma(w, fma(t{q}, x{r}, x{q} * t{r}), tw * qr), dx{p});")
+                    L.append(f"          dx{q} = fma(cg, fma(w, fma(t{p}, x{r}, x{p} * t{r}), tw * pr), dx{q});")
+                    L.append(f"          dx{r} = fma(cg, fma(w, fma(t{p}, x{q}, x{p} * t{q}), tw * pq), dx{r}); }}")
+        L.append(f"        d_x0n[((size_t)b * D + {d}) * U + u] = dw; }}")
+    for d in range(spec.x0_segs):
+        if d not in by_d:
+            L.append(f"      d_x0n[((size_t)b * D + {d}) * U + u] = T(0);")
+    L.append("      T* dxp = d_x1 + (size_t)b * A * U + u;")
+    L += [f"      dxp[{a} * U] = dx{a};" for a in range(spec.x1_segs)]
+    L.append("      T* dgp = d_go + (size_t)b * V * U + u;")
+    L += [f"      dgp[{v} * U] = dg{v};" for v in range(spec.out_segs)]
+    L.append("    }\n  }\n}")
+    L.append("""
+extern "C" int fasteq_stc_forward(const void*, const void*, const int32_t*, int64_t, int64_t, void*, fasteq_stream_t) {
+  return FASTEQ_UNSUPPORTED;  // double-backward module
+}
+extern "C" int fasteq_stc_backward(const void*, const void*, const void*, const int32_t*, int64_t, int64_t, void*, void*, fasteq_stream_t) {
+  return FASTEQ_UNSUPPORTED;  // double-backward module
+}
+extern "C" int fasteq_stc_double_backward(const void* go, const void* x1, const void* x0, const int32_t* i0, const void* ggx1,
+                                          const void* ggx0_per_node, int64_t batch, int64_t n_species, void* d_go, void* d_x1,
+                                          void* d_x0_per_node, fasteq_stream_t stream) {
+  if (batch < 0 || n_species < 0) return FASTEQ_INVALID;
+  if (batch == 0) return FASTEQ_OK;
+  if (!go || !x1 || !x0 || !i0 || !ggx1 || !ggx0_per_node || !d_go || !d_x1 || !d_x0_per_node) return FASTEQ_INVALID;
+  int* st = nullptr;
+  cudaError_t e = cudaGetSymbolAddress((void**)&st, g_status_word);
+  if (e != cudaSuccess) return cuda_fail(e);
+  const long long grid = batch < (1LL << 30) ? batch : (1LL << 30);
+  fasteq_stc_dbwd_kernel<<<(unsigned)grid, NT, 0, (cudaStream_t)stream>>>((const T*)go, (const T*)x1, (const T*)x0, i0, (const T*)ggx1,
+      (const T*)ggx0_per_node, batch, n_species, (T*)d_go, (T*)d_x1, (T*)d_x0_per_node, st);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
+}""")
+    return L
+
+
 def emit_stc(spec: STCSpec, direction: str, need_gx0: bool = False) -> str:
     dt = spec.dtype
     groups = _groups(spec)
@@ -156,7 +244,7 @@ constexpr int U = {spec.u}, A = {spec.x1_segs}, D = {spec.x0_segs}, V = {spec.ou
 extern "C" int fasteq_stc_describe(fasteq_stc_desc* d) {{
   if (!d) return FASTEQ_INVALID;
   d->abi_version = FASTEQ_ABI_VERSION; d->dtype = {0 if dt == 'f32' else 1}; d->u = U; d->x1_segs = A; d->x0_segs = D;
-  d->out_segs = V; d->num_paths = {len(spec.paths)}; d->direction = {0 if direction == 'fwd' else 1}; d->need_gx0 = {int(need_gx0)};
+  d->out_segs = V; d->num_paths = {len(spec.paths)}; d->direction = {dict(fwd=0, bwd=1, dbwd=2)[direction]}; d->need_gx0 = {int(need_gx0)};
   return FASTEQ_OK;
 }}
 """
@@ -198,7 +286,14 @@ extern "C" int fasteq_stc_forward(const void* x1, const void* x0, const int32_t*
 }
 extern "C" int fasteq_stc_backward(const void*, const void*, const void*, const int32_t*, int64_t, int64_t, void*, void*, fasteq_stream_t) {
   return FASTEQ_UNSUPPORTED;  // forward module
-}""")
+}
+extern "C" int fasteq_stc_double_backward(const void*, const void*, const void*, const int32_t*, const void*, const void*, int64_t,
+                                          int64_t, void*, void*, void*, fasteq_stream_t) {
+  return FASTEQ_UNSUPPORTED;  // this module holds another direction
+}
+""")
+    elif direction == "dbwd":
+        body += _emit_double_backward(spec, groups, dt)
     else:
         body.append(f"""
 constexpr bool NEED_GX0 = {str(need_gx0).lower()};
@@ -259,5 +354,10 @@ extern "C" int fasteq_stc_backward(const void* go, const void* x1, const void* x
                                                                         n_species, (T*)gx1, (T*)gx0_per_node, st);
   e = cudaGetLastError();
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
-}""")
+}
+extern "C" int fasteq_stc_double_backward(const void*, const void*, const void*, const int32_t*, const void*, const void*, int64_t,
+                                          int64_t, void*, void*, void*, fasteq_stream_t) {
+  return FASTEQ_UNSUPPORTED;  // this module holds another direction
+}
+""")
     return head + "\n".join(body) + "\n"

@@ -114,23 +114,24 @@ class MACEStyleModel(torch.nn.Module):
         self.layers = torch.nn.ModuleList(layers)
         self.readouts = torch.nn.ParameterList(torch.nn.Parameter(torch.randn(channels) / math.sqrt(channels)) for _ in range(num_layers))
 
-    def edge_features(self, pos, edge_src, edge_dst, edge_shift):
-        """(harmonics or None, radial basis, edge vectors or None): with ``fuse_sh`` the vectors go to the layers."""
-        if self.fuse_geometry and edge_geometry_usable(pos, self.num_basis):
+    def edge_features(self, pos, edge_src, edge_dst, edge_shift, second_order: bool = False):
+        """(harmonics or None, radial basis, edge vectors or None): with ``fuse_sh`` the vectors go to the layers.
+        ``second_order``: keep to operators whose backward is itself differentiable (force-loss training)."""
+        if self.fuse_geometry and not second_order and edge_geometry_usable(pos, self.num_basis):
             vec, radial = edge_geometry(pos, edge_src, edge_dst, edge_shift, self.r_max, self.num_basis, self.envelope_p)
         else:
             vec = pos[edge_src] + edge_shift - pos[edge_dst]
             r = vec.norm(dim=-1)
             radial = bessel_basis(r, self.r_max, self.num_basis) * polynomial_cutoff(r, self.r_max, self.envelope_p).unsqueeze(-1)
-        if self.fuse_sh and vec.is_cuda:
+        if self.fuse_sh and not second_order and vec.is_cuda:
             return None, radial, vec
         return self.sh(vec), radial, None
 
-    def node_energies(self, pos, species, edge_src, edge_dst, edge_shift, halo=None):
+    def node_energies(self, pos, species, edge_src, edge_dst, edge_shift, halo=None, second_order: bool = False):
         """``halo`` (a ``parallel.HaloExchange``) extends per-node tensors with ghost rows; ``pos`` and
         ``species`` then hold the owned nodes only and the edge indices are local ids."""
         pos_ext = pos if halo is None else halo(pos)
-        edge_sh, edge_radial, edge_vec = self.edge_features(pos_ext, edge_src, edge_dst, edge_shift)
+        edge_sh, edge_radial, edge_vec = self.edge_features(pos_ext, edge_src, edge_dst, edge_shift, second_order)
         h = self.embedding[species]
         e = pos.new_zeros(pos.shape[0])
         for layer, ro in zip(self.layers, self.readouts):
@@ -139,16 +140,18 @@ class MACEStyleModel(torch.nn.Module):
         return e
 
     def forward(self, pos, species, edge_src, edge_dst, edge_shift, node_graph=None, n_graphs: int = 1, forces: bool = True,
-                halo=None):
+                halo=None, create_graph: bool = False):
+        """``create_graph``: keep the forces differentiable (a force loss can then be back-propagated to the weights);
+        the evaluation then stays on operators with a second-order path (no in-kernel harmonics / fused geometry)."""
         if forces:
             pos = pos.detach().requires_grad_(True)
-        e_node = self.node_energies(pos, species, edge_src, edge_dst, edge_shift, halo)
+        e_node = self.node_energies(pos, species, edge_src, edge_dst, edge_shift, halo, second_order=create_graph)
         if node_graph is None:
             energy = e_node.sum().reshape(1)
         else:
             energy = torch.zeros(n_graphs, dtype=e_node.dtype, device=e_node.device).index_add(0, node_graph, e_node)
         out = {"energy": energy}
         if forces:
-            (g,) = torch.autograd.grad(e_node.sum(), pos)
+            (g,) = torch.autograd.grad(e_node.sum(), pos, create_graph=create_graph)
             out["forces"] = -g
         return out

@@ -77,12 +77,44 @@ class _Dense(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         x, weight = ctx.saved_tensors
-        gx = gw = None
-        if ctx.needs_input_grad[0]:
-            gx = _gemm(grad_out, weight.t(), weight, True)      # [M, N] @ [N, K] with Bt = weight^T [K, N]
-        if ctx.needs_input_grad[1]:
-            gw = grad_out.t() @ x
+        need_x, need_w = ctx.needs_input_grad
+        if not (need_x or need_w):
+            return None, None
+        gx, gw = _DenseBackward.apply(grad_out.contiguous(), x, weight, need_x, need_w)
+        return (gx if need_x else None), (gw if need_w else None)
+
+
+class _DenseBackward(torch.autograd.Function):
+    """First backward as a differentiable function (``y = x W^T`` is bilinear):
+    ``d_g = ggx W^T + x ggW^T``, ``d_x = g ggW``, ``d_W = g^T ggx``."""
+
+    @staticmethod
+    def forward(ctx, g, x, weight, need_x, need_w):
+        ctx.need = (need_x, need_w)
+        ctx.save_for_backward(g, x, weight)
+        ctx.set_materialize_grads(False)
+        gx = _gemm(g, weight.t(), weight, True) if need_x else x.new_empty((0,))     # [M, N] @ [N, K], Bt = weight^T [K, N]
+        gw = g.t() @ x if need_w else weight.new_empty((0,))                         # reduction over the rows: plain matmul
         return gx, gw
+
+    @staticmethod
+    def backward(ctx, ggx, ggw):
+        g, x, weight = ctx.saved_tensors
+        ggx = ggx.contiguous() if (ggx is not None and ctx.need[0]) else None
+        ggw = ggw.contiguous() if (ggw is not None and ctx.need[1]) else None
+        want_g, want_x, want_w = ctx.needs_input_grad[:3]
+        d_g = d_x = d_w = None
+        if want_g:
+            if ggx is not None:
+                d_g = _gemm(ggx, weight, weight, False)
+            if ggw is not None:
+                t = _gemm(x, ggw)
+                d_g = t if d_g is None else d_g + t
+        if want_x and ggw is not None:
+            d_x = _gemm(g, ggw.t())
+        if want_w and ggx is not None:
+            d_w = g.t() @ ggx
+        return d_g, d_x, d_w, None, None
 
 
 def dense(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

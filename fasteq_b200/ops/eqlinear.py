@@ -188,51 +188,116 @@ def _run(lib, prob, w, w3, a, c, geom_key, precision, dgrad: bool, stream):
                 "fasteq_eqlinear_dgrad" if dgrad else "fasteq_eqlinear_forward")
 
 
+class _Plan:
+    """One operator call resolved: geometry, precision and the three launches over the caller's tensors.
+    ``w`` always has the caller's layout ``[P, u, v]`` flattened; ``x`` is ``[batch, I * u]``, ``g`` ``[batch, J * v]``."""
+
+    def __init__(self, geom, precision, batch, w_shape):
+        self.geom, self.precision, self.batch, self.w_shape = geom, precision, batch, tuple(w_shape)
+        mapping, coeff, u, v, I, J = geom
+        self.key = (tuple(mapping), tuple(coeff), u, v, I, J)
+        self.table = [(m[0], m[1], q, m[3]) for q, m in enumerate(mapping)]
+
+    def _problem(self):
+        mapping, coeff, u, v, I, J = self.geom
+        return _make_problem(self.table, coeff, u, v, I, J, self.batch, self.precision)
+
+    def _w3(self, w):
+        mapping, _, u, v, _, _ = self.geom
+        return _order_weights(w.reshape(len(mapping), u, v).contiguous(), mapping)
+
+    def forward(self, w, x):
+        mapping, coeff, u, v, I, J = self.geom
+        x3 = x.reshape(self.batch, I, u).contiguous()
+        out = torch.empty((self.batch, J, v), dtype=x.dtype, device=x.device)
+        with torch.cuda.device(x.device):
+            _run(_core(), self._problem(), w, self._w3(w), x3, out, self.key, self.precision, False,
+                 torch.cuda.current_stream(x.device).cuda_stream)
+        return out.reshape(self.batch, J * v)
+
+    def dgrad(self, w, g):
+        mapping, coeff, u, v, I, J = self.geom
+        g3 = g.reshape(self.batch, J, v).contiguous()
+        dx = torch.empty((self.batch, I, u), dtype=g3.dtype, device=g3.device)
+        with torch.cuda.device(g3.device):
+            _run(_core(), self._problem(), w, self._w3(w), g3, dx, self.key, self.precision, True,
+                 torch.cuda.current_stream(g3.device).cuda_stream)
+        return dx.reshape(self.batch, I * u)
+
+    def wgrad(self, x, g):
+        mapping, coeff, u, v, I, J = self.geom
+        x3 = x.reshape(self.batch, I, u).contiguous()
+        g3 = g.reshape(self.batch, J, v).contiguous()
+        dw = torch.empty((len(mapping), u, v), dtype=g3.dtype, device=g3.device)
+        lib = _core()
+        with torch.cuda.device(g3.device):
+            _cabi.check(lib.fasteq_eqlinear_wgrad(C.byref(self._problem()), x3.data_ptr(), g3.data_ptr(), dw.data_ptr(),
+                                                  torch.cuda.current_stream(g3.device).cuda_stream), lib, "fasteq_eqlinear_wgrad")
+        wps = [m[2] for m in mapping]
+        if wps != list(range(len(wps))):      # block q of the table is block wps[q] of the caller's tensor
+            full = torch.empty_like(dw)
+            full[torch.tensor(wps, device=dw.device)] = dw
+            dw = full
+        return dw.reshape(self.w_shape)
+
+
 class _EqLinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, w, x, geom, precision):
         mapping, coeff, u, v, I, J = geom
-        P = len(mapping)
-        _check_inputs(w, x, u, v, I, P)
-        batch = x.numel() // (I * u)
-        x3 = x.reshape(batch, I, u).contiguous()
-        w3 = _order_weights(w.reshape(P, u, v).contiguous(), mapping)
-        out = torch.empty((batch, J, v), dtype=x.dtype, device=x.device)
-        lib = _core()
-        prob = _make_problem([(m[0], m[1], q, m[3]) for q, m in enumerate(mapping)], coeff, u, v, I, J, batch, precision)
-        geom_key = (tuple(mapping), tuple(coeff), u, v, I, J)
-        with torch.cuda.device(x.device):
-            _run(lib, prob, w, w3, x3, out, geom_key, precision, False, torch.cuda.current_stream(x.device).cuda_stream)
-        ctx.save_for_backward(w3, x3 if ctx.needs_input_grad[0] else None)
-        ctx.geom, ctx.precision, ctx.batch, ctx.w_shape = geom, precision, batch, w.shape
-        ctx.w_ref, ctx.geom_key = w, geom_key
-        return out.reshape(batch, J * v)
+        _check_inputs(w, x, u, v, I, len(mapping))
+        plan = _Plan(geom, precision, x.numel() // (I * u), w.shape)
+        ctx.plan = plan
+        ctx.save_for_backward(w, x)
+        return plan.forward(w, x)
 
     @staticmethod
     def backward(ctx, grad_out):
-        w3, x3 = ctx.saved_tensors
-        mapping, coeff, u, v, I, J = ctx.geom
-        g3 = grad_out.reshape(ctx.batch, J, v).contiguous()
-        lib = _core()
-        prob = _make_problem([(m[0], m[1], q, m[3]) for q, m in enumerate(mapping)], coeff, u, v, I, J, ctx.batch, ctx.precision)
-        dx = dw = None
-        with torch.cuda.device(g3.device):
-            stream = torch.cuda.current_stream(g3.device).cuda_stream
-            if ctx.needs_input_grad[1]:
-                dx = torch.empty((ctx.batch, I, u), dtype=g3.dtype, device=g3.device)
-                _run(lib, prob, ctx.w_ref, w3, g3, dx, ctx.geom_key, ctx.precision, True, stream)
-                dx = dx.reshape(ctx.batch, I * u)
-            if ctx.needs_input_grad[0]:
-                dw = torch.empty((len(mapping), u, v), dtype=g3.dtype, device=g3.device)
-                _cabi.check(lib.fasteq_eqlinear_wgrad(C.byref(prob), x3.data_ptr(), g3.data_ptr(), dw.data_ptr(), stream),
-                            lib, "fasteq_eqlinear_wgrad")
-                wps = [m[2] for m in mapping]
-                if wps != list(range(len(wps))):      # block q of the table is block wps[q] of the caller's tensor
-                    full = torch.empty_like(dw)
-                    full[torch.tensor(wps, device=dw.device)] = dw
-                    dw = full
-                dw = dw.reshape(ctx.w_shape)
-        return dw, dx, None, None
+        w, x = ctx.saved_tensors
+        need_w, need_x = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        if not (need_w or need_x):
+            return None, None, None, None
+        dw, dx = _EqLinearBackwardFn.apply(grad_out.contiguous(), w, x, ctx.plan, need_w, need_x)
+        return (dw if need_w else None), (dx.reshape(x.shape) if need_x else None), None, None
+
+
+class _EqLinearBackwardFn(torch.autograd.Function):
+    """First backward as a differentiable function.  The operator is bilinear in (w, x), so each term of the
+    second backward is one of the three launches again, with a second-order cotangent in place of an operand:
+
+        d_go = F(w, ggx) + F(ggw, x)        d_w = Wg(ggx, go)        d_x = Dg(ggw, go)
+    """
+
+    @staticmethod
+    def forward(ctx, go, w, x, plan, need_w, need_x):
+        ctx.plan, ctx.need = plan, (need_w, need_x)
+        ctx.save_for_backward(go, w, x)
+        ctx.set_materialize_grads(False)
+        dw = plan.wgrad(x, go) if need_w else w.new_empty((0,))
+        dx = plan.dgrad(w, go) if need_x else x.new_empty((0,))
+        return dw, dx
+
+    @staticmethod
+    def backward(ctx, ggw, ggx):
+        go, w, x = ctx.saved_tensors
+        plan = ctx.plan
+        ggw = ggw.contiguous() if (ggw is not None and ctx.need[0]) else None
+        ggx = ggx.contiguous() if (ggx is not None and ctx.need[1]) else None
+        want_go, want_w, want_x = ctx.needs_input_grad[:3]
+        d_go = d_w = d_x = None
+        if want_go:
+            if ggx is not None:
+                d_go = plan.forward(w, ggx)
+            if ggw is not None:
+                t = plan.forward(ggw, x)
+                d_go = t if d_go is None else d_go + t
+            if d_go is not None:
+                d_go = d_go.reshape(go.shape)
+        if want_w and ggx is not None:
+            d_w = plan.wgrad(ggx, go)
+        if want_x and ggw is not None:
+            d_x = plan.dgrad(ggw, go).reshape(x.shape)
+        return d_go, d_w, d_x, None, None, None
 
 
 def fast_equi_linear(descriptor, w, x, *, compute_precision=None):

@@ -4,8 +4,8 @@ Mirror of the reference's ``SphericalHarmonics`` module and ``spherical_harmonic
 (fasteq/triton/spherical_harmonics.py:493-575): ``irreps_out`` may be an int, a list of degrees or an
 irreps string; ``normalize`` divides by ``max(|r|, 1e-12)``; ``normalization`` is ``"integral"``
 (default), ``"component"`` or ``"norm"``.  The kernels are generated per (degrees, dtype, flags) and
-called through the C ABI (``fasteq_sh_forward`` / ``fasteq_sh_backward``).  The backward is not
-itself differentiable.
+called through the C ABI (``fasteq_sh_forward`` / ``fasteq_sh_backward`` / ``fasteq_sh_double_backward``);
+the backward is itself differentiable (Hessian-vector kernel), so force losses can be trained.
 """
 from __future__ import annotations
 
@@ -29,11 +29,12 @@ def _module(ls: Tuple[int, ...], dtype: torch.dtype, normalize: bool, normalizat
         lib = _MODULES.get(key)
     if lib is None:
         dt = "f32" if dtype == torch.float32 else "f64"
-        name = f"sh_{'_'.join(map(str, ls))}_{dt}_{int(normalize)}_{normalization}_v1"
+        name = f"sh_{'_'.join(map(str, ls))}_{dt}_{int(normalize)}_{normalization}_v2"
         so = _build.build_generated(name, _emit.emit_sh(ls, dt, normalize, normalization))
         lib = C.CDLL(so, mode=C.RTLD_LOCAL)
         lib.fasteq_sh_forward.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
         lib.fasteq_sh_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
+        lib.fasteq_sh_double_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]
         lib.fasteq_last_cuda_error.restype = C.c_char_p
         with _lock:
             _MODULES.setdefault(key, lib)
@@ -51,21 +52,46 @@ class _SH(torch.autograd.Function):
         with torch.cuda.device(x.device):
             _cabi.check(lib.fasteq_sh_forward(flat.data_ptr(), n, out.data_ptr(), torch.cuda.current_stream(x.device).cuda_stream),
                         lib, "fasteq_sh_forward")
-        ctx.save_for_backward(flat)
+        ctx.save_for_backward(x)       # the input itself: a view made here would be cut off from its autograd history
         ctx.cfg = (ls, normalize, normalization, x.shape)
         return out.reshape(*x.shape[:-1], nout)
 
     @staticmethod
     def backward(ctx, grad_out):
-        (flat,) = ctx.saved_tensors
+        (x,) = ctx.saved_tensors
         ls, normalize, normalization, shape = ctx.cfg
+        flat = x.reshape(-1, 3)
         g = grad_out.reshape(flat.shape[0], -1).contiguous()
+        return _SHBackward.apply(g, flat, ls, normalize, normalization).reshape(shape), None, None, None
+
+
+class _SHBackward(torch.autograd.Function):
+    """Vector gradient as a differentiable function: its backward is the generated Hessian-vector kernel."""
+
+    @staticmethod
+    def forward(ctx, g, flat, ls, normalize, normalization):
         gv = torch.empty_like(flat)
         lib = _module(ls, flat.dtype, normalize, normalization)
         with torch.cuda.device(flat.device):
             _cabi.check(lib.fasteq_sh_backward(flat.data_ptr(), g.data_ptr(), flat.shape[0], gv.data_ptr(),
                                                torch.cuda.current_stream(flat.device).cuda_stream), lib, "fasteq_sh_backward")
-        return gv.reshape(shape), None, None, None
+        ctx.save_for_backward(g, flat)
+        ctx.cfg = (ls, normalize, normalization)
+        return gv
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, ggv):
+        g, flat = ctx.saved_tensors
+        ls, normalize, normalization = ctx.cfg
+        t = ggv.reshape(flat.shape).contiguous()
+        d_g, d_v = torch.empty_like(g), torch.empty_like(flat)
+        lib = _module(ls, flat.dtype, normalize, normalization)
+        with torch.cuda.device(flat.device):
+            _cabi.check(lib.fasteq_sh_double_backward(flat.data_ptr(), g.data_ptr(), t.data_ptr(), flat.shape[0], d_g.data_ptr(),
+                                                      d_v.data_ptr(), torch.cuda.current_stream(flat.device).cuda_stream),
+                        lib, "fasteq_sh_double_backward")
+        return d_g, d_v, None, None, None
 
 
 class SphericalHarmonics(torch.nn.Module):

@@ -20,7 +20,7 @@ from .. import _build, _cabi
 from ..codegen import stc as _emit
 
 STC_PAD_VALUE = -1
-_EMITTER_VERSION = "stc-v1"
+_EMITTER_VERSION = "stc-v2"
 _lock = threading.Lock()
 
 
@@ -37,6 +37,7 @@ class STCModule:
         lib.fasteq_stc_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
         lib.fasteq_stc_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                             C.c_void_p, C.c_void_p, C.c_void_p]
+        lib.fasteq_stc_double_backward.argtypes = [C.c_void_p] * 6 + [C.c_int64, C.c_int64] + [C.c_void_p] * 4
         lib.fasteq_stc_device_status.argtypes = [C.POINTER(C.c_int32)]
         lib.fasteq_last_cuda_error.restype = C.c_char_p
         self.lib = lib
@@ -120,7 +121,7 @@ class FastSymmetricTensorContractionUniform1dFunction(torch.autograd.Function):
         with torch.cuda.device(x1.device):
             _cabi.check(mod.lib.fasteq_stc_forward(x1c.data_ptr(), x0c.data_ptr(), i32.data_ptr(), B, x0c.shape[0], out.data_ptr(),
                                                    torch.cuda.current_stream(x1.device).cuda_stream), mod.lib, "fasteq_stc_forward")
-        ctx.save_for_backward(x1c, x0c, i32)
+        ctx.save_for_backward(x1, x0, i32)      # the inputs themselves, so that a second backward reaches them
         ctx.spec = spec
         return out.view(B, -1)
 
@@ -131,8 +132,21 @@ class FastSymmetricTensorContractionUniform1dFunction(torch.autograd.Function):
         need_x1, need_x0 = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         if not (need_x1 or need_x0):
             return (None,) * 8
+        gx1, gx0n = FastSTCBackwardFunction.apply(grad_out.contiguous(), x1.contiguous(), x0.contiguous(), i32, spec, bool(need_x0))
+        gx0 = None
+        if need_x0:
+            # summed over nodes of equal species here (differentiable torch op; the kernel writes per-node rows)
+            gx0 = torch.zeros_like(x0).index_add(0, i32.long(), gx0n)
+        return (gx1 if need_x1 else None), gx0, None, None, None, None, None, None
+
+
+class FastSTCBackwardFunction(torch.autograd.Function):
+    """First backward as a differentiable function (reference: fasteq/ops/stc_uniform1d_jit.py:801-901), so that
+    force losses can be trained: its own backward is the generated second-order kernel."""
+
+    @staticmethod
+    def forward(ctx, go, x1, x0, i32, spec, need_x0):
         B = x1.shape[0]
-        go = grad_out.contiguous()
         gx1 = torch.empty_like(x1)
         gx0n = torch.empty((B, spec.x0_segs, spec.u), dtype=x1.dtype, device=x1.device) if need_x0 else None
         mod = get_module(spec, "bwd", bool(need_x0))
@@ -140,10 +154,33 @@ class FastSymmetricTensorContractionUniform1dFunction(torch.autograd.Function):
             _cabi.check(mod.lib.fasteq_stc_backward(go.data_ptr(), x1.data_ptr(), x0.data_ptr(), i32.data_ptr(), B, x0.shape[0],
                                                     gx1.data_ptr(), gx0n.data_ptr() if need_x0 else None,
                                                     torch.cuda.current_stream(x1.device).cuda_stream), mod.lib, "fasteq_stc_backward")
-        gx0 = None
-        if need_x0:
-            gx0 = torch.zeros_like(x0).index_add_(0, i32.long(), gx0n)
-        return (gx1 if need_x1 else None), gx0, None, None, None, None, None, None
+        ctx.save_for_backward(go, x1, x0, i32)
+        ctx.spec, ctx.need_x0 = spec, need_x0
+        return gx1, (gx0n if need_x0 else x1.new_empty((0,)))
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, ggx1, ggx0n):
+        go, x1, x0, i32 = ctx.saved_tensors
+        spec = ctx.spec
+        B = x1.shape[0]
+        ggx1 = ggx1.contiguous() if ggx1 is not None else torch.zeros_like(x1)
+        if ctx.need_x0 and ggx0n is not None:
+            ggx0n = ggx0n.contiguous()
+        else:
+            ggx0n = torch.zeros((B, spec.x0_segs, spec.u), dtype=x1.dtype, device=x1.device)
+        d_go = torch.empty((B, spec.out_segs, spec.u), dtype=x1.dtype, device=x1.device)
+        d_x1 = torch.empty_like(x1)
+        d_x0n = torch.empty((B, spec.x0_segs, spec.u), dtype=x1.dtype, device=x1.device)
+        mod = get_module(spec, "dbwd")
+        with torch.cuda.device(x1.device):
+            _cabi.check(mod.lib.fasteq_stc_double_backward(go.data_ptr(), x1.data_ptr(), x0.data_ptr(), i32.data_ptr(), ggx1.data_ptr(),
+                                                           ggx0n.data_ptr(), B, x0.shape[0], d_go.data_ptr(), d_x1.data_ptr(),
+                                                           d_x0n.data_ptr(), torch.cuda.current_stream(x1.device).cuda_stream),
+                        mod.lib, "fasteq_stc_double_backward")
+        want = ctx.needs_input_grad
+        d_x0 = torch.zeros_like(x0).index_add_(0, i32.long(), d_x0n) if want[2] else None
+        return (d_go.view(go.shape) if want[0] else None), (d_x1 if want[1] else None), d_x0, None, None, None
 
 
 def fast_stc_uniform1d_jit(x1, x0, i0, coeffs_tensor, paths_tensor, idx_lists_tensor, num_out_segments: int, *,

@@ -133,6 +133,14 @@ int fasteq_stc_forward(const void* x1, const void* x0, const int32_t* i0, int64_
  * species (the reference does the same with index_add_, stc_uniform1d_jit.py:883-886). */
 int fasteq_stc_backward(const void* grad_out, const void* x1, const void* x0, const int32_t* i0, int64_t batch,
                         int64_t n_species, void* grad_x1, void* grad_x0_per_node, fasteq_stream_t stream);
+/* Second order (modules built for direction 2; others return FASTEQ_UNSUPPORTED): with ggx1 [batch, x1_segs, u] and
+ * ggx0_per_node [batch, x0_segs, u] the cotangents of grad_x1 and of the per-node grad_x0, writes the
+ * gradients of <ggx1, grad_x1> + <ggx0, grad_x0> with respect to grad_out, x1 and (per node) x0.
+ * Replaces the reference's double-backward launcher run(go, x1, x0, i0, ggx0, ggx1, V) -> (dgo, dx1, dx0)
+ * (fasteq/ops/stc_uniform1d_jit.py:964-968). */
+int fasteq_stc_double_backward(const void* grad_out, const void* x1, const void* x0, const int32_t* i0, const void* ggx1,
+                               const void* ggx0_per_node, int64_t batch, int64_t n_species, void* d_grad_out, void* d_x1,
+                               void* d_x0_per_node, fasteq_stream_t stream);
 int fasteq_stc_device_status(int32_t* code /* host */);
 
 /* ------------------------------------------------------------------------- *
@@ -143,6 +151,11 @@ int fasteq_stc_device_status(int32_t* code /* host */);
 int fasteq_sh_num_outputs(void);
 int fasteq_sh_forward(const void* vec, int64_t n, void* out, fasteq_stream_t stream);
 int fasteq_sh_backward(const void* vec, const void* grad_out, int64_t n, void* grad_vec, fasteq_stream_t stream);
+/* Second order: with ggvec [n, 3] the cotangent of grad_vec, d_grad_out[i] = <dY_i/dvec, ggvec> and
+ * d_vec = sum_i grad_out[i] (d2Y_i / dvec dvec) ggvec (the reference's double backward uses an analytic
+ * Hessian-vector product for the same purpose, fasteq/triton/spherical_harmonics.py:368-383). */
+int fasteq_sh_double_backward(const void* vec, const void* grad_out, const void* ggvec, int64_t n, void* d_grad_out, void* d_vec,
+                              fasteq_stream_t stream);
 
 /* ------------------------------------------------------------------------- *
  * Core library.

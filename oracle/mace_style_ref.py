@@ -57,11 +57,13 @@ def stc(x1, x0, i0, d):
     return torch.stack([r if r is not None else zero for r in acc], dim=1).reshape(x3.shape[0], -1)
 
 
-def energy_and_forces(model, pos, species, edge_src, edge_dst, edge_shift):
-    """Evaluate ``model`` (a ``MACEStyleModel`` whose parameters were moved to CPU/float64) with the oracle operators."""
+def energy_and_forces(model, pos, species, edge_src, edge_dst, edge_shift, params=None, create_graph=False):
+    """Evaluate ``model`` (a ``MACEStyleModel`` whose parameters were moved to CPU/float64) with the oracle operators.
+    ``params`` (optional) replaces the state dict, e.g. with leaves that require grad; with ``create_graph`` the
+    forces stay attached to the graph so that a force loss can be differentiated."""
     from fasteq_b200.nn.mace_style import bessel_basis, polynomial_cutoff
     pos = pos.detach().double().requires_grad_(True)
-    p = {k: v.detach().double().cpu() for k, v in model.state_dict().items()}
+    p = params if params is not None else {k: v.detach().double().cpu() for k, v in model.state_dict().items()}
     vec = pos[edge_src] + edge_shift.double() - pos[edge_dst]
     r = vec.norm(dim=-1)
     radial = bessel_basis(r, model.r_max, model.num_basis) * polynomial_cutoff(r, model.r_max, model.envelope_p).unsqueeze(-1)
@@ -82,8 +84,19 @@ def energy_and_forces(model, pos, species, edge_src, edge_dst, edge_shift):
         prod = stc(mid, p[pre + "product.weight"], species, layer.product.descriptor)
         h = eqlinear(prod, p[pre + "linear_out.weight"], layer.linear_out.descriptor)
         e = e + h[:, : model.channels] @ p[f"readouts.{li}"]
-    (g,) = torch.autograd.grad(e.sum(), pos)
-    return e.detach(), -g
+    (g,) = torch.autograd.grad(e.sum(), pos, create_graph=create_graph)
+    return (e if create_graph else e.detach()), -g
+
+
+def force_loss_gradients(model, pos, species, edge_src, edge_dst, edge_shift, target_forces, names):
+    """d/d(parameter) of ``sum |F - F_target|^2`` for the named parameters (float64, double backward on the CPU)."""
+    p = {k: v.detach().double().cpu() for k, v in model.state_dict().items()}
+    for n in names:
+        p[n] = p[n].clone().requires_grad_(True)
+    _, f = energy_and_forces(model, pos, species, edge_src, edge_dst, edge_shift, params=p, create_graph=True)
+    loss = ((f - target_forces.double()) ** 2).sum()
+    grads = torch.autograd.grad(loss, [p[n] for n in names])
+    return float(loss), dict(zip(names, grads))
 
 
 def gate_ref(x, spec):

@@ -51,3 +51,22 @@ def test_dense_leading_dimensions_and_fallback_dtypes():
     assert out.shape == (5, 31, 64) and _rel(out.cpu(), x @ w.t()) <= 1e-14
     out32 = dense(x.float().cuda(), w.float().cuda())
     assert out32.shape == (5, 31, 64) and _rel(out32.cpu(), x @ w.t()) <= 2e-6
+
+
+def test_dense_second_order():
+    from fasteq_b200.ops.dense import dense
+    g = torch.Generator().manual_seed(8)
+    M, N, K = 300, 64, 64
+    x, w, go = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g) / 8, torch.randn(M, N, generator=g)
+    rx, rw = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+
+    def second(fn, dev, dt):
+        xt, wt, gt = (t.to(dt).to(dev).requires_grad_(True) for t in (x, w, go))
+        gx, gw = torch.autograd.grad(fn(xt, wt), (xt, wt), gt, create_graph=True)
+        L = (gx * rx.to(dt).to(dev)).sum() + (gw * rw.to(dt).to(dev)).sum()
+        return [t.detach().cpu().double() for t in torch.autograd.grad(L, (gt, xt, wt))]
+
+    ref = second(lambda a, b: a @ b.t(), "cpu", torch.float64)
+    got = second(dense, "cuda", torch.float32)
+    for a, b in zip(got, ref):
+        assert _rel(a, b) <= 1e-5

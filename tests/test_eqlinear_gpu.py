@@ -130,3 +130,35 @@ def test_weight_gradient_with_permuted_weight_blocks():
     (gw,) = torch.autograd.grad(out, wd, r.cuda())
     ref = eqlinear_ref.eqlinear_wgrad(x.numpy().reshape(B, I, u), r.numpy().reshape(B, J, v), mapping, coeff, len(d.paths))
     assert _rel_fro(gw.cpu().numpy().reshape(ref.shape), ref) <= 1e-12
+
+
+def test_second_order_by_composition():
+    """The first backward is differentiable (force-loss training): gradients of <r_x, grad_x> + <r_w, grad_w>
+    with respect to grad_out, w and x against torch autograd on a float64 restatement."""
+    from fasteq_b200.ops.eqlinear import fast_equi_linear, _descriptor_problem
+    d = linear("24x0e+24x1o+24x1o+24x2e", "40x0e+40x1o+40x2e")
+    mapping, coeff, u, v, I, J = _descriptor_problem(d)
+    g = torch.Generator().manual_seed(9)
+    B = 130
+    x = torch.randn(B, I * u, generator=g, dtype=torch.float64)
+    w = torch.randn(len(d.paths) * u * v, generator=g, dtype=torch.float64)
+    go = torch.randn(B, J * v, generator=g, dtype=torch.float64)
+    rx, rw = torch.randn(B, I * u, generator=g, dtype=torch.float64), torch.randn(w.shape, generator=g, dtype=torch.float64)
+
+    def ref_fn(wt, xt):
+        w3, x3 = wt.reshape(len(d.paths), u, v), xt.reshape(B, I, u)
+        out = xt.new_zeros(B, J, v)
+        for (ir, orow, wp, rows), c in zip(mapping, coeff):
+            out[:, orow:orow + rows, :] = out[:, orow:orow + rows, :] + c * (x3[:, ir:ir + rows, :] @ w3[wp])
+        return out.reshape(B, J * v)
+
+    def second(fn, dev):
+        wt, xt, gt = (t.to(dev).requires_grad_(True) for t in (w, x, go))
+        gw, gx = torch.autograd.grad(fn(wt, xt), (wt, xt), gt, create_graph=True)
+        L = (gx * rx.to(dev)).sum() + (gw * rw.to(dev)).sum()
+        return [t.detach().cpu() for t in torch.autograd.grad(L, (gt, wt, xt))]
+
+    ref = second(ref_fn, "cpu")
+    got = second(lambda wt, xt: fast_equi_linear(d, wt, xt), "cuda")
+    for a, b in zip(got, ref):
+        assert _rel_fro(a.numpy(), b.numpy()) <= 1e-12

@@ -45,3 +45,42 @@ def test_zero_vector_is_finite():
     sh = spherical_harmonics(3, v, True, "component")
     (g,) = torch.autograd.grad(sh.sum(), v)
     assert torch.isfinite(sh).all() and torch.isfinite(g).all()
+
+
+@pytest.mark.parametrize("normalize,normalization", [(True, "component"), (False, "integral")])
+def test_second_order_matches_torch_autograd(normalize, normalization):
+    """The vector gradient is differentiable: d/d(grad_out) and d/d(vec) of <r, grad_vec> against torch autograd on a
+    float64 evaluation of the same polynomials."""
+    import math
+    from fasteq_b200.ops.spherical_harmonics import SphericalHarmonics
+    from fasteq_b200.sh import sh_polynomials
+    ls = [0, 1, 2, 3]
+    table = sh_polynomials(3)
+
+    def ref_sh(v):
+        if normalize:
+            v = v / v.norm(dim=-1, keepdim=True).clamp_min(1e-12)
+        cols = []
+        for l in ls:
+            scale = {"component": 1.0, "norm": 1.0 / math.sqrt(2 * l + 1), "integral": 1.0 / math.sqrt(4 * math.pi)}[normalization]
+            for p in table[l]:
+                acc = torch.zeros_like(v[:, 0])
+                for (a, b, c), coef in p.items():
+                    acc = acc + coef * scale * v[:, 0] ** a * v[:, 1] ** b * v[:, 2] ** c
+                cols.append(acc)
+        return torch.stack(cols, 1)
+
+    g = torch.Generator().manual_seed(2)
+    vec = torch.randn(200, 3, generator=g, dtype=torch.float64) * 1.7
+    go = torch.randn(200, 16, generator=g, dtype=torch.float64)
+    r = torch.randn(200, 3, generator=g, dtype=torch.float64)
+
+    def second(fn, dev):
+        v, gt = vec.to(dev).requires_grad_(True), go.to(dev).requires_grad_(True)
+        (gv,) = torch.autograd.grad(fn(v), v, gt, create_graph=True)
+        return [t.detach().cpu() for t in torch.autograd.grad((gv * r.to(dev)).sum(), (gt, v))]
+
+    ref = second(ref_sh, "cpu")
+    got = second(SphericalHarmonics(ls, normalize, normalization), "cuda")
+    for a, b in zip(got, ref):
+        assert float((a - b).abs().max()) <= 1e-10 * max(1.0, float(b.abs().max()))

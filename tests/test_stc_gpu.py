@@ -58,3 +58,47 @@ def test_rejects_cpu_and_mismatched_inputs():
         fast_stc_uniform1d_jit(x1, x0.double(), i0, coeffs, paths, idx_lists, d.out_segs)
     out = fast_stc_uniform1d_jit(x1, x0, i0, coeffs, paths, idx_lists, d.out_segs)
     assert out.shape == (3, d.out_segs * 4) and float(out.abs().max()) == 0.0
+
+
+def _torch_stc(x1, x0, i0, paths, coeffs, out_segs, pad_value=-1):
+    """Differentiable float64 restatement of the path formula (for second-order references)."""
+    B, _, U = x1.shape
+    xg = x0[i0]
+    cols = [x1.new_zeros(B, U) for _ in range(out_segs)]
+    for row, c in zip(paths, coeffs):
+        vals = [int(t) for t in row if int(t) != pad_value]
+        a, d, v = vals[:-2], vals[-2], vals[-1]
+        term = xg[:, d, :] * float(c)
+        for t in a:
+            term = term * x1[:, t, :]
+        cols[v] = cols[v] + term
+    return torch.stack(cols, 1).reshape(B, out_segs * U)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float64, 1e-11), (torch.float32, 2e-5)])
+def test_second_order_matches_torch_autograd(dtype, tol):
+    """grad of <r1, grad_x1> + <r0, grad_x0> with respect to grad_out, x1 and x0 (what a force loss needs)."""
+    from fasteq_b200.ops import fast_stc_uniform1d_jit
+    d = symmetric_contraction("16x0e+16x1o+16x2e", "16x0e+16x1o")
+    U, B, S = d.u_dim, 37, 3
+    g = torch.Generator().manual_seed(1)
+    x1 = (torch.randn(B, d.x1_segs, U, generator=g, dtype=torch.float64) * 0.5)
+    x0 = (torch.randn(S, d.x0_segs, U, generator=g, dtype=torch.float64) * 0.3)
+    i0 = torch.randint(0, S, (B,), generator=g)
+    go = torch.randn(B, d.out_segs * U, generator=g, dtype=torch.float64)
+    r1 = torch.randn(B, d.x1_segs, U, generator=g, dtype=torch.float64)
+    r0 = torch.randn(S, d.x0_segs, U, generator=g, dtype=torch.float64)
+
+    def second_order(fn, dt, dev):
+        a, w, gout = (t.to(dt).to(dev).requires_grad_(True) for t in (x1, x0, go))
+        out = fn(a, w)
+        gx1, gx0 = torch.autograd.grad(out, (a, w), gout, create_graph=True)
+        L = (gx1 * r1.to(dt).to(dev)).sum() + (gx0 * r0.to(dt).to(dev)).sum()
+        return [t.detach().cpu().double() for t in torch.autograd.grad(L, (gout, a, w))]
+
+    ref = second_order(lambda a, w: _torch_stc(a, w, i0, d.paths, d.coeffs, d.out_segs), torch.float64, "cpu")
+    coeffs, paths, idx_lists = d.tensors(dtype, "cuda")
+    got = second_order(lambda a, w: fast_stc_uniform1d_jit(a, w, i0.cuda(), coeffs, paths, idx_lists, d.out_segs), dtype, "cuda")
+    for name, a, b in zip(("d grad_out", "d x1", "d x0"), got, ref):
+        err = float((a - b).abs().max() / b.abs().max())
+        assert err <= tol, f"{name}: relative error {err:.3e}"
