@@ -183,6 +183,13 @@ radial_chain_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         tma_load_3d(slab1, &tmIO1, col0, (int)r0, n_tc - 1, full1);
       }
     }
+    // the basis row of a tile is fetched one tile ahead, so its global-load latency is off the chain
+    float b_next[NB];
+    {
+      const long long r = (long long)blockIdx.x * BM + quarter * 32 + lane;
+#pragma unroll
+      for (int k = 0; k < NB; ++k) b_next[k] = (r < a.M && k < a.nb) ? __ldg(a.basis + r * a.nb + k) : 0.f;
+    }
     for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
       const long long row0 = tile * BM + quarter * 32;
       const long long row = row0 + lane;
@@ -191,7 +198,12 @@ radial_chain_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       const bool has_next = tile + gridDim.x < n_tiles;
       float b[NB];
 #pragma unroll
-      for (int k = 0; k < NB; ++k) b[k] = (valid && k < a.nb) ? __ldg(a.basis + row * a.nb + k) : 0.f;
+      for (int k = 0; k < NB; ++k) b[k] = b_next[k];
+      {
+        const long long r = next_row0 + lane;
+#pragma unroll
+        for (int k = 0; k < NB; ++k) b_next[k] = (has_next && r < a.M && k < a.nb) ? __ldg(a.basis + r * a.nb + k) : 0.f;
+      }
       float v[32];
       if (!BWD) {
 #pragma unroll
