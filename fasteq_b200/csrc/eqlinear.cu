@@ -35,6 +35,7 @@ struct GroupTable {
   float path_coeff_f[kMaxPaths];
   double path_coeff_d[kMaxPaths];
   long long tile_first[kMaxPaths + 1];  // prefix of row tiles per group
+  long long wide_tile_first[kMaxPaths + 1];  // the same for 128-row tiles
 };
 
 template <typename T> __device__ __forceinline__ T coeff_of(const GroupTable& t, int q);
@@ -148,6 +149,122 @@ __global__ void __launch_bounds__(NT) eqlinear_kernel(const __grid_constant__ Gr
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// FP64 variant with a 128 x 128 tile and 8 x 8 outputs per thread: the 64 x 64 kernel above spends two
+// shared-memory wavefronts per FMA wavefront in FP64 (4 x 4 outputs per 8 operand loads), this one a
+// quarter of that.  A thread owns rows {32 i + 2 ty + r} and columns {32 j + 2 tx + c} (i, j < 4; r, c < 2),
+// so that every operand load is one conflict-free 16-byte access per quarter warp.  Global tiles are
+// fetched one step ahead into registers.  Plain (non-blocked) summation: FP64 has the head-room.
+constexpr int WM = 128, WN = 128, WK = 8;
+
+template <bool TRANS>
+__global__ void __launch_bounds__(NT) eqlinear_wide_f64_kernel(const __grid_constant__ GroupTable tab, const double* __restrict__ A,
+                                                               const double* __restrict__ W, double* __restrict__ C, long long batch,
+                                                               int a_rows_per_b, int c_rows_per_b, int K, int N, int u, int v) {
+  __shared__ double sA[2][WK][WM + 2];
+  __shared__ double sW[2][WK][WN + 2];
+  const long long tile = blockIdx.x;
+  int g = 0;
+  while (g + 1 < tab.n_groups && tile >= tab.wide_tile_first[g + 1]) ++g;
+  const long long row0 = (tile - tab.wide_tile_first[g]) * WM;
+  const int gi = tab.group_rows[g];
+  const long long n_rows = batch * gi;
+  const int n0 = blockIdx.y * WN;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  double acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.0;
+
+  // A loader: thread -> (row = tid / 2, four consecutive k starting at 4 * (tid % 2))
+  const int lrow = threadIdx.x / 2, lk = (threadIdx.x % 2) * 4;
+  const long long ar = row0 + lrow;
+  const bool avalid = ar < n_rows;
+  const size_t abase = avalid ? ((size_t)(ar / gi) * a_rows_per_b + (size_t)(ar % gi)) * (size_t)K : 0;
+  // W loader: TRANS (W used as [k = v index][n = u index], contiguous in k): like A; else contiguous in n
+  const int wn_t = threadIdx.x / 2, wk_t = (threadIdx.x % 2) * 4;     // TRANS
+  const int wk_n = threadIdx.x / 32, wn_n = (threadIdx.x % 32) * 4;   // not TRANS
+
+  const int q0 = tab.group_first[g], q1 = tab.group_first[g + 1];
+  const int k_steps = (K + WK - 1) / WK;
+  const int total_steps = (q1 - q0) * k_steps;
+  double ra[4], rw[4];
+  auto fetch = [&](int step) {
+    const int q = q0 + step / k_steps, k0 = (step % k_steps) * WK;
+    const double cq = tab.path_coeff_d[q];
+    const double* aq = A + (size_t)tab.path_a_row[q] * K;
+    const double* wq = W + (size_t)tab.path_w[q] * u * v;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int k = k0 + lk + e;
+      ra[e] = (avalid && k < K) ? cq * aq[abase + k] : 0.0;       // the path coefficient rides on the A operand
+    }
+    if (TRANS) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int k = k0 + wk_t + e, n = n0 + wn_t;
+        rw[e] = (k < K && n < N) ? wq[(size_t)n * v + k] : 0.0;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int k = k0 + wk_n, n = n0 + wn_n + e;
+        rw[e] = (k < K && n < N) ? wq[(size_t)k * v + n] : 0.0;
+      }
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) sA[buf][lk + e][lrow] = ra[e];
+    if (TRANS) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sW[buf][wk_t + e][wn_t] = rw[e];
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sW[buf][wk_n][wn_n + e] = rw[e];
+    }
+  };
+  if (total_steps > 0) { fetch(0); stash(0); }
+  __syncthreads();
+  for (int step = 0; step < total_steps; ++step) {
+    const int buf = step & 1;
+    if (step + 1 < total_steps) fetch(step + 1);
+#pragma unroll
+    for (int k = 0; k < WK; ++k) {
+      double a[8], b[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const double2 t = *reinterpret_cast<const double2*>(&sA[buf][k][32 * i + 2 * ty]);
+        a[2 * i] = t.x; a[2 * i + 1] = t.y;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const double2 t = *reinterpret_cast<const double2*>(&sW[buf][k][32 * j + 2 * tx]);
+        b[2 * j] = t.x; b[2 * j + 1] = t.y;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fma(a[i], b[j], acc[i][j]);
+    }
+    if (step + 1 < total_steps) stash(buf ^ 1);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const long long rr = row0 + 32 * (i / 2) + 2 * ty + (i & 1);
+    if (rr >= n_rows) continue;
+    double* crow = C + ((size_t)(rr / gi) * c_rows_per_b + tab.group_c_row[g] + (int)(rr % gi)) * (size_t)N;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + 32 * j + 2 * tx;
+      if (n + 1 < N) *reinterpret_cast<double2*>(crow + n) = make_double2(acc[i][2 * j], acc[i][2 * j + 1]);
+      else if (n < N) crow[n] = acc[i][2 * j];
+    }
+  }
+}
+
 // rows of C that no group writes must read as zero
 template <typename T>
 __global__ void zero_rows_kernel(T* C, long long batch, int c_rows_per_b, int N, const __grid_constant__ GroupTable tab) {
@@ -193,9 +310,11 @@ int build_table(const fasteq_eqlinear_problem* p, bool dgrad, GroupTable* t, boo
     t->path_coeff_d[k] = p->coeff[q];
   }
   t->group_first[t->n_groups] = P;
-  t->tile_first[0] = 0;
-  for (int g = 0; g < t->n_groups; ++g)
+  t->tile_first[0] = 0; t->wide_tile_first[0] = 0;
+  for (int g = 0; g < t->n_groups; ++g) {
     t->tile_first[g + 1] = t->tile_first[g] + (p->batch * t->group_rows[g] + BM - 1) / BM;
+    t->wide_tile_first[g + 1] = t->wide_tile_first[g] + (p->batch * t->group_rows[g] + 127) / 128;
+  }
   *covers_all = true;
   for (int r = 0; r < c_rows; ++r) if (!covered[r]) *covers_all = false;
   return FASTEQ_OK;
@@ -213,6 +332,15 @@ int launch(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const vo
   if (!covers) {
     const long long total = p->batch * c_rows * N;
     zero_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, s>>>((T*)c, p->batch, c_rows, N, tab);
+  }
+  if (sizeof(T) == 8 && N >= 64 && (N % 2) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0) {
+    const long long wt = tab.wide_tile_first[tab.n_groups];
+    if (wt > 0x7fffffffLL) return FASTEQ_UNSUPPORTED;
+    dim3 wgrid((unsigned)wt, (unsigned)((N + WN - 1) / WN));
+    if (dgrad) eqlinear_wide_f64_kernel<true><<<wgrid, NT, 0, s>>>(tab, (const double*)a, (const double*)w, (double*)c, p->batch, a_rows, c_rows, K, N, p->u, p->v);
+    else       eqlinear_wide_f64_kernel<false><<<wgrid, NT, 0, s>>>(tab, (const double*)a, (const double*)w, (double*)c, p->batch, a_rows, c_rows, K, N, p->u, p->v);
+    cudaError_t we = cudaGetLastError();
+    return we == cudaSuccess ? FASTEQ_OK : cuda_fail(we);
   }
   const long long tiles = tab.tile_first[tab.n_groups];
   if (tiles > 0x7fffffffLL) return FASTEQ_UNSUPPORTED;
