@@ -89,6 +89,68 @@ __global__ void gate_bwd_kernel(const T* __restrict__ x, const T* __restrict__ g
   }
 }
 
+template <typename T> __device__ __forceinline__ T act_dd(int code, T x) {
+  switch (code) {
+    case 1: { const T s = T(1) / (T(1) + exp(-x)); return s * (T(1) - s) * (T(2) + x * (T(1) - T(2) * s)); }
+    case 2: { const T t = tanh(x); return T(-2) * t * (T(1) - t * t); }
+    case 3: { const T s = T(1) / (T(1) + exp(-x)); return s * (T(1) - s) * (T(1) - T(2) * s); }
+    default: return T(0);
+  }
+}
+
+// Second order: t = cotangent of grad_x.  d_go over the output elements, d_x over the input elements.
+template <typename T>
+__global__ void gate_dbwd_go_kernel(const T* __restrict__ x, const T* __restrict__ t_, T* __restrict__ d_go, long long batch, int u,
+                                    const __grid_constant__ GateTable t) {
+  const long long total = batch * t.n_out * u;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % u);
+    const int so = (int)((i / u) % t.n_out);
+    const long long b = i / ((long long)u * t.n_out);
+    const T* row = x + (size_t)b * t.n_in * u;
+    const T* trow = t_ + (size_t)b * t.n_in * u;
+    if (so < t.n_scalar) {
+      d_go[i] = trow[(size_t)so * u + c] * T(t.cst[so]) * act_d<T>(t.act[so], row[(size_t)so * u + c]);
+    } else {
+      const int si = so + t.n_gate, g = t.gate_of[si];
+      const T xg = row[(size_t)g * u + c];
+      // grad_x[gate] = c a'(x_g) sum_m go_m x_m  and  grad_x[gated m] = go_m c a(x_g)
+      d_go[i] = T(t.cst[g]) * (trow[(size_t)g * u + c] * act_d<T>(t.act[g], xg) * row[(size_t)si * u + c] +
+                               trow[(size_t)si * u + c] * act_f<T>(t.act[g], xg));
+    }
+  }
+}
+
+template <typename T>
+__global__ void gate_dbwd_x_kernel(const T* __restrict__ x, const T* __restrict__ go, const T* __restrict__ t_, T* __restrict__ d_x,
+                                   long long batch, int u, const __grid_constant__ GateTable t) {
+  const long long total = batch * t.n_in * u;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % u);
+    const int si = (int)((i / u) % t.n_in);
+    const long long b = i / ((long long)u * t.n_in);
+    const T* row = x + (size_t)b * t.n_in * u;
+    const T* trow = t_ + (size_t)b * t.n_in * u;
+    const T* grow = go + (size_t)b * t.n_out * u;
+    if (si < t.n_scalar) {
+      d_x[i] = trow[(size_t)si * u + c] * grow[(size_t)si * u + c] * T(t.cst[si]) * act_dd<T>(t.act[si], row[(size_t)si * u + c]);
+    } else if (si < t.n_scalar + t.n_gate) {
+      const T xg = row[(size_t)si * u + c];
+      T dot = T(0), tdot = T(0);
+      for (int m = 0; m < t.n_gated[si]; ++m) {
+        const int sg = t.first_gated[si] + m;
+        const T gm = grow[(size_t)(sg - t.n_gate) * u + c];
+        dot += gm * row[(size_t)sg * u + c];
+        tdot += gm * trow[(size_t)sg * u + c];
+      }
+      d_x[i] = T(t.cst[si]) * (trow[(size_t)si * u + c] * act_dd<T>(t.act[si], xg) * dot + act_d<T>(t.act[si], xg) * tdot);
+    } else {
+      const int g = t.gate_of[si];
+      d_x[i] = trow[(size_t)g * u + c] * T(t.cst[g]) * act_d<T>(t.act[g], row[(size_t)g * u + c]) * grow[(size_t)(si - t.n_gate) * u + c];
+    }
+  }
+}
+
 int build(const fasteq_gate_problem* p, GateTable* t) {
   if (!p || p->n_scalar < 0 || p->n_gate < 0 || p->u < 1 || p->batch < 0) return FASTEQ_INVALID;
   if ((p->n_scalar + p->n_gate) > 0 && (!p->act || !p->cst)) return FASTEQ_INVALID;
@@ -133,6 +195,26 @@ extern "C" int fasteq_gate_backward(const fasteq_gate_problem* p, const void* x,
   const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
   if (p->dtype == FASTEQ_F32) gate_bwd_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)x, (const float*)grad_out, (float*)grad_x, p->batch, p->u, t);
   else gate_bwd_kernel<double><<<blocks, 256, 0, (cudaStream_t)stream>>>((const double*)x, (const double*)grad_out, (double*)grad_x, p->batch, p->u, t);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
+}
+
+extern "C" int fasteq_gate_double_backward(const fasteq_gate_problem* p, const void* x, const void* grad_out, const void* ggx,
+                                           void* d_grad_out, void* d_x, fasteq_stream_t stream) {
+  GateTable t; int rc = build(p, &t);
+  if (rc != FASTEQ_OK) return rc;
+  if (p->batch == 0) return FASTEQ_OK;
+  if (!x || !grad_out || !ggx || !d_grad_out || !d_x) return FASTEQ_INVALID;
+  auto blocks_for = [](long long total) { return (unsigned)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32); };
+  const long long n_out = p->batch * t.n_out * p->u, n_in = p->batch * t.n_in * p->u;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (p->dtype == FASTEQ_F32) {
+    gate_dbwd_go_kernel<float><<<blocks_for(n_out), 256, 0, s>>>((const float*)x, (const float*)ggx, (float*)d_grad_out, p->batch, p->u, t);
+    gate_dbwd_x_kernel<float><<<blocks_for(n_in), 256, 0, s>>>((const float*)x, (const float*)grad_out, (const float*)ggx, (float*)d_x, p->batch, p->u, t);
+  } else {
+    gate_dbwd_go_kernel<double><<<blocks_for(n_out), 256, 0, s>>>((const double*)x, (const double*)ggx, (double*)d_grad_out, p->batch, p->u, t);
+    gate_dbwd_x_kernel<double><<<blocks_for(n_in), 256, 0, s>>>((const double*)x, (const double*)grad_out, (const double*)ggx, (double*)d_x, p->batch, p->u, t);
+  }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }

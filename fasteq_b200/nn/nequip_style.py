@@ -76,27 +76,29 @@ class NequIPStyleModel(torch.nn.Module):
         self.layers = torch.nn.ModuleList(layers)
         self.readout = torch.nn.Parameter(torch.randn(channels) / math.sqrt(channels))
 
-    def node_energies(self, pos, species, edge_src, edge_dst, edge_shift, halo=None):
+    def node_energies(self, pos, species, edge_src, edge_dst, edge_shift, halo=None, second_order: bool = False):
+        """``second_order``: keep to operators whose backward is itself differentiable (force-loss training)."""
         pos_ext = pos if halo is None else halo(pos)
-        if self.fuse_geometry and edge_geometry_usable(pos_ext, self.num_basis):
+        if self.fuse_geometry and not second_order and edge_geometry_usable(pos_ext, self.num_basis):
             vec, radial = edge_geometry(pos_ext, edge_src, edge_dst, edge_shift, self.r_max, self.num_basis, self.envelope_p)
         else:
             vec = pos_ext[edge_src] + edge_shift - pos_ext[edge_dst]
             r = vec.norm(dim=-1)
             radial = bessel_basis(r, self.r_max, self.num_basis) * polynomial_cutoff(r, self.r_max, self.envelope_p).unsqueeze(-1)
-        fused = self.fuse_sh and vec.is_cuda
+        fused = self.fuse_sh and vec.is_cuda and not second_order
         edge_sh = None if fused else self.sh(vec)
         h = self.embedding[species]
         for layer in self.layers:
             h = layer(h, edge_sh, radial, edge_dst, edge_src, halo, vec if fused else None)
         return h[:, : self.channels] @ self.readout
 
-    def forward(self, pos, species, edge_src, edge_dst, edge_shift, forces: bool = True, halo=None):
+    def forward(self, pos, species, edge_src, edge_dst, edge_shift, forces: bool = True, halo=None, create_graph: bool = False):
+        """``create_graph``: keep the forces differentiable, for a force loss."""
         if forces:
             pos = pos.detach().requires_grad_(True)
-        e_node = self.node_energies(pos, species, edge_src, edge_dst, edge_shift, halo)
+        e_node = self.node_energies(pos, species, edge_src, edge_dst, edge_shift, halo, second_order=create_graph)
         out = {"energy": e_node.sum().reshape(1)}
         if forces:
-            (g,) = torch.autograd.grad(e_node.sum(), pos)
+            (g,) = torch.autograd.grad(e_node.sum(), pos, create_graph=create_graph)
             out["forces"] = -g
         return out

@@ -40,6 +40,7 @@ def _lib():
     if not _ready:
         lib.fasteq_gate_forward.argtypes = [C.POINTER(_Problem), C.c_void_p, C.c_void_p, C.c_void_p]
         lib.fasteq_gate_backward.argtypes = [C.POINTER(_Problem), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        lib.fasteq_gate_double_backward.argtypes = [C.POINTER(_Problem)] + [C.c_void_p] * 6
         _ready = True
     return lib
 
@@ -81,15 +82,21 @@ class _Gate(torch.autograd.Function):
         with torch.cuda.device(x.device):
             _cabi.check(lib.fasteq_gate_forward(C.byref(prob), xc.data_ptr(), out.data_ptr(), torch.cuda.current_stream(x.device).cuda_stream),
                         lib, "fasteq_gate_forward")
-        ctx.save_for_backward(xc)
+        ctx.save_for_backward(x)       # the input itself, so that a second backward reaches it
         ctx.spec = spec
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        (xc,) = ctx.saved_tensors
-        spec = ctx.spec
-        go = grad_out.contiguous()
+        (x,) = ctx.saved_tensors
+        return _GateBackward.apply(grad_out.contiguous(), x.contiguous(), ctx.spec), None
+
+
+class _GateBackward(torch.autograd.Function):
+    """Input gradient as a differentiable function (second-order kernels ``fasteq_gate_double_backward``)."""
+
+    @staticmethod
+    def forward(ctx, go, xc, spec):
         gx = torch.empty_like(xc)
         B = xc.numel() // (spec.n_in * spec.u)
         lib = _lib()
@@ -97,7 +104,25 @@ class _Gate(torch.autograd.Function):
         with torch.cuda.device(xc.device):
             _cabi.check(lib.fasteq_gate_backward(C.byref(prob), xc.data_ptr(), go.data_ptr(), gx.data_ptr(),
                                                  torch.cuda.current_stream(xc.device).cuda_stream), lib, "fasteq_gate_backward")
-        return gx, None
+        ctx.save_for_backward(go, xc)
+        ctx.spec = spec
+        return gx
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, ggx):
+        go, xc = ctx.saved_tensors
+        spec = ctx.spec
+        t = ggx.contiguous()
+        d_go, d_x = torch.empty_like(go), torch.empty_like(xc)
+        B = xc.numel() // (spec.n_in * spec.u)
+        lib = _lib()
+        prob = spec.problem(B, xc.dtype)
+        with torch.cuda.device(xc.device):
+            _cabi.check(lib.fasteq_gate_double_backward(C.byref(prob), xc.data_ptr(), go.data_ptr(), t.data_ptr(), d_go.data_ptr(),
+                                                        d_x.data_ptr(), torch.cuda.current_stream(xc.device).cuda_stream),
+                        lib, "fasteq_gate_double_backward")
+        return d_go, d_x, None
 
 
 def gate(x: torch.Tensor, spec: GateSpec) -> torch.Tensor:

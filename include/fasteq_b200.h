@@ -284,6 +284,10 @@ typedef struct fasteq_gate_problem {
 int fasteq_gate_forward(const fasteq_gate_problem* p /* host */, const void* x, void* out, fasteq_stream_t stream);
 int fasteq_gate_backward(const fasteq_gate_problem* p /* host */, const void* x, const void* grad_out, void* grad_x,
                          fasteq_stream_t stream);
+/* Second order: with ggx [batch, n_in, u] the cotangent of grad_x, the gradients of <ggx, grad_x> with respect to
+ * grad_out and x (force-loss training through gated networks). */
+int fasteq_gate_double_backward(const fasteq_gate_problem* p /* host */, const void* x, const void* grad_out, const void* ggx,
+                                void* d_grad_out, void* d_x, fasteq_stream_t stream);
 
 /* Dense layer of the radial MLP: C[M, N] = A[M, K] @ Bt[N, K]^T, FP32 data, 3xTF32 arithmetic on the
  * tensor cores (Bt is a torch.nn.Linear weight, [out_features, in_features]).  K and N multiples of 4,

@@ -55,3 +55,26 @@ def test_nequip_style_energy_and_forces(dtype, tol):
     assert abs(float(out["energy"]) - float(e_ref.sum())) <= tol * max(abs(float(e_ref.sum())), float(e_ref.abs().max()))
     f = out["forces"].cpu().double()
     assert (f - f_ref).abs().max() <= tol * f_ref.abs().max()
+
+
+def test_gate_second_order_matches_torch_autograd():
+    """d/d(grad_out) and d/d(x) of <r, grad_x> against torch autograd on the dense float64 restatement."""
+    from fasteq_b200.ops.gate import GateSpec, gate
+    from oracle.mace_style_ref import gate_ref
+    u = 8
+    spec = GateSpec(u, ["silu", "tanh", "sigmoid"], ["silu", "tanh"], [1, 2])
+    g = torch.Generator().manual_seed(4)
+    B = 53
+    x = torch.randn(B, spec.n_in * u, generator=g, dtype=torch.float64)
+    go = torch.randn(B, spec.n_out * u, generator=g, dtype=torch.float64)
+    r = torch.randn(B, spec.n_in * u, generator=g, dtype=torch.float64)
+
+    def second(fn, dev):
+        xt, gt = x.to(dev).requires_grad_(True), go.to(dev).requires_grad_(True)
+        (gx,) = torch.autograd.grad(fn(xt), xt, gt, create_graph=True)
+        return [t.detach().cpu() for t in torch.autograd.grad((gx * r.to(dev)).sum(), (gt, xt))]
+
+    ref = second(lambda t: gate_ref(t, spec), "cpu")
+    got = second(lambda t: gate(t, spec), "cuda")
+    for a, b in zip(got, ref):
+        assert float((a - b).abs().max()) <= 1e-12 * max(1.0, float(b.abs().max()))
