@@ -11,7 +11,10 @@
 // 64 x 64 layers run as 3xTF32 tensor-core products (same split as gemm_tf32x3.cu) chained through
 // shared memory and TMEM.
 //
-// One persistent CTA per SM walks tiles of 128 edges:
+// One persistent CTA per SM walks tiles of 128 edges, two at a time ("slots"): while the tensor core works on one
+// slot's layer the workers compute the other slot's activation, so neither the MMA round trip nor the
+// activation arithmetic sits idle; both slots share the one operand region (it is only busy during an MMA) and
+// have their own TMEM accumulator:
 //   warp 0    : loads the pre-split hidden weights once (TMA, SWIZZLE_128B), they stay resident
 //   warp 1    : issues the tcgen05.mma of a layer when the eight worker warps have written its operand
 //   warps 2-9 : workers; a thread owns half a row of the tile (TMEM lane = row, 32 of the 64 columns):
@@ -98,10 +101,10 @@ radial_chain_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   float* w1s = reinterpret_cast<float*>(slab_base + N_WORKERS * 2 * SLAB_BYTES);   // [H][NB], zero padded
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(w1s) + H * MAX_NB * 4);
   uint64_t* w_full = bars;            // 1
-  uint64_t* a_ready = bars + 1;       // the eight worker warps have written the operand
-  uint64_t* z_full = bars + 2;        // the accumulator is complete
-  uint64_t* slab_full = bars + 3;     // [8 warps][2] backward: a TMA load has landed in the slab
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 + 2 * N_WORKERS);
+  uint64_t* a_ready = bars + 1;       // [2 slots] the eight worker warps have written the slot's operand
+  uint64_t* z_full = bars + 3;        // [2 slots] the slot's accumulator is complete
+  uint64_t* slab_full = bars + 5;     // [8 warps][2] backward: a TMA load has landed in the slab
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5 + 2 * N_WORKERS);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long n_tiles = (a.M + BM - 1) / BM;
@@ -113,12 +116,11 @@ radial_chain_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   }
   if (threadIdx.x == 0) {
     mbar_init(w_full, 1);
-    mbar_init(a_ready, N_WORKERS);
-    mbar_init(z_full, 1);
+    for (int t = 0; t < 2; ++t) { mbar_init(&a_ready[t], N_WORKERS); mbar_init(&z_full[t], 1); }
     for (int i = 0; i < 2 * N_WORKERS; ++i) mbar_init(&slab_full[i], 1);
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, H);
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * H);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -137,25 +139,35 @@ radial_chain_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       const uint32_t idesc = idesc_tf32_m128(H);
       mbar_wait(w_full, 0u, status);
       tc_fence_after();
-      uint32_t cnt = 0;
-      for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      uint32_t cnt[2] = {0u, 0u};
+      // two tiles ("slots") are in flight per CTA; the workers hand over operands in the fixed order
+      // (slot 0, step s), (slot 1, step s), (slot 0, step s + 1), ... and both slots share the one operand region
+      for (long long pair = 0;; ++pair) {
+        const long long t0 = blockIdx.x + 2 * pair * gridDim.x;
+        if (t0 >= n_tiles) break;
+        const bool has1 = t0 + gridDim.x < n_tiles;
         for (int s = 0; s < n_tc; ++s) {
-          mbar_wait(a_ready, cnt & 1u, status);
-          ++cnt;
-          tc_fence_after();
 #pragma unroll
-          for (int kb = 0; kb < 2; ++kb) {
-            const uint32_t a_hi = smem_u32(a_base + kb * (2 * BM * BK * 4)), a_lo = a_hi + BM * BK * 4;
-            const uint32_t b_hi = smem_u32(w_base + s * W_LAYER_BYTES + kb * (2 * H * BK * 4)), b_lo = b_hi + H * BK * 4;
+          for (int slot = 0; slot < 2; ++slot) {
+            if (slot == 1 && !has1) continue;
+            mbar_wait(&a_ready[slot], cnt[slot] & 1u, status);
+            ++cnt[slot];
+            tc_fence_after();
+            const uint32_t tmem_d = tmem_base + (uint32_t)(slot * H);
 #pragma unroll
-            for (int kk = 0; kk < BK / 8; ++kk) {
-              const uint32_t off = kk * 32;
-              mma_tf32(tmem_base, make_desc(a_lo + off), make_desc(b_hi + off), idesc, (kb | kk) ? 1u : 0u);
-              mma_tf32(tmem_base, make_desc(a_hi + off), make_desc(b_lo + off), idesc, 1u);
-              mma_tf32(tmem_base, make_desc(a_hi + off), make_desc(b_hi + off), idesc, 1u);
+            for (int kb = 0; kb < 2; ++kb) {
+              const uint32_t a_hi = smem_u32(a_base + kb * (2 * BM * BK * 4)), a_lo = a_hi + BM * BK * 4;
+              const uint32_t b_hi = smem_u32(w_base + s * W_LAYER_BYTES + kb * (2 * H * BK * 4)), b_lo = b_hi + H * BK * 4;
+#pragma unroll
+              for (int kk = 0; kk < BK / 8; ++kk) {
+                const uint32_t off = kk * 32;
+                mma_tf32(tmem_d, make_desc(a_lo + off), make_desc(b_hi + off), idesc, (kb | kk) ? 1u : 0u);
+                mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_lo + off), idesc, 1u);
+                mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_hi + off), idesc, 1u);
+              }
             }
+            mma_commit(&z_full[slot]);
           }
-          mma_commit(z_full);
         }
       }
     }
@@ -165,171 +177,184 @@ radial_chain_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     const int half = wk >> 2;                         // which 32 of the 64 columns
     const int quarter = warp & 3;                     // the TMEM lanes this warp may read
     const int trow = quarter * 32 + lane;             // row of the tile = TMEM lane
-    const uint32_t tmem_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 32);
-    unsigned char* slab0 = slab_base + wk * 2 * SLAB_BYTES;
-    unsigned char* slab1 = slab0 + SLAB_BYTES;
-    uint64_t* full0 = &slab_full[2 * wk];
-    uint64_t* full1 = full0 + 1;
-    uint32_t n_z = 0, n_f0 = 0, n_f1 = 0, n_store = 0;
+    const uint32_t tmem_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 32);
+    unsigned char* slab[2] = {slab_base + wk * 2 * SLAB_BYTES, slab_base + wk * 2 * SLAB_BYTES + SLAB_BYTES};
+    uint64_t* full[2] = {&slab_full[2 * wk], &slab_full[2 * wk + 1]};
+    uint32_t n_full[2] = {0u, 0u}, n_z[2] = {0u, 0u}, n_store = 0;
     const int col0 = half * 32;
 
-    if (BWD && lane == 0 && (long long)blockIdx.x < n_tiles) {
-      // first tile: dE/dh_L block into slab 0, the top derivative block into slab 1
-      const long long r0 = (long long)blockIdx.x * BM + quarter * 32;
-      mbar_arrive_expect_tx(full0, SLAB_BYTES);
-      tma_load_3d(slab0, &tmIO0, col0, (int)r0, 0, full0);
-      if (n_tc > 0) {
-        mbar_arrive_expect_tx(full1, SLAB_BYTES);
-        tma_load_3d(slab1, &tmIO1, col0, (int)r0, n_tc - 1, full1);
+    // ---- backward: tiled TMA loads of [32 rows x 32 columns] blocks into this warp's two slabs.  Every block is
+    // requested one phase before it is read: the blocks of a slot's start (dE/dh_L -> slab 0, top derivative ->
+    // slab 1) while the other slot starts, the lower derivative of slot t (-> slab t) after both slots have started.
+    auto request = [&](int which, const CUtensorMap* map, int z, long long row0) {
+      fence_async_smem();                 // earlier generic reads of the slab precede the async write
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive_expect_tx(full[which], SLAB_BYTES);
+        tma_load_3d(slab[which], map, col0, (int)row0, z, full[which]);
       }
-    }
-    // the basis row of a tile is fetched one tile ahead, so its global-load latency is off the chain
-    float b_next[NB];
-    {
-      const long long r = (long long)blockIdx.x * BM + quarter * 32 + lane;
+    };
+    auto landed = [&](int which) { mbar_wait(full[which], n_full[which] & 1u, status); ++n_full[which]; };
+    auto request_start = [&](long long row0) {          // the two blocks a slot's start reads
+      request(0, &tmIO0, 0, row0);
+      if (n_tc > 0) request(1, &tmIO1, n_tc - 1, row0);
+    };
+    // ---- forward: one 32 x 32 block leaves through the slabs (alternating) as a tiled TMA store
+    auto store_block = [&](const float (&val)[32], const CUtensorMap* map, int z, long long row0) {
+      unsigned char* sl = slab[n_store & 1u];
+      if (lane == 0) bulk_wait_read<1>();     // the slab used two stores ago has been read
+      __syncwarp();
 #pragma unroll
-      for (int k = 0; k < NB; ++k) b_next[k] = (r < a.M && k < a.nb) ? __ldg(a.basis + r * a.nb + k) : 0.f;
-    }
-    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-      const long long row0 = tile * BM + quarter * 32;
-      const long long row = row0 + lane;
-      const bool valid = row < a.M;
-      const long long next_row0 = (tile + gridDim.x) * BM + quarter * 32;
-      const bool has_next = tile + gridDim.x < n_tiles;
-      float b[NB];
-#pragma unroll
-      for (int k = 0; k < NB; ++k) b[k] = b_next[k];
-      {
-        const long long r = next_row0 + lane;
-#pragma unroll
-        for (int k = 0; k < NB; ++k) b_next[k] = (has_next && r < a.M && k < a.nb) ? __ldg(a.basis + r * a.nb + k) : 0.f;
+      for (int c = 0; c < 8; ++c) *swz(sl, lane, c) = make_float4(val[4 * c], val[4 * c + 1], val[4 * c + 2], val[4 * c + 3]);
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (row0 < a.M) tma_store_block(map, col0, row0, z, sl);
+        bulk_commit();
       }
-      float v[32];
-      if (!BWD) {
+      ++n_store;
+    };
+    auto load_basis = [&](float (&bb)[NB], long long row0, bool exists) {
+      const long long r = row0 + lane;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float z = 0.f;
+      for (int k = 0; k < NB; ++k) bb[k] = (exists && r < a.M && k < a.nb) ? __ldg(a.basis + r * a.nb + k) : 0.f;
+    };
+    auto first_layer = [&](const float (&bb)[NB], int j, float& h, float& d) {
+      float z = 0.f;
 #pragma unroll
-          for (int k = 0; k < NB; ++k) z = fmaf(w1s[(col0 + j) * NB + k], b[k], z);
-          float d;
-          silu_and_derivative(z, v[j], d);
-        }
-      } else {
-        mbar_wait(full0, n_f0 & 1u, status); ++n_f0;
-        if (n_tc > 0) { mbar_wait(full1, n_f1 & 1u, status); ++n_f1; }
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          float4 gv = *swz(slab0, lane, c);
-          if (n_tc > 0) {
-            const float4 dv = *swz(slab1, lane, c);
-            gv.x *= dv.x; gv.y *= dv.y; gv.z *= dv.z; gv.w *= dv.w;
-          }
-          v[4 * c] = gv.x; v[4 * c + 1] = gv.y; v[4 * c + 2] = gv.z; v[4 * c + 3] = gv.w;
-        }
-        // both slabs are free again: fetch the next derivative of this tile, or the next tile's blocks
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (n_tc > 1) {
-            mbar_arrive_expect_tx(full0, SLAB_BYTES);
-            tma_load_3d(slab0, &tmIO1, col0, (int)row0, n_tc - 2, full0);
-          } else if (has_next) {
-            mbar_arrive_expect_tx(full0, SLAB_BYTES);
-            tma_load_3d(slab0, &tmIO0, col0, (int)next_row0, 0, full0);
-          }
-          if (has_next && n_tc > 0) {
-            mbar_arrive_expect_tx(full1, SLAB_BYTES);
-            tma_load_3d(slab1, &tmIO1, col0, (int)next_row0, n_tc - 1, full1);
-          }
-        }
-      }
-      for (int s = 0; s < n_tc; ++s) {
-        write_operand(a_base, half, trow, v);
-        fence_async_smem();              // generic-proxy writes -> visible to the tensor core's async proxy
-        tc_fence_before();               // this thread's earlier accumulator reads precede the next MMA
-        __syncwarp();
-        if (lane == 0) mbar_arrive(a_ready);
-        mbar_wait(z_full, n_z & 1u, status);
-        ++n_z;
-        tc_fence_after();
-        uint32_t r[32];
-        tmem_ld_32(tmem_acc, r);
+      for (int k = 0; k < NB; ++k) z = fmaf(w1s[(col0 + j) * NB + k], bb[k], z);
+      silu_and_derivative(z, h, d);
+    };
+    auto hand_over = [&](int slot, const float (&val)[32]) {     // operand of the slot's next layer -> MMA warp
+      write_operand(a_base, half, trow, val);
+      fence_async_smem();              // generic-proxy writes -> visible to the tensor core's async proxy
+      tc_fence_before();               // this thread's earlier accumulator reads precede the next MMA
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&a_ready[slot]);
+    };
+    auto accumulator = [&](int slot, uint32_t (&r)[32]) {        // waits for the slot's MMA, then reads its 32 columns
+      mbar_wait(&z_full[slot], n_z[slot] & 1u, status);
+      ++n_z[slot];
+      tc_fence_after();
+      tmem_ld_32(tmem_lane + (uint32_t)(slot * H), r);
+    };
+
+    const long long stride = (long long)gridDim.x * BM;
+    long long row0_of[2];
+    float b[2][NB], v[32];
+    if (BWD && (long long)blockIdx.x < n_tiles) request_start((long long)blockIdx.x * BM + quarter * 32);
+    for (long long pair = 0;; ++pair) {
+      const long long t0 = blockIdx.x + 2 * pair * gridDim.x;
+      if (t0 >= n_tiles) break;
+      const bool has1 = t0 + gridDim.x < n_tiles;
+      const bool has_next = t0 + 2 * gridDim.x < n_tiles;
+      row0_of[0] = t0 * BM + quarter * 32;
+      row0_of[1] = row0_of[0] + stride;
+      load_basis(b[0], row0_of[0], true);
+      load_basis(b[1], row0_of[1], has1);
+
+      // start of a slot: the operand of the first tensor-core layer (or, without one, the final vector)
+      auto start = [&](int slot) {
         if (!BWD) {
-          unsigned char* sl = (n_store & 1u) ? slab1 : slab0;
-          if (lane == 0) bulk_wait_read<1>();     // the slab used two stores ago has been read
-          __syncwarp();
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            float d[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) silu_and_derivative(__uint_as_float(r[4 * c + e]), v[4 * c + e], d[e]);
-            *swz(sl, lane, c) = make_float4(d[0], d[1], d[2], d[3]);
-          }
-          fence_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            if (row0 < a.M) tma_store_block(&tmIO1, col0, row0, s, sl);
-            bulk_commit();
-          }
-          ++n_store;
+          for (int j = 0; j < 32; ++j) { float d; first_layer(b[slot], j, v[j], d); }
         } else {
-          const bool more = s + 1 < n_tc;     // multiply by the derivative of the layer below
-          if (more) { mbar_wait(full0, n_f0 & 1u, status); ++n_f0; }
+          landed(0);
+          if (n_tc > 0) landed(1);
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
-            float4 dv = make_float4(1.f, 1.f, 1.f, 1.f);
-            if (more) dv = *swz(slab0, lane, c);
-            v[4 * c] = __uint_as_float(r[4 * c]) * dv.x; v[4 * c + 1] = __uint_as_float(r[4 * c + 1]) * dv.y;
-            v[4 * c + 2] = __uint_as_float(r[4 * c + 2]) * dv.z; v[4 * c + 3] = __uint_as_float(r[4 * c + 3]) * dv.w;
+            float4 gv = *swz(slab[0], lane, c);
+            if (n_tc > 0) {
+              const float4 dv = *swz(slab[1], lane, c);
+              gv.x *= dv.x; gv.y *= dv.y; gv.z *= dv.z; gv.w *= dv.w;
+            }
+            v[4 * c] = gv.x; v[4 * c + 1] = gv.y; v[4 * c + 2] = gv.z; v[4 * c + 3] = gv.w;
           }
-          if (more) {
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              if (s + 2 < n_tc) {
-                mbar_arrive_expect_tx(full0, SLAB_BYTES);
-                tma_load_3d(slab0, &tmIO1, col0, (int)row0, n_tc - 3 - s, full0);
-              } else if (has_next) {
-                mbar_arrive_expect_tx(full0, SLAB_BYTES);
-                tma_load_3d(slab0, &tmIO0, col0, (int)next_row0, 0, full0);
-              }
+          // both slabs are free: what is read next?
+          if (slot == 0 && has1) request_start(row0_of[1]);
+          else {
+            // both slots have started (or there is only one): the lower derivatives, else the next pair's start
+            if (n_tc > 1) {
+              request(0, &tmIO1, n_tc - 2, row0_of[0]);
+              if (has1) request(1, &tmIO1, n_tc - 2, row0_of[1]);
+            } else if (has_next) {
+              request_start(row0_of[0] + 2 * stride);
             }
           }
         }
+      };
+      // after tensor-core layer s of a slot: the operand of layer s + 1, or the final vector
+      auto after_layer = [&](int slot, int s, const uint32_t (&r)[32]) {
+        if (!BWD) {
+          float d[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) silu_and_derivative(__uint_as_float(r[j]), v[j], d[j]);
+          store_block(d, &tmIO1, s, row0_of[slot]);
+        } else {
+          const bool more = s + 1 < n_tc;      // multiply by the derivative of the layer below (n_tc <= 2: s == 0)
+          if (more) landed(slot);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float4 dv = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (more) dv = *swz(slab[slot], lane, c);
+            v[4 * c] = __uint_as_float(r[4 * c]) * dv.x; v[4 * c + 1] = __uint_as_float(r[4 * c + 1]) * dv.y;
+            v[4 * c + 2] = __uint_as_float(r[4 * c + 2]) * dv.z; v[4 * c + 3] = __uint_as_float(r[4 * c + 3]) * dv.w;
+          }
+          // slab `slot` is free again: the next pair's start blocks go there (dE/dh_L into slab 0, derivative into slab 1)
+          if (more && has_next) {
+            if (slot == 0) request(0, &tmIO0, 0, row0_of[0] + 2 * stride);
+            else request(1, &tmIO1, n_tc - 1, row0_of[0] + 2 * stride);
+          }
+        }
+      };
+      auto finish = [&](int slot) {
+        if (!BWD) {
+          store_block(v, &tmIO0, 0, row0_of[slot]);
+        } else {
+          float gb[NB];
+#pragma unroll
+          for (int k = 0; k < NB; ++k) gb[k] = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float h, d;
+            first_layer(b[slot], j, h, d);
+            const float gz = v[j] * d;
+#pragma unroll
+            for (int k = 0; k < NB; ++k) gb[k] = fmaf(gz, w1s[(col0 + j) * NB + k], gb[k]);
+          }
+          const long long row = row0_of[slot] + lane;
+          if (row < a.M) {
+            // the two half-row owners of an edge add into a zero-filled row: two addends, order-independent
+#pragma unroll
+            for (int k = 0; k < NB; ++k)
+              if (k < a.nb) red_add(a.grad_basis + row * a.nb + k, gb[k]);
+          }
+        }
+      };
+
+      if (n_tc == 0) {
+        start(0); finish(0);
+        if (has1) { start(1); finish(1); }
+        continue;
       }
-      if (!BWD) {
-        unsigned char* sl = (n_store & 1u) ? slab1 : slab0;
-        if (lane == 0) bulk_wait_read<1>();
-        __syncwarp();
-#pragma unroll
-        for (int c = 0; c < 8; ++c) *swz(sl, lane, c) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (row0 < a.M) tma_store_block(&tmIO0, col0, row0, 0, sl);
-          bulk_commit();
-        }
-        ++n_store;
-      } else {
-        float gb[NB];
-#pragma unroll
-        for (int k = 0; k < NB; ++k) gb[k] = 0.f;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float z = 0.f;
-#pragma unroll
-          for (int k = 0; k < NB; ++k) z = fmaf(w1s[(col0 + j) * NB + k], b[k], z);
-          float h, d;
-          silu_and_derivative(z, h, d);
-          const float gz = v[j] * d;
-#pragma unroll
-          for (int k = 0; k < NB; ++k) gb[k] = fmaf(gz, w1s[(col0 + j) * NB + k], gb[k]);
-        }
-        if (valid) {
-          // the two half-row owners of an edge add into a zero-filled row: two addends, order-independent
-#pragma unroll
-          for (int k = 0; k < NB; ++k)
-            if (k < a.nb) red_add(a.grad_basis + row * a.nb + k, gb[k]);
+      // slot 0's first operand goes to the tensor core; slot 1's is computed while that MMA runs
+      start(0);
+      hand_over(0, v);
+      if (has1) start(1);
+      for (int s = 0; s < n_tc; ++s) {
+        uint32_t r[32];
+        // here: MMA (slot 0, layer s) is in flight, v holds slot 1's operand for layer s
+        accumulator(0, r);                       // the operand region is free again
+        if (has1) hand_over(1, v);               // MMA (slot 1, layer s) starts
+        after_layer(0, s, r);                    // ... and runs while slot 0's activation is computed
+        if (s + 1 == n_tc) finish(0);
+        if (has1) {
+          accumulator(1, r);                     // the operand region is free again
+          if (s + 1 < n_tc) hand_over(0, v);     // MMA (slot 0, layer s + 1) starts
+          after_layer(1, s, r);
+          if (s + 1 == n_tc) finish(1);
+        } else if (s + 1 < n_tc) {
+          hand_over(0, v);
         }
       }
     }
@@ -339,7 +364,7 @@ radial_chain_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, H);
+    tmem_dealloc(tmem_base, 2 * H);
   }
 }
 
