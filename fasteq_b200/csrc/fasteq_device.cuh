@@ -77,7 +77,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
 
 // 1-D bulk copy global -> shared (TMA engine, no tensor map): both addresses
 // 16-byte aligned, size a multiple of 16 bytes; completion is signalled on the
-// mbarrier as transferred bytes.  No multicast.
+// mbarrier as transferred bytes.  The copy targets this CTA only.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"

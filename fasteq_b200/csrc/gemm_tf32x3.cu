@@ -22,7 +22,7 @@
 //   warps 6..9   : read a finished accumulator with tcgen05.ld and store the tile through swizzled
 //                  staging slabs and TMA stores
 // Every mbarrier wait is bounded (about two seconds), after which a status word is set and the
-// waiter falls through; TMEM is always released before the CTA ends.  No multicast, no clusters.
+// waiter falls through; TMEM is always released before the CTA ends.  Single-CTA copies only, no clusters.
 #include <cstdio>
 #include <cstdint>
 #include <cuda.h>
