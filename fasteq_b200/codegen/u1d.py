@@ -841,11 +841,11 @@ extern "C" int fasteq_u1d_backward(const fasteq_u1d_graph* gh, const void* go, c
   Graph g; int grid = 1;
   int rc = fill_graph(gh, &g, &grid, {tun.min_blocks});
   if (rc != FASTEQ_OK) return rc;
-  if ((NEED_GW && !gw) || (NEED_GX && !gx) || (NEED_GY && !gy)) return FASTEQ_INVALID;
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t e = cudaSuccess;
   {' '.join(zero)}
-  if (gh->n_edges == 0) return FASTEQ_OK;
+  if (gh->n_edges == 0) return FASTEQ_OK;          // per-edge buffers are empty (and may be null); the rest is zeroed
+  if ((NEED_GW && !gw) || (NEED_GX && !gx) || (NEED_GY && !gy)) return FASTEQ_INVALID;
   if (!go || !w || !x || !y) return FASTEQ_INVALID;
   g.bulk_ok = aligned16(w) && aligned16(x) && aligned16(y) && aligned16(go) && ((U * sizeof(T)) % 16 == 0) &&
               ((CT * sizeof(T)) % 16 == 0);

@@ -61,7 +61,7 @@ class _SH(torch.autograd.Function):
         (x,) = ctx.saved_tensors
         ls, normalize, normalization, shape = ctx.cfg
         flat = x.reshape(-1, 3)
-        g = grad_out.reshape(flat.shape[0], -1).contiguous()
+        g = grad_out.reshape(flat.shape[0], grad_out.shape[-1]).contiguous()
         return _SHBackward.apply(g, flat, ls, normalize, normalization).reshape(shape), None, None, None
 
 

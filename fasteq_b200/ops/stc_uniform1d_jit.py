@@ -123,7 +123,7 @@ class FastSymmetricTensorContractionUniform1dFunction(torch.autograd.Function):
                                                    torch.cuda.current_stream(x1.device).cuda_stream), mod.lib, "fasteq_stc_forward")
         ctx.save_for_backward(x1, x0, i32)      # the inputs themselves, so that a second backward reaches them
         ctx.spec = spec
-        return out.view(B, -1)
+        return out.view(B, spec.out_segs * spec.u)
 
     @staticmethod
     def backward(ctx, grad_out):

@@ -154,17 +154,20 @@ class _EngineExchange(torch.autograd.Function):
         nlocal, ntotal = int(engine.nlocal), int(engine.ntotal)
         if x_owned.shape[0] != nlocal:
             raise ValueError(f"engine exchange: {x_owned.shape[0]} owned rows given, the engine owns {nlocal}")
-        flat = x_owned.reshape(nlocal, -1)
+        width = 1
+        for d in x_owned.shape[1:]:
+            width *= int(d)
+        flat = x_owned.reshape(nlocal, width)          # explicit width: a rank may own no atoms
         src = torch.zeros((ntotal, flat.shape[1]), dtype=flat.dtype, device=flat.device)
         src[:nlocal] = flat
         out = torch.empty_like(src)
         engine.forward_exchange(src, out, out.shape[1])
-        ctx.engine, ctx.nlocal, ctx.tail = engine, nlocal, x_owned.shape[1:]
+        ctx.engine, ctx.nlocal, ctx.tail, ctx.width = engine, nlocal, x_owned.shape[1:], width
         return out.reshape((ntotal,) + tuple(x_owned.shape[1:]))
 
     @staticmethod
     def backward(ctx, grad_ext):
-        g = grad_ext.reshape(grad_ext.shape[0], -1).contiguous()
+        g = grad_ext.reshape(grad_ext.shape[0], ctx.width).contiguous()
         out = torch.empty_like(g)
         ctx.engine.reverse_exchange(g, out, out.shape[1])
         return out[: ctx.nlocal].reshape((ctx.nlocal,) + tuple(ctx.tail)), None

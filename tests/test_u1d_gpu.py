@@ -146,14 +146,19 @@ def test_empty_graph_and_isolated_receivers():
     N = 7
     x = torch.randn(N, d.x_seg_num * 32, device="cuda")
     for E in (0, 1):
-        w = torch.randn(E, d.w_seg_num * 32, device="cuda")
-        y = torch.randn(E, d.y_seg_num, device="cuda")
+        w = torch.randn(E, d.w_seg_num * 32, device="cuda", requires_grad=True)
+        y = torch.randn(E, d.y_seg_num, device="cuda", requires_grad=True)
         src = torch.zeros(E, dtype=torch.int32, device="cuda")
         dst = torch.full((E,), 4, dtype=torch.int32, device="cuda")
-        out = fast_uniform1d_jit(w, x, y, {1: src}, {0: dst}, meta)
+        xg = x.clone().requires_grad_(True)
+        out = fast_uniform1d_jit(w, xg, y, {1: src}, {0: dst}, meta)
         assert out.shape == (N, d.out_seg_num * 32)
-        rows = out.abs().sum(dim=1)
+        rows = out.detach().abs().sum(dim=1)
         assert torch.count_nonzero(rows) == (1 if E else 0)
+        # backward of an empty edge list: empty per-edge gradients, a zero sender gradient
+        gw, gx, gy = torch.autograd.grad(out.sum(), (w, xg, y))
+        assert gw.shape == w.shape and gy.shape == y.shape and gx.shape == x.shape
+        assert torch.count_nonzero(gx.abs().sum(dim=1)) == (1 if E else 0)
 
 
 def test_no_device_fault_recorded():
@@ -219,8 +224,8 @@ def test_in_kernel_spherical_harmonics_match_the_two_step_path(in1, lmax, dtype,
     ref = torch.autograd.grad(out_ref, (w, x, vec), r)
     out = tp(x, None, w, dst, src, edge_vec=vec)
     got = torch.autograd.grad(out, (w, x, vec), r)
-    scale = lambda t: float(t.abs().max())
-    assert float((out - out_ref).abs().max()) <= tol * scale(out_ref)
+    scale = lambda t: float(t.detach().abs().max())
+    assert float((out - out_ref).detach().abs().max()) <= tol * scale(out_ref)
     for a, b in zip(got, ref):
         assert a.shape == b.shape and float((a - b).abs().max()) <= tol * scale(b)
     with pytest.raises(RuntimeError):
