@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from typing import Dict, Optional, Tuple
+from typing import Dict, List, Optional, Set, Tuple
 
 import numpy as np
 import torch
@@ -67,7 +67,8 @@ def get_module(spec: U1DSpec, direction: str, needs=(False, False, False), tunin
 
 class GraphPlan:
     """Receiver-sorted CSR view of a scatter index: sortedness, permutation, segment offsets
-    and per-grid partitions.  Built once per index tensor (one host sync) and cached."""
+    and per-grid partitions.  Built once per index tensor (one host sync) and cached.  Each build step
+    leaves an event behind it; ``ready_on_current_stream`` makes a later user on another stream wait for them."""
 
     def __init__(self, dst: torch.Tensor, n_rows: int, seg_ptr: Optional[torch.Tensor] = None):
         if dst.dim() != 1:
@@ -77,6 +78,8 @@ class GraphPlan:
         self.n_edges = int(dst.numel())
         dev = dst.device
         self._parts: Dict[int, torch.Tensor] = {}
+        self._ready: List[Tuple[int, torch.cuda.Event]] = []
+        self._waited: Set[int] = set()          # streams already ordered behind every event in _ready
         self.device = dev
         if seg_ptr is not None:
             # the caller vouches for a receiver-sorted index and brings its CSR offsets (the GPU
@@ -102,8 +105,28 @@ class GraphPlan:
             self.seg_ptr = torch.empty(self.n_rows + 1, dtype=torch.int32, device=dev)
             _cabi.check(core.fasteq_graph_build_csr(sorted_dst.data_ptr(), self.n_edges, self.n_rows,
                                                     self.seg_ptr.data_ptr(), stream), core, "fasteq_graph_build_csr")
-        self._parts: Dict[int, torch.Tensor] = {}
-        self.device = dev
+        self._mark_built()
+
+    def _mark_built(self) -> None:
+        cur = torch.cuda.current_stream(self.device)
+        if torch.cuda.is_current_stream_capturing():
+            return
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        self._ready = [(sid, e) for sid, e in self._ready if sid != cur.cuda_stream] + [(cur.cuda_stream, ev)]
+        self._waited = set()
+
+    def ready_on_current_stream(self) -> None:
+        """Order the current stream behind the kernels that built this plan on other streams."""
+        if not self._ready or torch.cuda.is_current_stream_capturing():
+            return
+        cur = torch.cuda.current_stream(self.device)
+        if cur.cuda_stream in self._waited:
+            return
+        for sid, ev in self._ready:
+            if sid != cur.cuda_stream:
+                cur.wait_event(ev)
+        self._waited.add(cur.cuda_stream)
 
     def partition(self, n_parts: int) -> torch.Tensor:
         p = self._parts.get(n_parts)
@@ -115,6 +138,7 @@ class GraphPlan:
                 _cabi.check(core.fasteq_graph_partition(self.seg_ptr.data_ptr(), self.n_rows, self.n_edges, n_parts,
                                                         p.data_ptr(), stream), core, "fasteq_graph_partition")
             self._parts[n_parts] = p
+            self._mark_built()
         return p
 
 
@@ -252,6 +276,7 @@ class _Call:
             n_parts = max(1, min(_sm_count(dev) * int(mod.desc.ctas_per_sm), self.n_out_rows))
             g.part_ptr = self.plan.partition(n_parts).data_ptr()
             g.n_parts = n_parts
+            self.plan.ready_on_current_stream()
         return g
 
 

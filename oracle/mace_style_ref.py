@@ -96,7 +96,7 @@ def force_loss_gradients(model, pos, species, edge_src, edge_dst, edge_shift, ta
     _, f = energy_and_forces(model, pos, species, edge_src, edge_dst, edge_shift, params=p, create_graph=True)
     loss = ((f - target_forces.double()) ** 2).sum()
     grads = torch.autograd.grad(loss, [p[n] for n in names])
-    return float(loss), dict(zip(names, grads))
+    return float(loss.detach()), dict(zip(names, grads))
 
 
 def gate_ref(x, spec):
