@@ -426,6 +426,203 @@ gemm_tf32x3_as_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Persistent form of the A-stationary kernel for K <= 64: one CTA per SM walks row blocks round-robin.  The A
+// block is double buffered (the next block lands and is split by two warps of their own while the MMAs of the
+// current one run) and the two TMEM accumulators alternate across block boundaries, so the load / split
+// prologue and the store tail of a block hide behind its neighbours' MMAs.
+//   warp 0: TMA producer (A blocks, weight tiles)   warp 1: tcgen05.mma issue   warps 2-3: hi / lo split of A
+//   warps 4-7: accumulator read-back and TMA stores
+// Shared-memory bandwidth is the busiest resource here (every 128 x 128 x 8 TF32 MMA reads 8 KB of operands, the
+// weight ring and the store staging add as much again per tile).  Writing the accumulator rows straight from
+// registers (32-byte st.global per thread) instead of staging them was measured slower: the row-scattered
+// sectors cost more in the memory system than the staging costs in shared memory.
+constexpr int NT_ASP = 256;
+
+struct AspCfg {
+  static constexpr int KB = 2;
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int A_BUF = KB * 2 * A_BYTES;        // [KB][hi 16 KB | lo 16 KB]
+  static constexpr int B_BYTES = AS_BN * BK * 4;
+  static constexpr int RING = 2;
+  static constexpr int STORE_BYTES = 4 * 2 * 4096;
+  static constexpr int SMEM_BYTES = 2 * A_BUF + RING * 2 * B_BYTES + STORE_BYTES + 1024 + 1024;
+};
+
+__global__ void __launch_bounds__(NT_ASP, 1)
+gemm_tf32x3_asp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBhi,
+                       const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmC, long long M, int N, int K,
+                       int m_blocks, int* status) {
+  using C_ = AspCfg;
+  constexpr int RING = C_::RING;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* a_base = smem;                                   // [2 buffers][KB][hi | lo]
+  unsigned char* b_base = smem + 2 * C_::A_BUF;                   // [RING][hi 16 KB | lo 16 KB]
+  unsigned char* store_base = b_base + RING * 2 * C_::B_BYTES;    // [4 warps][2 slabs][32 rows x 128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(store_base + C_::STORE_BYTES);
+  uint64_t* a_full = bars;              // [2] raw A block landed
+  uint64_t* a_split = bars + 2;         // [2] its hi / lo parts are in place (two split warps)
+  uint64_t* a_empty = bars + 4;         // [2] the MMAs of the block have completed
+  uint64_t* b_full = bars + 6;          // [RING]
+  uint64_t* b_empty = b_full + RING;    // [RING]
+  uint64_t* acc_full = b_empty + RING;  // [2]
+  uint64_t* acc_empty = acc_full + 2;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (N + AS_BN - 1) / AS_BN;
+  const int n_kb = (K + BK - 1) / BK;            // <= KB
+  const int first = (int)blockIdx.x, stride = (int)gridDim.x;
+
+  if (threadIdx.x == 0) {
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&a_full[b], 1); mbar_init(&a_split[b], 2); mbar_init(&a_empty[b], 1);
+      mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4);
+    }
+    for (int s = 0; s < RING; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 256u);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      auto load_a = [&](int j, int blk) {
+        const int buf = j & 1;
+        mbar_wait(&a_empty[buf], (((uint32_t)j >> 1) & 1u) ^ 1u, status);
+        unsigned char* dst = a_base + (size_t)buf * C_::A_BUF;
+        mbar_arrive_expect_tx(&a_full[buf], (uint32_t)(n_kb * C_::A_BYTES));
+        for (int kb = 0; kb < n_kb; ++kb) tma_load_3d(dst + (size_t)kb * 2 * C_::A_BYTES, &tmA, kb * BK, 0, blk * BM, &a_full[buf]);
+      };
+      if (first < m_blocks) load_a(0, first);
+      int it = 0;
+      for (int j = 0, blk = first; blk < m_blocks; ++j, blk += stride) {
+        bool next_pending = blk + stride < m_blocks;
+        int local = 0;
+        for (int nt = 0; nt < n_tiles; ++nt) {
+          for (int kb = 0; kb < n_kb; ++kb, ++it, ++local) {
+            // the next A block is requested once this block's first weight tiles are on their way
+            if (next_pending && local == RING) { load_a(j + 1, blk + stride); next_pending = false; }
+            const int s = it % RING;
+            mbar_wait(&b_empty[s], ((it / RING) & 1u) ^ 1u, status);
+            unsigned char* st = b_base + (size_t)s * 2 * C_::B_BYTES;
+            mbar_arrive_expect_tx(&b_full[s], (uint32_t)(2 * C_::B_BYTES));
+            tma_load_3d(st, &tmBhi, kb * BK, nt * AS_BN, 0, &b_full[s]);
+            tma_load_3d(st + C_::B_BYTES, &tmBlo, kb * BK, nt * AS_BN, 0, &b_full[s]);
+          }
+        }
+        if (next_pending) load_a(j + 1, blk + stride);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = idesc_tf32_m128(AS_BN);
+      int it = 0;
+      uint32_t t = 0;
+      for (int j = 0, blk = first; blk < m_blocks; ++j, blk += stride) {
+        const int abuf = j & 1;
+        mbar_wait(&a_split[abuf], ((uint32_t)j >> 1) & 1u, status);
+        tc_fence_after();
+        const uint32_t a0 = smem_u32(a_base + (size_t)abuf * C_::A_BUF);
+        for (int nt = 0; nt < n_tiles; ++nt, ++t) {
+          const uint32_t buf = t & 1u;
+          mbar_wait(&acc_empty[buf], ((t >> 1) & 1u) ^ 1u, status);
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + buf * AS_BN;
+          for (int kb = 0; kb < n_kb; ++kb, ++it) {
+            const int s = it % RING;
+            mbar_wait(&b_full[s], (it / RING) & 1u, status);
+            tc_fence_after();
+            const uint32_t a_hi = a0 + (uint32_t)(kb * 2 * C_::A_BYTES), a_lo = a_hi + C_::A_BYTES;
+            const uint32_t b_hi = smem_u32(b_base + (size_t)s * 2 * C_::B_BYTES), b_lo = b_hi + C_::B_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < BK / 8; ++kk) {
+              const uint32_t off = kk * 32;
+              mma_tf32(tmem_d, make_desc(a_lo + off), make_desc(b_hi + off), idesc, (kb | kk) ? 1u : 0u);
+              mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_lo + off), idesc, 1u);
+              mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_hi + off), idesc, 1u);
+            }
+            mma_commit(&b_empty[s]);
+          }
+          mma_commit(&acc_full[buf]);
+        }
+        mma_commit(&a_empty[abuf]);
+      }
+    }
+  } else if (warp < 4) {
+    const int tid = threadIdx.x - 64;          // 0 .. 63
+    for (int j = 0, blk = first; blk < m_blocks; ++j, blk += stride) {
+      const int abuf = j & 1;
+      mbar_wait(&a_full[abuf], ((uint32_t)j >> 1) & 1u, status);
+      for (int kb = 0; kb < n_kb; ++kb) {
+        float4* hi = reinterpret_cast<float4*>(a_base + (size_t)abuf * C_::A_BUF + (size_t)kb * 2 * C_::A_BYTES);
+        float4* lo = hi + C_::A_BYTES / 16;
+#pragma unroll 4
+        for (int i = 0; i < C_::A_BYTES / 16 / 64; ++i) {
+          const float4 v = hi[tid + i * 64];
+          float4 h, l;
+          split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+          hi[tid + i * 64] = h; lo[tid + i * 64] = l;
+        }
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&a_split[abuf]);
+    }
+  } else {
+    const int quarter = warp & 3;
+    unsigned char* slab = store_base + (size_t)quarter * 2 * 4096;
+    int chunk_no = 0;
+    uint32_t t = 0;
+    for (int j = 0, blk = first; blk < m_blocks; ++j, blk += stride) {
+      const long long row0 = (long long)blk * BM + quarter * 32;
+      for (int nt = 0; nt < n_tiles; ++nt, ++t) {
+        const uint32_t buf = t & 1u;
+        mbar_wait(&acc_full[buf], (t >> 1) & 1u, status);
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < AS_BN / 32; ++c, ++chunk_no) {
+          uint32_t r[32];
+          tmem_ld_32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * AS_BN + (uint32_t)(c * 32), r);
+          unsigned char* sl = slab + (size_t)(chunk_no & 1) * 4096;
+          if (lane == 0) bulk_wait_read<1>();     // the slab used two chunks ago has been read by its store
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            // SWIZZLE_128B: 16-byte chunk q of row `lane` sits at chunk position q ^ (lane & 7)
+            *reinterpret_cast<float4*>(sl + lane * 128 + ((q ^ (lane & 7)) << 4)) =
+                make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int col0 = nt * AS_BN + c * 32;
+            if (col0 < N && row0 < M) {
+              asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                           ::"l"(&tmC), "r"(col0), "r"((int)row0), "r"(0), "r"(smem_u32(sl)) : "memory");
+            }
+            bulk_commit();
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      }
+    }
+    if (lane == 0) bulk_wait_read<0>();   // the staging slabs must outlive their stores
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256u);
+  }
+}
+
 __global__ void split_weights_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, long long n) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const float v = w[i];
@@ -539,6 +736,22 @@ static int launch_as_kb(const CUtensorMap& ma, const CUtensorMap& mbh, const CUt
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }
 
+static int launch_as_persistent(const CUtensorMap& ma, const CUtensorMap& mbh, const CUtensorMap& mbl, const CUtensorMap& mc, long long M,
+                                int N, int K, cudaStream_t s) {
+  int* st = nullptr;
+  cudaError_t e = cudaGetSymbolAddress((void**)&st, g_tc_status);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaFuncSetAttribute(gemm_tf32x3_asp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AspCfg::SMEM_BYTES);
+  if (e != cudaSuccess) return cuda_fail(e);
+  const long long m_blocks = (M + BM - 1) / BM;
+  const int sms = sm_count();
+  if (sms < 1) return FASTEQ_CUDA_ERROR;
+  const unsigned grid = (unsigned)(m_blocks < sms ? m_blocks : sms);     // one persistent CTA per SM
+  gemm_tf32x3_asp_kernel<<<grid, NT_ASP, AspCfg::SMEM_BYTES, s>>>(ma, mbh, mbl, mc, M, N, K, (int)m_blocks, st);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
+}
+
 // plain C[M, N] = A[M, K] @ Bt[N, K]^T with K <= 128 and several N tiles
 // `split`: hi / lo parts of Bt (2 * N * K floats)
 int launch_a_stationary(const float* A, long long M, int K, const float* split, int N, float* C, cudaStream_t s) {
@@ -550,7 +763,7 @@ int launch_a_stationary(const float* A, long long M, int K, const float* split, 
   if (rc == FASTEQ_OK) rc = make_map(&mbl, split + nw, (uint64_t)K, (uint64_t)N, 1, (uint64_t)K, (uint64_t)N * K, BK, AS_BN, 1);
   if (rc == FASTEQ_OK) {
     const int kb = (K + BK - 1) / BK;
-    rc = kb <= 2 ? launch_as_kb<2>(ma, mbh, mbl, mc, M, N, K, s) : launch_as_kb<4>(ma, mbh, mbl, mc, M, N, K, s);
+    rc = kb <= 2 ? launch_as_persistent(ma, mbh, mbl, mc, M, N, K, s) : launch_as_kb<4>(ma, mbh, mbl, mc, M, N, K, s);
   }
   return rc;
 }

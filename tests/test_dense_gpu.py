@@ -14,6 +14,8 @@ def _rel(a, b):
 @pytest.mark.parametrize("M,N,K", [
     (1, 64, 8), (77, 64, 64), (128, 8, 64), (1000, 64, 1664), (513, 1664, 64), (300, 512, 64), (257, 128, 128),
     (148 * 128 * 3 + 77, 64, 64), (148 * 128 * 2 + 5, 64, 8), (40000, 128, 128), (20000, 12, 20),
+    # wide shallow layers: every persistent CTA of the A-stationary kernel walks several row blocks
+    (148 * 128 * 3 + 77, 512, 64), (148 * 128 * 2 + 5, 256, 32), (5000, 260, 40), (148 * 128 + 1, 1280, 64),
 ])
 def test_dense_forward_matches_float64(M, N, K):
     from fasteq_b200.ops.dense import dense, tensorcore_device_status
