@@ -427,26 +427,29 @@ gemm_tf32x3_as_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 }
 
 // ------------------------------------------------------------------------------------------------
-// Persistent form of the A-stationary kernel for K <= 64: one CTA per SM walks row blocks round-robin.  The A
-// block is double buffered (the next block lands and is split by two warps of their own while the MMAs of the
-// current one run) and the two TMEM accumulators alternate across block boundaries, so the load / split
-// prologue and the store tail of a block hide behind its neighbours' MMAs.
-//   warp 0: TMA producer (A blocks, weight tiles)   warp 1: tcgen05.mma issue   warps 2-3: hi / lo split of A
-//   warps 4-7: accumulator read-back and TMA stores
-// Shared-memory bandwidth is the busiest resource here (every 128 x 128 x 8 TF32 MMA reads 8 KB of operands, the
-// weight ring and the store staging add as much again per tile).  Writing the accumulator rows straight from
-// registers (32-byte st.global per thread) instead of staging them was measured slower: the row-scattered
-// sectors cost more in the memory system than the staging costs in shared memory.
-constexpr int NT_ASP = 256;
+// Persistent form of the A-stationary kernel for K <= 64: one CTA per SM walks row blocks round-robin, and the
+// A block lives in TENSOR MEMORY.  Shared-memory bandwidth is the busiest resource of this shape (every
+// 128 x 128 x 8 TF32 MMA with both operands in shared memory reads 8 KB), so four warps split each raw A block
+// (thread = row = TMEM lane) into hi / lo and write both with tcgen05.st; the MMAs then take A from tensor memory
+// and only the weight tile from shared memory.  A is double buffered (raw tile in shared memory and hi / lo in
+// tensor memory) and the two accumulators alternate across block boundaries, so the load / split prologue and
+// the store tail of a block hide behind its neighbours' MMAs.
+//   warp 0: TMA producer (A blocks, weight tiles)   warp 1: tcgen05.mma issue   warps 2-5: hi / lo split of A
+//   warps 6-9: accumulator read-back and TMA stores
+// Tensor memory (512 columns): accumulators [0, 256); A buffer b at 256 + 128 b: hi [0, 64), lo [64, 128).
+// Writing the accumulator rows straight from registers (32-byte st.global per thread) instead of staging them
+// for TMA stores was measured slower: row-scattered sectors cost more than the staging.
+constexpr int NT_ASP = 320;
 
 struct AspCfg {
   static constexpr int KB = 2;
   static constexpr int A_BYTES = BM * BK * 4;
-  static constexpr int A_BUF = KB * 2 * A_BYTES;        // [KB][hi 16 KB | lo 16 KB]
+  static constexpr int A_BUF = KB * A_BYTES;             // raw FP32 block, [KB][16 KB]
   static constexpr int B_BYTES = AS_BN * BK * 4;
-  static constexpr int RING = 2;
+  static constexpr int RING = 4;
   static constexpr int STORE_BYTES = 4 * 2 * 4096;
   static constexpr int SMEM_BYTES = 2 * A_BUF + RING * 2 * B_BYTES + STORE_BYTES + 1024 + 1024;
+  static constexpr uint32_t TMEM_COLS = 512, TMEM_A0 = 256, TMEM_A_STRIDE = 128, TMEM_A_LO = 64;
 };
 
 __global__ void __launch_bounds__(NT_ASP, 1)
@@ -457,14 +460,15 @@ gemm_tf32x3_asp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   constexpr int RING = C_::RING;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* a_base = smem;                                   // [2 buffers][KB][hi | lo]
+  unsigned char* a_base = smem;                                   // [2 buffers][KB][raw 16 KB]
   unsigned char* b_base = smem + 2 * C_::A_BUF;                   // [RING][hi 16 KB | lo 16 KB]
   unsigned char* store_base = b_base + RING * 2 * C_::B_BYTES;    // [4 warps][2 slabs][32 rows x 128 B]
   uint64_t* bars = reinterpret_cast<uint64_t*>(store_base + C_::STORE_BYTES);
   uint64_t* a_full = bars;              // [2] raw A block landed
-  uint64_t* a_split = bars + 2;         // [2] its hi / lo parts are in place (two split warps)
-  uint64_t* a_empty = bars + 4;         // [2] the MMAs of the block have completed
-  uint64_t* b_full = bars + 6;          // [RING]
+  uint64_t* a_split = bars + 2;         // [2] hi / lo are in tensor memory (four split warps)
+  uint64_t* a_raw_empty = bars + 4;     // [2] the split warps have read the raw block
+  uint64_t* a_tmem_empty = bars + 6;    // [2] the MMAs of the block have completed
+  uint64_t* b_full = bars + 8;          // [RING]
   uint64_t* b_empty = b_full + RING;    // [RING]
   uint64_t* acc_full = b_empty + RING;  // [2]
   uint64_t* acc_empty = acc_full + 2;   // [2]
@@ -477,13 +481,13 @@ gemm_tf32x3_asp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 
   if (threadIdx.x == 0) {
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&a_full[b], 1); mbar_init(&a_split[b], 2); mbar_init(&a_empty[b], 1);
+      mbar_init(&a_full[b], 1); mbar_init(&a_split[b], 4); mbar_init(&a_raw_empty[b], 4); mbar_init(&a_tmem_empty[b], 1);
       mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4);
     }
     for (int s = 0; s < RING; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, 256u);
+  if (warp == 1) tmem_alloc(tmem_slot, C_::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -493,10 +497,10 @@ gemm_tf32x3_asp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     if (lane == 0) {
       auto load_a = [&](int j, int blk) {
         const int buf = j & 1;
-        mbar_wait(&a_empty[buf], (((uint32_t)j >> 1) & 1u) ^ 1u, status);
+        mbar_wait(&a_raw_empty[buf], (((uint32_t)j >> 1) & 1u) ^ 1u, status);
         unsigned char* dst = a_base + (size_t)buf * C_::A_BUF;
         mbar_arrive_expect_tx(&a_full[buf], (uint32_t)(n_kb * C_::A_BYTES));
-        for (int kb = 0; kb < n_kb; ++kb) tma_load_3d(dst + (size_t)kb * 2 * C_::A_BYTES, &tmA, kb * BK, 0, blk * BM, &a_full[buf]);
+        for (int kb = 0; kb < n_kb; ++kb) tma_load_3d(dst + (size_t)kb * C_::A_BYTES, &tmA, kb * BK, 0, blk * BM, &a_full[buf]);
       };
       if (first < m_blocks) load_a(0, first);
       int it = 0;
@@ -506,7 +510,7 @@ gemm_tf32x3_asp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         for (int nt = 0; nt < n_tiles; ++nt) {
           for (int kb = 0; kb < n_kb; ++kb, ++it, ++local) {
             // the next A block is requested once this block's first weight tiles are on their way
-            if (next_pending && local == RING) { load_a(j + 1, blk + stride); next_pending = false; }
+            if (next_pending && local == 2) { load_a(j + 1, blk + stride); next_pending = false; }
             const int s = it % RING;
             mbar_wait(&b_empty[s], ((it / RING) & 1u) ^ 1u, status);
             unsigned char* st = b_base + (size_t)s * 2 * C_::B_BYTES;
@@ -527,7 +531,7 @@ gemm_tf32x3_asp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const int abuf = j & 1;
         mbar_wait(&a_split[abuf], ((uint32_t)j >> 1) & 1u, status);
         tc_fence_after();
-        const uint32_t a0 = smem_u32(a_base + (size_t)abuf * C_::A_BUF);
+        const uint32_t a_hi0 = tmem_base + C_::TMEM_A0 + (uint32_t)abuf * C_::TMEM_A_STRIDE, a_lo0 = a_hi0 + C_::TMEM_A_LO;
         for (int nt = 0; nt < n_tiles; ++nt, ++t) {
           const uint32_t buf = t & 1u;
           mbar_wait(&acc_empty[buf], ((t >> 1) & 1u) ^ 1u, status);
@@ -537,41 +541,50 @@ gemm_tf32x3_asp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             const int s = it % RING;
             mbar_wait(&b_full[s], (it / RING) & 1u, status);
             tc_fence_after();
-            const uint32_t a_hi = a0 + (uint32_t)(kb * 2 * C_::A_BYTES), a_lo = a_hi + C_::A_BYTES;
             const uint32_t b_hi = smem_u32(b_base + (size_t)s * 2 * C_::B_BYTES), b_lo = b_hi + C_::B_BYTES;
 #pragma unroll
             for (int kk = 0; kk < BK / 8; ++kk) {
-              const uint32_t off = kk * 32;
-              mma_tf32(tmem_d, make_desc(a_lo + off), make_desc(b_hi + off), idesc, (kb | kk) ? 1u : 0u);
-              mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_lo + off), idesc, 1u);
-              mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_hi + off), idesc, 1u);
+              const uint32_t off = kk * 32, col = (uint32_t)(kb * BK + kk * 8);
+              mma_tf32_a_tmem(tmem_d, a_lo0 + col, make_desc(b_hi + off), idesc, (kb | kk) ? 1u : 0u);
+              mma_tf32_a_tmem(tmem_d, a_hi0 + col, make_desc(b_lo + off), idesc, 1u);
+              mma_tf32_a_tmem(tmem_d, a_hi0 + col, make_desc(b_hi + off), idesc, 1u);
             }
             mma_commit(&b_empty[s]);
           }
           mma_commit(&acc_full[buf]);
         }
-        mma_commit(&a_empty[abuf]);
+        mma_commit(&a_tmem_empty[abuf]);
       }
     }
-  } else if (warp < 4) {
-    const int tid = threadIdx.x - 64;          // 0 .. 63
+  } else if (warp < 6) {
+    // thread = row of the block = its TMEM lane; 16-byte chunk q of row r sits at chunk position q ^ (r & 7)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
     for (int j = 0, blk = first; blk < m_blocks; ++j, blk += stride) {
       const int abuf = j & 1;
       mbar_wait(&a_full[abuf], ((uint32_t)j >> 1) & 1u, status);
+      mbar_wait(&a_tmem_empty[abuf], (((uint32_t)j >> 1) & 1u) ^ 1u, status);
+      tc_fence_after();
+      const uint32_t t_hi = tmem_base + ((uint32_t)(quarter * 32) << 16) + C_::TMEM_A0 + (uint32_t)abuf * C_::TMEM_A_STRIDE;
       for (int kb = 0; kb < n_kb; ++kb) {
-        float4* hi = reinterpret_cast<float4*>(a_base + (size_t)abuf * C_::A_BUF + (size_t)kb * 2 * C_::A_BYTES);
-        float4* lo = hi + C_::A_BYTES / 16;
-#pragma unroll 4
-        for (int i = 0; i < C_::A_BYTES / 16 / 64; ++i) {
-          const float4 v = hi[tid + i * 64];
+        const unsigned char* tile = a_base + (size_t)abuf * C_::A_BUF + (size_t)kb * C_::A_BYTES;
+        uint32_t hi_bits[32], lo_bits[32];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 v = *reinterpret_cast<const float4*>(tile + row * 128 + ((q ^ (row & 7)) << 4));
           float4 h, l;
           split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
-          hi[tid + i * 64] = h; lo[tid + i * 64] = l;
+          hi_bits[4 * q] = __float_as_uint(h.x); hi_bits[4 * q + 1] = __float_as_uint(h.y);
+          hi_bits[4 * q + 2] = __float_as_uint(h.z); hi_bits[4 * q + 3] = __float_as_uint(h.w);
+          lo_bits[4 * q] = __float_as_uint(l.x); lo_bits[4 * q + 1] = __float_as_uint(l.y);
+          lo_bits[4 * q + 2] = __float_as_uint(l.z); lo_bits[4 * q + 3] = __float_as_uint(l.w);
         }
+        tmem_st_32(t_hi + (uint32_t)(kb * BK), hi_bits);
+        tmem_st_32(t_hi + C_::TMEM_A_LO + (uint32_t)(kb * BK), lo_bits);
       }
-      fence_async_smem();
+      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&a_split[abuf]);
+      if (lane == 0) { mbar_arrive(&a_split[abuf]); mbar_arrive(&a_raw_empty[abuf]); }
     }
   } else {
     const int quarter = warp & 3;
@@ -619,7 +632,7 @@ gemm_tf32x3_asp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256u);
+    tmem_dealloc(tmem_base, C_::TMEM_COLS);
   }
 }
 
