@@ -114,7 +114,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       int it = 0;
       for (long long tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x) {
         const Tile tl = decode_tile(tab, tile, m_tiles, n_tiles, kb_per_seg, BN);
-        for (int kb = 0; kb < tl.n_kb; ++kb, ++it) {
+        // each tile starts its walk over the k-blocks at a different one, so that the CTAs do not all fetch the same
+        // weight lines from L2 at the same moment (the terms of a sum are the same, their order depends on the tile)
+        const int kb_start = (int)(tile % tl.n_kb);
+        for (int kbi = 0; kbi < tl.n_kb; ++kbi, ++it) {
+          const int kb = kbi + kb_start < tl.n_kb ? kbi + kb_start : kbi + kb_start - tl.n_kb;
           const int s = it % STAGES;
           mbar_wait(&empty[s], ((it / STAGES) & 1u) ^ 1u, status);
           unsigned char* st = stage_base + (size_t)s * C_::STAGE_BYTES;
@@ -507,7 +511,8 @@ gemm_tf32x3_asp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       for (int j = 0, blk = first; blk < m_blocks; ++j, blk += stride) {
         bool next_pending = blk + stride < m_blocks;
         int local = 0;
-        for (int nt = 0; nt < n_tiles; ++nt) {
+        for (int nti = 0; nti < n_tiles; ++nti) {
+          const int nt = (nti + blk) % n_tiles;     // staggered walk over the weight tiles (see the epilogue)
           for (int kb = 0; kb < n_kb; ++kb, ++it, ++local) {
             // the next A block is requested once this block's first weight tiles are on their way
             if (next_pending && local == 2) { load_a(j + 1, blk + stride); next_pending = false; }
@@ -593,7 +598,10 @@ gemm_tf32x3_asp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     uint32_t t = 0;
     for (int j = 0, blk = first; blk < m_blocks; ++j, blk += stride) {
       const long long row0 = (long long)blk * BM + quarter * 32;
-      for (int nt = 0; nt < n_tiles; ++nt, ++t) {
+      for (int nti = 0; nti < n_tiles; ++nti, ++t) {
+        // row block b starts at weight tile b mod n_tiles: the CTAs do not all fetch the same weight lines from L2
+        // at the same moment
+        const int nt = (nti + blk) % n_tiles;
         const uint32_t buf = t & 1u;
         mbar_wait(&acc_full[buf], (t >> 1) & 1u, status);
         tc_fence_after();
