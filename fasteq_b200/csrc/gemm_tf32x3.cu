@@ -71,7 +71,11 @@ __device__ __forceinline__ Tile decode_tile(const TcTable& tab, long long tile, 
   return r;
 }
 
-template <int BN>
+// A_TMEM (BN = 64, where tensor memory has room: accumulators 256 columns, A ring 4 x 64): the split warps write
+// the hi / lo parts of a k-block to tensor memory (thread = row = TMEM lane, tcgen05.st) and the MMAs take A from
+// there, which removes 32 KB of shared-memory writes and 32 KB of reads per k-block from the pipe that bounds the
+// long-K case.
+template <int BN, bool A_TMEM>
 __global__ void __launch_bounds__(NT_P, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBhi,
                    const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmC,
@@ -81,6 +85,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using C_ = Cfg<BN>;
   constexpr int STAGES = C_::STAGES;
+  constexpr uint32_t TMEM_COLS = A_TMEM ? 512u : (uint32_t)(4 * BN);
+  static_assert(!A_TMEM || 4 * BN + STAGES * 2 * BK <= 512, "tensor memory: accumulators + A ring");
   unsigned char* stage_base = smem;
   unsigned char* store_base = smem + STAGES * C_::STAGE_BYTES;     // [4 warps][2 slabs][32 rows x 128 B]
   uint64_t* bars = reinterpret_cast<uint64_t*>(store_base + C_::STORE_BYTES);
@@ -100,13 +106,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     mbar_fence_init();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(4 * BN)) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_a = tmem_base + (uint32_t)(4 * BN);     // A_TMEM: [STAGES][hi 32 columns | lo 32 columns]
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -157,8 +164,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
           for (int kk = 0; kk < BK / 8; ++kk) {
             const uint32_t off = kk * 32;   // 8 TF32 values = 32 bytes along K inside the 128-byte swizzle row
-            mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_hi + off), idesc2, (kb | kk) ? 1u : 0u);
-            mma_tf32(tmem_d + (uint32_t)BN, make_desc(a_lo + off), make_desc(b_hi + off), idesc1, 1u);
+            if (A_TMEM) {
+              const uint32_t ta = tmem_a + (uint32_t)(s * 2 * BK + kk * 8);
+              mma_tf32_a_tmem(tmem_d, ta, make_desc(b_hi + off), idesc2, (kb | kk) ? 1u : 0u);
+              mma_tf32_a_tmem(tmem_d + (uint32_t)BN, ta + (uint32_t)BK, make_desc(b_hi + off), idesc1, 1u);
+            } else {
+              mma_tf32(tmem_d, make_desc(a_hi + off), make_desc(b_hi + off), idesc2, (kb | kk) ? 1u : 0u);
+              mma_tf32(tmem_d + (uint32_t)BN, make_desc(a_lo + off), make_desc(b_hi + off), idesc1, 1u);
+            }
           }
           mma_commit(&empty[s]);            // the stage may be refilled once these MMAs have read it
         }
@@ -183,12 +196,30 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           hi.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); lo.z = v.z - hi.z;
           hi.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); lo.w = v.w - hi.w;
         };
+        if (A_TMEM) {
+          // thread = row of the tile = its TMEM lane; 16-byte chunk j of row r sits at chunk position j ^ (r & 7)
+          const int row = (warp & 3) * 32 + lane;
+          uint32_t hi_bits[32], lo_bits[32];
 #pragma unroll
-        for (int i = 0; i < C_::A_BYTES / 16 / 128; ++i) {
-          float4 hi, lo; split(a_hi[tid + i * 128], hi, lo);
-          a_hi[tid + i * 128] = hi; a_lo[tid + i * 128] = lo;
+          for (int j = 0; j < 8; ++j) {
+            float4 hi, lo; split(*reinterpret_cast<const float4*>(st + row * 128 + ((j ^ (row & 7)) << 4)), hi, lo);
+            hi_bits[4 * j] = __float_as_uint(hi.x); hi_bits[4 * j + 1] = __float_as_uint(hi.y);
+            hi_bits[4 * j + 2] = __float_as_uint(hi.z); hi_bits[4 * j + 3] = __float_as_uint(hi.w);
+            lo_bits[4 * j] = __float_as_uint(lo.x); lo_bits[4 * j + 1] = __float_as_uint(lo.y);
+            lo_bits[4 * j + 2] = __float_as_uint(lo.z); lo_bits[4 * j + 3] = __float_as_uint(lo.w);
+          }
+          const uint32_t ta = tmem_a + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(s * 2 * BK);
+          tmem_st_32(ta, hi_bits);
+          tmem_st_32(ta + (uint32_t)BK, lo_bits);
+          tc_fence_before();
+        } else {
+#pragma unroll
+          for (int i = 0; i < C_::A_BYTES / 16 / 128; ++i) {
+            float4 hi, lo; split(a_hi[tid + i * 128], hi, lo);
+            a_hi[tid + i * 128] = hi; a_lo[tid + i * 128] = lo;
+          }
+          fence_async_smem();               // generic-proxy writes -> visible to the tensor core's async proxy
         }
-        fence_async_smem();                 // generic-proxy writes -> visible to the tensor core's async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive(&full_split[s]);
       }
@@ -245,7 +276,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(4 * BN)) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -706,7 +737,8 @@ static int launch_bn(const TcTable& tab, const CUtensorMap& ma, const CUtensorMa
   int* st = nullptr;
   cudaError_t e = cudaGetSymbolAddress((void**)&st, g_tc_status);
   if (e != cudaSuccess) return cuda_fail(e);
-  e = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
+  constexpr bool A_TMEM = (BN == 64);
+  e = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, A_TMEM>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
   if (e != cudaSuccess) return cuda_fail(e);
   const long long m_tiles = (M + BM - 1) / BM;
   const int n_tiles = (N + BN - 1) / BN;
@@ -714,7 +746,7 @@ static int launch_bn(const TcTable& tab, const CUtensorMap& ma, const CUtensorMa
   const int sms = sm_count();
   if (sms < 1) return FASTEQ_CUDA_ERROR;
   const unsigned grid = (unsigned)(total < sms ? total : sms);     // one persistent CTA per SM
-  gemm_tf32x3_kernel<BN><<<grid, NT_P, Cfg<BN>::SMEM_BYTES, s>>>(ma, mbh, mbl, mc, tab, M, N, K, total, (int)m_tiles, n_tiles, st);
+  gemm_tf32x3_kernel<BN, A_TMEM><<<grid, NT_P, Cfg<BN>::SMEM_BYTES, s>>>(ma, mbh, mbl, mc, tab, M, N, K, total, (int)m_tiles, n_tiles, st);
   e = cudaGetLastError();
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }
