@@ -17,8 +17,9 @@
 //   warp 0       : TMA producer -- 3-D tiled loads (SWIZZLE_128B) of the raw A and Bt k-blocks
 //   warp 1       : allocates TMEM, issues tcgen05.mma (kind::tf32, M = 128, N = BN, K = 8) from one lane,
 //                  releases ring stages and signals the epilogue with tcgen05.commit
-//   warps 2..5   : split each raw k-block into hi / lo tiles in place (the swizzle is position
-//                  preserving, so no layout knowledge is needed)
+//   warps 2..5   : split each raw k-block into hi / lo tiles: in place in shared memory at BN = 128 (the
+//                  swizzle is position preserving), into tensor memory at BN = 64 (thread = row = TMEM
+//                  lane, tcgen05.st; the MMAs then take their A operand from tensor memory)
 //   warps 6..9   : read a finished accumulator with tcgen05.ld and store the tile through swizzled
 //                  staging slabs and TMA stores
 // Every mbarrier wait is bounded (about two seconds), after which a status word is set and the
