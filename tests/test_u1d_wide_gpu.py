@@ -1,0 +1,135 @@
+"""GPU parity, against the numpy oracle, of the 128-channel Uniform1D signatures that select the
+"wide" kernel layout: one CTA of four producer/consumer pipelines, two channels per thread with
+packed arithmetic.  These are the layouts the benchmark's headline figure and the MACE-style
+model run on; each test asserts the layout it exercises so that it cannot drift onto another.
+"""
+import numpy as np
+import pytest
+import torch
+
+from fasteq_b200.codegen.u1d import default_tuning
+from fasteq_b200.codegen.u1d_common import make_spec
+from fasteq_b200.descriptors import channelwise_tensor_product, full_channelwise_instructions
+from fasteq_b200.irreps import Irreps
+from fasteq_b200.sh import spherical_harmonics_host
+from oracle import uniform1d_ref
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5   # FP32, relative to the largest reference magnitude
+
+# (irreps_in1, parity filter, weight segments, output segments, deep-ring "small" variant)
+SIGNATURES = [
+    ("128x0e+128x1o", None, 13, 55, False),        # benchmark default: all couplings up to l = 3
+    ("128x0e+128x1o", "natural", 10, 40, False),   # second interaction layer of the MACE-style model
+    ("128x0e", "natural", 4, 16, True),            # first interaction layer: scalar senders
+]
+
+
+def _descriptor(in1, parity):
+    sh = Irreps.spherical_harmonics(3)
+    io, ins = full_channelwise_instructions(in1, sh, 3, parity_filter=parity)
+    return channelwise_tensor_product(in1, sh, io, ins)
+
+
+def _graph(n_nodes, g):
+    """Receiver-sorted edges with empty receivers (also the first and the last row), single-edge
+    receivers, and receivers whose edge count exceeds a producer batch (32) and every ring depth."""
+    deg = torch.randint(0, 24, (n_nodes,), generator=g)
+    deg[0] = 0
+    deg[n_nodes - 1] = 0
+    deg[5:9] = 0
+    deg[9] = 1
+    deg[17] = 33
+    deg[40] = 97
+    deg[41] = 64
+    deg[n_nodes - 2] = 150
+    dst = torch.repeat_interleave(torch.arange(n_nodes), deg)
+    src = torch.randint(0, n_nodes, (int(dst.numel()),), generator=g)
+    return src, dst
+
+
+def _close(got, ref, what):
+    got = got.detach().cpu().double().numpy().reshape(ref.shape)
+    err = np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30)
+    assert err <= TOL, f"{what}: relative error {err:.3e} > {TOL:.0e}"
+
+
+@pytest.mark.parametrize("in1,parity,w_segs,out_segs,small", SIGNATURES)
+def test_default_tuning_is_the_four_pipeline_packed_layout(in1, parity, w_segs, out_segs, small):
+    d = _descriptor(in1, parity)
+    assert (d.w_seg_num, d.out_seg_num) == (w_segs, out_segs)
+    spec = make_spec(d.i_list, d.j_list, d.k_list, d.v_list, d.coeff_list, w_segs=d.w_seg_num, x_segs=d.x_seg_num,
+                     y_segs=d.y_seg_num, out_segs=d.out_seg_num, u=d.u_dim, dtype="f32")
+    for direction in ("fwd", "bwd"):
+        tun = default_tuning(spec, direction)
+        assert (tun.pipes, tun.vec, tun.ct, tun.groups) == (4, 2, 128, 1), (direction, tun)
+    assert (default_tuning(spec, "fwd").stages == 10) == small
+
+
+@pytest.mark.parametrize("fused_sh", [False, True], ids=["y_harmonics", "y_vectors"])
+@pytest.mark.parametrize("in1,parity,w_segs,out_segs,small", SIGNATURES)
+def test_wide_layout_matches_oracle(in1, parity, w_segs, out_segs, small, fused_sh):
+    from fasteq_b200.ops import fast_uniform1d_jit
+    from fasteq_b200.ops import uniform1d_jit as u1d
+    d = _descriptor(in1, parity)
+    U, N = d.u_dim, 211
+    g = torch.Generator().manual_seed(20 + w_segs)
+    src, dst = _graph(N, g)
+    E = int(dst.numel())
+    assert E > 2000
+    w = torch.randn(E, d.w_seg_num * U, generator=g)
+    x = torch.randn(N, d.x_seg_num * U, generator=g)
+    vec = torch.randn(E, 3, generator=g) * 1.7
+    r = torch.randn(N, d.out_seg_num * U, generator=g)
+    y_ref = spherical_harmonics_host(3, vec.double().numpy(), normalize=True)           # float64 [E, 16]
+    meta = dict(d.meta(torch.float32, "cuda"))
+    if fused_sh:
+        meta["y_sh"] = ((0, 1, 2, 3), True, "component")
+        y_dev = vec.cuda().requires_grad_(True)
+    else:
+        y_dev = torch.from_numpy(y_ref).float().cuda().requires_grad_(True)
+    wd, xd = w.cuda().requires_grad_(True), x.cuda().requires_grad_(True)
+    idx_in, idx_out = {1: src.int().cuda()}, {0: dst.int().cuda()}
+    out = fast_uniform1d_jit(wd, xd, y_dev, idx_in, idx_out, meta)
+    gw, gx, gy = torch.autograd.grad(out, (wd, xd, y_dev), r.cuda())
+
+    # the modules that just ran are the wide ones
+    call = u1d._Call(wd, xd, y_dev, idx_in, idx_out, meta)
+    for direction, needs in (("fwd", (False, False, False)), ("bwd", (True, True, True))):
+        tun = u1d._tuning_for(call.spec, direction, (wd, xd, y_dev))
+        assert tun.pipes == 4 and tun.vec == 2
+        mod = u1d.get_module(call.spec, direction, needs, tuning=tun)
+        assert mod.desc.threads == 4 * (64 + 32)
+        assert mod.device_status() == 0
+
+    paths = list(zip(d.i_list.tolist(), d.j_list.tolist(), d.k_list.tolist(), d.v_list.tolist()))
+    a = lambda t, s: t.double().numpy().reshape(t.shape[0], s, -1)
+    y64 = y_ref if fused_sh else y_dev.detach().cpu().double().numpy()
+    y3 = y64.reshape(E, d.y_seg_num, 1)
+    kw = dict(src_x=src.numpy(), dst=dst.numpy())
+    ref = uniform1d_ref.uniform1d_forward(a(w, d.w_seg_num), a(x, d.x_seg_num), y3, paths, d.coeff_list, d.out_seg_num,
+                                          num_out_rows=N, **kw)
+    rgw, rgx, rgy = uniform1d_ref.uniform1d_backward(a(r, d.out_seg_num), a(w, d.w_seg_num), a(x, d.x_seg_num), y3, paths,
+                                                     d.coeff_list, **kw)
+    _close(out, ref, "forward")
+    _close(gw, rgw, "grad_w")
+    _close(gx, rgx, "grad_x")
+    if fused_sh:
+        # chain the oracle's harmonic gradient through the harmonics' Jacobian (central differences in float64)
+        v64 = vec.double().numpy()
+        jac = np.zeros((E, 16, 3))
+        h = 1e-6
+        for ax in range(3):
+            dv = np.zeros(3); dv[ax] = h
+            jac[:, :, ax] = (spherical_harmonics_host(3, v64 + dv, True) - spherical_harmonics_host(3, v64 - dv, True)) / (2 * h)
+        rgv = np.einsum("ek,eka->ea", rgy.reshape(E, 16).astype(np.float64), jac)
+        got = gy.detach().cpu().double().numpy()
+        err = np.abs(got - rgv).max() / max(np.abs(rgv).max(), 1e-30)
+        assert err <= 2e-5, f"grad_vec: relative error {err:.3e}"   # the finite-difference Jacobian adds ~1e-9; FP32 harmonics ~1e-6
+    else:
+        _close(gy, rgy, "grad_y")
+    # rows without edges are written as exact zeros
+    empty = torch.ones(N, dtype=torch.bool)
+    empty[dst.unique()] = False
+    assert torch.count_nonzero(out.detach()[empty.cuda()]) == 0
