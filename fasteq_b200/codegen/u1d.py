@@ -429,7 +429,8 @@ fasteq_u1d_fwd_kernel(const Graph g, const T* __restrict__ w, const T* __restric
   for (;;) {{
     const int stage = it % STAGES;
     const uint32_t ph = (it / STAGES) & 1u;
-    mbar_wait(&full[stage], ph, g.status);
+    // a wait that gave up means the stage record below was never written: stop, do not address memory from it
+    if (!mbar_wait(&full[stage], ph, g.status)) break;
     const unsigned char* st = stages + (size_t)stage * STAGE_BYTES;
     const Meta m = *reinterpret_cast<const Meta*>(st + OFF_META);
     const int valid = (U % CT == 0) ? CT : ((U - m.ct * CT) < CT ? (U - m.ct * CT) : CT);
@@ -597,7 +598,7 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
       // stage the receiver's grad_out tile once per segment
       const int b = nseg % (NGO ? NGO : 1);
       const uint32_t ph = (nseg / (NGO ? NGO : 1)) & 1u;
-      mbar_wait(&go_empty[b], ph ^ 1u, g.status);
+      if (!mbar_wait(&go_empty[b], ph ^ 1u, g.status)) {{ p.failed = true; return; }}
       const int valid = (U - ct * CT) < CT ? (U - ct * CT) : CT;
       if (ln == 0) mbar_arrive_expect_tx(&go_full[b], g.bulk_ok ? (uint32_t)(OSEG * valid * sizeof(T)) : 0u);
       __syncwarp();
@@ -656,13 +657,14 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
     L.append("""  for (;;) {
     const int stage = it % STAGES;
     const uint32_t ph = (it / STAGES) & 1u;
-    mbar_wait(&full[stage], ph, g.status);
+    // a wait that gave up means the stage record (or the grad_out tile) was never written: stop here
+    if (!mbar_wait(&full[stage], ph, g.status)) break;
     unsigned char* st = stages + (size_t)stage * STAGE_BYTES;
     const Meta m = *reinterpret_cast<const Meta*>(st + OFF_META);
     const int valid = (U % CT == 0) ? CT : ((U - m.ct * CT) < CT ? (U - m.ct * CT) : CT);
     const bool live = ch < valid;
     const int gb = nseg % (NGO ? NGO : 1);
-    if (NGO && (m.flags & F_FIRST)) mbar_wait(&go_full[gb], (nseg / (NGO ? NGO : 1)) & 1u, g.status);""")
+    if (NGO && (m.flags & F_FIRST) && !mbar_wait(&go_full[gb], (nseg / (NGO ? NGO : 1)) & 1u, g.status)) break;""")
     if spec.w_shared and need_gw:
         L.append("    if ((m.flags & (F_DATA | F_DONE)) && (m.ct != gws_ct || (m.flags & F_DONE))) {")
         L.append("      if (ch < ((U - gws_ct * CT) < CT ? (U - gws_ct * CT) : CT)) {")

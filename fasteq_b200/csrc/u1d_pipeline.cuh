@@ -78,6 +78,7 @@ __device__ __forceinline__ void copy_tile(unsigned char* sdst, const T* grow, in
 struct Producer {
   const Graph& g; const T* w; const T* x; const T* y;
   unsigned char* stages; uint64_t* full; uint64_t* empty; int lane; uint32_t it; int vblock;
+  bool failed = false;   // a wait of this lane gave up: the warp stops issuing copies and reductions (see dead())
 
   static __device__ __forceinline__ int valid_of(int ct) { return (U - ct * CT) < CT ? (U - ct * CT) : CT; }
   static __device__ __forceinline__ uint32_t tx_bytes(int valid) {
@@ -97,7 +98,7 @@ struct Producer {
   __device__ __forceinline__ void fill_one(uint32_t myit, int flags, int row, int ct, int e, int xr, int yr, Flush&& flush) {
     const int stage = myit % STAGES;
     const uint32_t ph = (myit / STAGES) & 1u;
-    mbar_wait(&empty[stage], ph ^ 1u, g.status);
+    if (!mbar_wait(&empty[stage], ph ^ 1u, g.status)) { failed = true; return; }
     unsigned char* st = stages + (size_t)stage * STAGE_BYTES;
     if (myit >= (uint32_t)STAGES) flush(st);
     const int valid = valid_of(ct);
@@ -131,6 +132,24 @@ struct Producer {
     cp_async_arrive_noinc(&full[stage]);
   }
 
+  // True for the whole warp once any lane's wait has given up (or a caller-side wait set `failed`).
+  // A stalled pipeline must not go on: the stage records the consumers would read next were never
+  // written, and flush() would add partial sums into gradients.
+  __device__ __forceinline__ bool dead() { return __any_sync(0xffffffffu, failed) != 0; }
+
+  // After a failed wait: give the copies this warp has already issued a bounded time to land before the
+  // CTA may exit (a full barrier completes on the producer's own arrives plus the copied bytes, whatever
+  // the consumers do).
+  __device__ __forceinline__ void settle() {
+    if (lane < STAGES && it > (uint32_t)lane) {
+      const uint32_t k = ((it - 1u - (uint32_t)lane) / STAGES) * STAGES + (uint32_t)lane;   // last fill of stage `lane`
+      const uint32_t ph = (k / STAGES) & 1u;
+#pragma unroll 1
+      for (int i = 0; i < 100000; ++i) if (mbar_try_wait(&full[lane], ph)) break;
+    }
+    __syncwarp();
+  }
+
   // Y_SH: the y operand is the edge vector; its harmonics are evaluated here, into the stage's y row
   __device__ __forceinline__ void sh_row(unsigned char* st, int yr) {
     const T* v = y + (size_t)yr * 3;
@@ -146,7 +165,8 @@ struct Producer {
   __device__ __forceinline__ void fill_coop(int flags, int row, int ct, int e, int xr, int yr, Flush&& flush) {
     const int stage = it % STAGES;
     const uint32_t ph = (it / STAGES) & 1u;
-    mbar_wait(&empty[stage], ph ^ 1u, g.status);
+    if (!mbar_wait(&empty[stage], ph ^ 1u, g.status)) failed = true;
+    if (dead()) return;
     unsigned char* st = stages + (size_t)stage * STAGE_BYTES;
     if (lane == 0) {
       if (it >= (uint32_t)STAGES) flush(st);
@@ -206,6 +226,7 @@ struct Producer {
         if (each_is_segment || (last && j == m - 1)) flags |= F_LAST;
         const int r = each_is_segment ? e : row;
         if (each_is_segment) begin(r, ct, lane);
+        if (dead()) return;
         if (g.bulk_ok) {
           if (lane == 0) fill_one(it, flags, r, ct, e, xr, yr, flush);
           __syncwarp();
@@ -235,8 +256,12 @@ struct Producer {
           for (int i = 0; i < n; ++i) {
             const int e0 = __shfl_sync(0xffffffffu, rp0, i), e1 = __shfl_sync(0xffffffffu, rp1, i);
             const int row = (int)(sb + i);
-            if (e0 >= e1) { if (cfg::EMIT_EMPTY_ROWS) fill_special(F_LAST, row, ct, flush); continue; }
+            if (e0 >= e1) {
+              if (cfg::EMIT_EMPTY_ROWS) { fill_special(F_LAST, row, ct, flush); if (dead()) { settle(); return; } }
+              continue;
+            }
             begin(row, ct, lane);
+            if (dead()) { settle(); return; }
             for (int pb = e0; pb < e1; pb += 32) {
               const int m = (e1 - pb) < 32 ? (e1 - pb) : 32;
               int me = 0, mx = 0, my = 0;
@@ -247,6 +272,7 @@ struct Producer {
                 my = cfg::Y_INDEXED ? checked(g.y_index[me], g.y_rows) : me;
               }
               fill_batch(m, me, mx, my, row, ct, pb == e0, pb + m == e1, false, flush, begin);
+              if (dead()) { settle(); return; }
             }
           }
         }
@@ -260,10 +286,12 @@ struct Producer {
             my = cfg::Y_INDEXED ? checked(g.y_index[me], g.y_rows) : me;
           }
           fill_batch(m, me, mx, my, 0, ct, true, true, true, flush, begin);
+          if (dead()) { settle(); return; }
         }
       }
     }
     fill_special(F_DONE, 0, 0, flush);
+    if (dead()) { settle(); return; }
     // drain: every stage still holding a finished edge gets its flush
     const uint32_t total = it;
     const uint32_t first = total > (uint32_t)STAGES ? total - STAGES : 0;
@@ -271,8 +299,7 @@ struct Producer {
     if (k < total) {
       const int stage = k % STAGES;
       const uint32_t ph = (k / STAGES) & 1u;
-      mbar_wait(&empty[stage], ph, g.status);
-      flush(stages + (size_t)stage * STAGE_BYTES);
+      if (mbar_wait(&empty[stage], ph, g.status)) flush(stages + (size_t)stage * STAGE_BYTES);
     }
     __syncwarp();
   }

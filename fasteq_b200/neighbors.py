@@ -79,5 +79,5 @@ def radius_graph(pos: torch.Tensor, atom_struct: torch.Tensor, box, cutoff: floa
                                                   dst.data_ptr(), shift.data_ptr(), stream), lib, "fasteq_neighbors_fill")
     if register_plan:
         from .ops.uniform1d_jit import register_sorted_plan
-        register_sorted_plan(dst, N, seg_ptr)
+        register_sorted_plan(dst, N, seg_ptr, owner=f"radius_graph:{dev}")
     return RadiusGraph(src, dst, shift, seg_ptr, max_deg)

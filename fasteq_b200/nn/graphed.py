@@ -15,6 +15,7 @@ from typing import Dict, Optional
 import torch
 
 from ..ops import _prepared
+from ..ops import uniform1d_jit as _u1d
 
 
 class GraphedEnergyForces:
@@ -32,9 +33,12 @@ class GraphedEnergyForces:
         torch.cuda.current_stream(pos.device).wait_stream(side)
         torch.cuda.synchronize(pos.device)
         self.graph = torch.cuda.CUDAGraph()
-        with _prepared.frozen_weights(), torch.cuda.graph(self.graph):
+        with _prepared.frozen_weights(), _u1d.record_plans() as plans, torch.cuda.graph(self.graph):
             self.static_out = model(self.static_pos, *static_args, **static_kwargs)
         self._prepared = _prepared.snapshot()      # the captured kernels read these buffers
+        # ... and the CSR offsets / permutations / partitions of these plans: the plan cache is a bounded LRU
+        # and would hand their memory back to the allocator after enough other graphs
+        self._plans = list(plans)
 
     def __call__(self, pos: torch.Tensor) -> Dict[str, torch.Tensor]:
         """Results live in static buffers that the next call overwrites; clone what must be kept."""

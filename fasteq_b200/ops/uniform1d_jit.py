@@ -17,6 +17,8 @@ from __future__ import annotations
 
 import ctypes
 import threading
+from collections import OrderedDict
+from contextlib import contextmanager
 from typing import Dict, List, Optional, Set, Tuple
 
 import numpy as np
@@ -123,9 +125,17 @@ class GraphPlan:
         cur = torch.cuda.current_stream(self.device)
         if cur.cuda_stream in self._waited:
             return
+        foreign = False
         for sid, ev in self._ready:
             if sid != cur.cuda_stream:
                 cur.wait_event(ev)
+                foreign = True
+        if foreign:
+            # a reader on a stream other than the building one: tell the allocator, so that an evicted
+            # plan's buffers are not handed out again while this stream still reads them
+            for t in (self.seg_ptr, self.perm, *self._parts.values()):
+                if t is not None:
+                    t.record_stream(cur)
         self._waited.add(cur.cuda_stream)
 
     def partition(self, n_parts: int) -> torch.Tensor:
@@ -142,31 +152,75 @@ class GraphPlan:
         return p
 
 
-_PLANS: Dict[Tuple, GraphPlan] = {}
+_PLANS: "OrderedDict[Tuple, GraphPlan]" = OrderedDict()   # least recently used first
 _PLAN_LIMIT = 64
+_OWNED: Dict[str, Tuple] = {}          # owner tag -> key of the plan that owner registered last
+_RECORDERS: List[list] = []            # lists that collect every plan a call uses (see record_plans)
+
+
+def _plan_key(dst: torch.Tensor, n_rows: int) -> Tuple:
+    return (dst.data_ptr(), dst.numel(), dst._version, str(dst.device), dst.dtype, int(n_rows))
+
+
+def _insert_plan(key: Tuple, plan: GraphPlan) -> None:
+    while len(_PLANS) >= _PLAN_LIMIT:
+        _PLANS.popitem(last=False)
+    _PLANS[key] = plan
 
 
 def graph_plan(dst: torch.Tensor, n_rows: int) -> GraphPlan:
-    key = (dst.data_ptr(), dst.numel(), dst._version, str(dst.device), dst.dtype, int(n_rows))
+    """Cached plan of a scatter index.  The key is the index tensor's storage address, length and torch
+    version counter: an index rewritten in place OUTSIDE torch's version tracking (memory shared with an
+    engine through DLPack / ``from_blob``, a write through ``.data``) keeps its key, so such callers must
+    treat index tensors as immutable or call ``invalidate_plan`` after every rewrite."""
+    key = _plan_key(dst, n_rows)
     plan = _PLANS.get(key)
     if plan is None:
-        if len(_PLANS) >= _PLAN_LIMIT:
-            _PLANS.pop(next(iter(_PLANS)))
         plan = GraphPlan(dst, n_rows)
         plan._keepalive = dst  # the key is the storage address: keep it from being recycled
-        _PLANS[key] = plan
+        _insert_plan(key, plan)
+    else:
+        _PLANS.move_to_end(key)
     return plan
 
 
-def register_sorted_plan(dst: torch.Tensor, n_rows: int, seg_ptr: torch.Tensor) -> GraphPlan:
-    """Install the plan of a receiver-sorted index whose CSR offsets are already known."""
-    key = (dst.data_ptr(), dst.numel(), dst._version, str(dst.device), dst.dtype, int(n_rows))
-    if len(_PLANS) >= _PLAN_LIMIT:
-        _PLANS.pop(next(iter(_PLANS)))
+def register_sorted_plan(dst: torch.Tensor, n_rows: int, seg_ptr: torch.Tensor, owner: Optional[str] = None) -> GraphPlan:
+    """Install the plan of a receiver-sorted index whose CSR offsets are already known.  ``owner``: a tag of
+    the caller that rebuilds its graph over and over (a neighbour-list builder): its previous plan is dropped
+    instead of filling the cache with dead index tensors."""
+    key = _plan_key(dst, n_rows)
+    if owner is not None:
+        old = _OWNED.get(owner)
+        if old is not None and old != key:
+            _PLANS.pop(old, None)
+        _OWNED[owner] = key
+    _PLANS.pop(key, None)
     plan = GraphPlan(dst, n_rows, seg_ptr)
     plan._keepalive = dst
-    _PLANS[key] = plan
+    _insert_plan(key, plan)
     return plan
+
+
+def invalidate_plan(dst: torch.Tensor) -> int:
+    """Forget every cached plan of this index tensor's storage (after an in-place rewrite that torch's
+    version counter does not see).  Returns the number of plans dropped."""
+    hits = [k for k in _PLANS if k[0] == dst.data_ptr() and k[3] == str(dst.device)]
+    for k in hits:
+        del _PLANS[k]
+    return len(hits)
+
+
+@contextmanager
+def record_plans():
+    """Collect the plans used by the operator calls made inside the block.  A CUDA graph captured there
+    bakes the plans' device pointers into its launches; whoever owns the graph must hold the collected
+    plans for as long as the graph is replayed (the cache alone may evict them)."""
+    got: list = []
+    _RECORDERS.append(got)
+    try:
+        yield got
+    finally:
+        _RECORDERS.remove(got)
 
 
 _SM_COUNT: Dict[int, int] = {}
@@ -277,6 +331,9 @@ class _Call:
             g.part_ptr = self.plan.partition(n_parts).data_ptr()
             g.n_parts = n_parts
             self.plan.ready_on_current_stream()
+            for rec in _RECORDERS:
+                if not any(p is self.plan for p in rec):
+                    rec.append(self.plan)
         return g
 
 

@@ -72,6 +72,16 @@ def build_standard_modules(verbose: bool = False) -> None:
             spec = cwtp_spec(in1, lsh, lout, dt)
             jobs.append((spec, "fwd", (False, False, False)))
             jobs.append((spec, "bwd", (True, True, True)))
+    # the 128-channel signatures of the wide-layout parity tests, with and without in-kernel harmonics
+    import dataclasses
+    for in1, parity in (("128x0e+128x1o", None), ("128x0e+128x1o", "natural"), ("128x0e", "natural")):
+        sh = Irreps.spherical_harmonics(3)
+        io, ins = full_channelwise_instructions(in1, sh, 3, parity_filter=parity)
+        d = channelwise_tensor_product(in1, sh, io, ins)
+        spec = make_spec(d.i_list, d.j_list, d.k_list, d.v_list, d.coeff_list, w_segs=d.w_seg_num, x_segs=d.x_seg_num,
+                         y_segs=d.y_seg_num, out_segs=d.out_seg_num, u=d.u_dim, dtype="f32")
+        for sp in (spec, dataclasses.replace(spec, y_sh=((0, 1, 2, 3), True, "component"))):
+            jobs += [(sp, "fwd", (False, False, False)), (sp, "bwd", (True, True, True))]
     stc_jobs = []
     for a, b, dtypes in STANDARD_STC:
         for dt in dtypes:

@@ -3,7 +3,9 @@ operations straight from the path tables (float64, autograd for the forces).
 
 Each operator is the path formula of the corresponding oracle (``uniform1d_ref``, ``eqlinear_ref``,
 ``stc_ref``) written with differentiable torch ops; the model structure follows
-``fasteq_b200.nn.mace_style`` and shares its parameters through ``load_from``.
+``fasteq_b200.nn.mace_style`` and takes its parameters from the model's state dict.  Of the product it reads only
+the modules' path tables (``layer.*.descriptor``, pinned to e3nn by the golden-vector tests) and hyper-parameters;
+the radial basis, the cutoff envelope and the SO3Linear row mapping are restated here.
 """
 from __future__ import annotations
 
@@ -30,9 +32,44 @@ def u1d_scatter(w, x, y, d, src, dst, n_out):
     return out.reshape(n_out, -1)
 
 
+def bessel_basis(r, r_max: float, num_basis: int):
+    """``sqrt(2 / r_max) * sin(n pi r / r_max) / r`` for n = 1 .. num_basis: NequIP's BesselEdgeLengthEncoding
+    (…/nequip/nn/embedding/_edge.py:174-189 writes it as ``sinc(x n pi) n pi`` up to the same prefactor)."""
+    n = torch.arange(1, num_basis + 1, dtype=r.dtype)
+    return math.sqrt(2.0 / r_max) * torch.sin(r.unsqueeze(-1) * (n * math.pi / r_max)) / r.unsqueeze(-1)
+
+
+def polynomial_cutoff(r, r_max: float, p: int = 5):
+    """``1 - (p+1)(p+2)/2 x^p + p(p+2) x^(p+1) - p(p+1)/2 x^(p+2)`` for ``x = r / r_max < 1``, else 0
+    (…/nequip/nn/embedding/cutoffs.py:17-27)."""
+    x = r / r_max
+    out = 1.0 - ((p + 1.0) * (p + 2.0) / 2.0) * torch.pow(x, p) + p * (p + 2.0) * torch.pow(x, p + 1) \
+        - (p * (p + 1.0) / 2.0) * torch.pow(x, p + 2)
+    return torch.where(x < 1.0, out, torch.zeros_like(out))
+
+
+def linear_mapping(desc):
+    """``[(in_row, out_row, weight_block, rows)]``, coefficients, u, v, I, J read from a ``uv,iu,iv`` descriptor's
+    public attributes only (``operands`` = weight / input / output segment shapes, ``paths[q].indices`` =
+    (weight block, input segment, output segment), ``paths[q].coefficients``): the segment protocol of
+    fasteq/ops/auto_schedule/eqlinear_descriptor.py:228-310, restated here so that the oracle does not run
+    the product's own descriptor parser."""
+    w_seg, in_seg, out_seg = (list(op) for op in desc.operands)
+    u, v = int(w_seg[0][0]), int(w_seg[0][1])
+    in_off = np.concatenate(([0], np.cumsum([int(s[0]) for s in in_seg])))
+    out_off = np.concatenate(([0], np.cumsum([int(s[0]) for s in out_seg])))
+    mapping, coeff = [], []
+    for path in desc.paths:
+        wq, a, b = (int(t) for t in path.indices)
+        rows = int(in_seg[a][0])
+        assert rows == int(out_seg[b][0]) and tuple(int(t) for t in w_seg[wq]) == (u, v)
+        mapping.append((int(in_off[a]), int(out_off[b]), wq, rows))
+        coeff.append(float(path.coefficients))
+    return mapping, coeff, u, v, int(in_off[-1]), int(out_off[-1])
+
+
 def eqlinear(x, w, desc):
-    from fasteq_b200.ops.eqlinear import _descriptor_problem
-    mapping, coeff, u, v, I, J = _descriptor_problem(desc)
+    mapping, coeff, u, v, I, J = linear_mapping(desc)
     x3, w3 = x.reshape(-1, I, u), w.reshape(len(mapping), u, v)
     rows = [None] * J
     for (ir, orow, wp, n), c in zip(mapping, coeff):
@@ -61,7 +98,6 @@ def energy_and_forces(model, pos, species, edge_src, edge_dst, edge_shift, param
     """Evaluate ``model`` (a ``MACEStyleModel`` whose parameters were moved to CPU/float64) with the oracle operators.
     ``params`` (optional) replaces the state dict, e.g. with leaves that require grad; with ``create_graph`` the
     forces stay attached to the graph so that a force loss can be differentiated."""
-    from fasteq_b200.nn.mace_style import bessel_basis, polynomial_cutoff
     pos = pos.detach().double().requires_grad_(True)
     p = params if params is not None else {k: v.detach().double().cpu() for k, v in model.state_dict().items()}
     vec = pos[edge_src] + edge_shift.double() - pos[edge_dst]
@@ -118,7 +154,6 @@ def gate_ref(x, spec):
 
 def nequip_energy_and_forces(model, pos, species, edge_src, edge_dst, edge_shift):
     """Oracle evaluation of ``fasteq_b200.nn.nequip_style.NequIPStyleModel`` (float64, CPU)."""
-    from fasteq_b200.nn.mace_style import bessel_basis, polynomial_cutoff
     pos = pos.detach().double().requires_grad_(True)
     p = {k: v.detach().double().cpu() for k, v in model.state_dict().items()}
     vec = pos[edge_src] + edge_shift.double() - pos[edge_dst]

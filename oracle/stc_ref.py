@@ -5,8 +5,10 @@ Restates the path semantics of fasteq/ops/auto_schedule/models.py:49-66 (padded 
 
     out[b, v, u] += c_p * prod_t x1[b, a_{p,t}, u] * x0[i0[b], d_p, u]
 
-The reference has no test that pins STC values ("parity unpinned" at the reference boundary);
-this formula is the pin for the operator, equivariance tests are the pin for the tables.
+The reference's own tests hold no STC values.  The pins are: this path formula for the operator; for the
+path TABLE, a span comparison with e3nn's ``ReducedTensorProducts`` (the e3nn shipped inside the reference's
+model bundles, golden file ``tests/golden/e3nn_golden.npz``: per output irrep and degree the table's basis
+elements and e3nn's change-of-basis rows span the same space) and an equivariance test.
 """
 from __future__ import annotations
 

@@ -113,6 +113,45 @@ out["gate_x"], out["gate_out"], out["gate_r"], out["gate_gx"] = gx.detach().nump
 out["gate_cst_scalars"] = np.array([a.cst if a is not None else 1.0 for a in gate.act_scalars.acts])
 out["gate_cst_gates"] = np.array([a.cst if a is not None else 1.0 for a in gate.act_gates.acts])
 
+# 6. Symmetric powers: e3nn's ReducedTensorProducts gives, per output irrep, a basis of the equivariant maps
+#    Sym^nu(V) -> irrep.  Stored as polynomial coefficients over index multisets a_1 <= .. <= a_nu
+#    (coefficient = sum of the symmetric tensor's entries over the distinct permutations of the multiset),
+#    for the output irreps the symmetric-contraction tests use.  The symmetric contraction of the MACE-style
+#    model contracts exactly these spaces with learned weights, so its table must span the same space.
+import itertools  # noqa: E402
+from e3nn.o3._reduce import ReducedTensorProducts  # noqa: E402
+FORMULA = {2: ("ij=ji", "ij"), 3: ("ijk=jik=ikj", "ijk")}
+for case, irr_in, wanted in (("l3", "1x0e+1x1o+1x2e+1x3o", ("0e", "1o")), ("l2", "1x0e+1x1o+1x2e", ("0e", "1o", "2e"))):
+    dim = Irreps(irr_in).dim
+    for nu in (2, 3):
+        rtp = ReducedTensorProducts(FORMULA[nu][0], i=irr_in)
+        Q = rtp.change_of_basis.numpy()                      # [irreps_out.dim, dim, .., dim]
+        multisets = list(itertools.combinations_with_replacement(range(dim), nu))
+        out[f"stc_{case}_nu{nu}_multisets"] = np.array(multisets, dtype=np.int64)
+        off = 0
+        for mul, ir in rtp.irreps_out:
+            rows = Q[off:off + mul * ir.dim].reshape((mul, ir.dim) + (dim,) * nu)
+            off += mul * ir.dim
+            if str(ir) not in wanted:
+                continue
+            poly = np.zeros((mul, ir.dim, len(multisets)))
+            for t, ms in enumerate(multisets):
+                for perm in set(itertools.permutations(ms)):
+                    poly[:, :, t] += rows[(slice(None), slice(None)) + perm]
+            out[f"stc_{case}_nu{nu}_{ir}"] = poly
+    out[f"stc_{case}_irreps_in"] = np.array([irr_in])
+
+# 7. Radial basis of the reference's NequIP bundle: 8 Bessel functions times the p = 5 polynomial cutoff of the
+#    normalised length x = r / r_max (module output: sinc(x n) n * cutoff(x); torch.sinc(z) = sin(pi z) / (pi z)).
+from nequip.nn.embedding._edge import BesselEdgeLengthEncoding  # noqa: E402
+from nequip.nn.embedding.cutoffs import PolynomialCutoff  # noqa: E402
+enc = BesselEdgeLengthEncoding(cutoff=PolynomialCutoff(p=5), num_bessels=8)
+xs = torch.cat([torch.linspace(0.02, 0.999, 40), torch.tensor([1.0, 1.05, 1.3])]).reshape(-1, 1)
+res = enc({enc.norm_length_field: xs})
+out["radial_x"] = xs.reshape(-1).numpy()
+out["radial_cutoff_p5"] = PolynomialCutoff(p=5)(xs).reshape(-1).numpy()
+out["radial_bessel8_times_cutoff"] = res[enc.edge_invariant_field].detach().numpy()
+
 dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "e3nn_golden.npz")
 np.savez_compressed(dst, **out)
 print("wrote", dst, os.path.getsize(dst), "bytes,", len(out), "arrays")

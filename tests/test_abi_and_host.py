@@ -81,6 +81,14 @@ def test_generated_source_has_no_cpu_path_and_bounded_waits():
     assert "fasteq_u1d_fwd_kernel<<<" in src and "extern \"C\" int fasteq_u1d_forward(" in src
     dev = open(os.path.join(ROOT, "fasteq_b200", "csrc", "fasteq_device.cuh")).read()
     assert "2000000000ull" in dev and "kDevWaitTimeout" in dev      # every mbarrier wait gives up
+    # no wait's verdict is dropped: consumers derive global addresses from the stage record a completed wait
+    # publishes, so a wait that gave up must end the loop (and stop the producer) instead of falling through
+    bwd = u1d.emit_backward(spec, u1d.default_tuning(spec, "bwd"), True, True, True)
+    pipe = open(os.path.join(ROOT, "fasteq_b200", "csrc", "u1d_pipeline.cuh")).read()
+    for text in (src, bwd, pipe):
+        for line in text.splitlines():
+            if "mbar_wait(" in line and not line.lstrip().startswith("//"):
+                assert "if (" in line and ("!mbar_wait(" in line or "if (mbar_wait(" in line), line
 
 
 def test_config1_graph_generator():

@@ -87,3 +87,37 @@ def test_path_oracle_reference_fixture():
     got = uniform1d_ref.uniform1d_forward(w, x, y, paths, coeffs, 3, src_x=src, dst=dst, num_out_rows=N)
     np.testing.assert_allclose(got, exp, rtol=1e-13, atol=1e-13)
     assert np.count_nonzero(got[:, 1]) == 0
+
+
+def test_radial_basis_matches_the_reference_bundle(golden):
+    """Polynomial cutoff (p = 5) and Bessel basis against the reference's NequIP bundle, for the model oracle's own
+    restatement and for the product's functions.  The bundle normalises the Bessel functions as ``sinc(n x) n``
+    (x = r / r_max); the MACE-style ``sqrt(2 / r_max) sin(n pi r / r_max) / r`` used here is that times the
+    constant ``sqrt(2 / r_max) pi / r_max``."""
+    import math
+    from fasteq_b200.nn import mace_style
+    from oracle import mace_style_ref
+    r_max = 5.0
+    x = torch.tensor(golden["radial_x"])
+    r = x * r_max
+    k = math.sqrt(2.0 / r_max) * math.pi / r_max
+    for mod in (mace_style_ref, mace_style):
+        cut = mod.polynomial_cutoff(r, r_max, 5)
+        np.testing.assert_allclose(cut.numpy(), golden["radial_cutoff_p5"], rtol=1e-12, atol=1e-14)
+        rb = mod.bessel_basis(r, r_max, 8) * cut.unsqueeze(-1)
+        np.testing.assert_allclose(rb.numpy(), k * golden["radial_bessel8_times_cutoff"], rtol=1e-11, atol=1e-13)
+    assert float(golden["radial_cutoff_p5"][-1]) == 0.0 and float(golden["radial_cutoff_p5"][-3]) == 0.0   # x >= 1
+
+
+def test_model_oracle_linear_mapping_matches_e3nn(golden):
+    """The model oracle's own reading of a uv,iu,iv descriptor reproduces e3nn ``Linear`` on the golden cases
+    (independently of the product's descriptor parser)."""
+    from fasteq_b200.descriptors import linear
+    from oracle import mace_style_ref
+    for name in ("simple", "multi"):
+        a, b = (str(s) for s in golden[f"lin_{name}_irreps"])
+        d = linear(a, b)
+        x = torch.tensor(mul_ir_to_ir_mul(golden[f"lin_{name}_x"], Irreps(a)))
+        w = torch.tensor(golden[f"lin_{name}_w"])
+        out = mace_style_ref.eqlinear(x, w, d)
+        np.testing.assert_allclose(ir_mul_to_mul_ir(out.numpy(), Irreps(b)), golden[f"lin_{name}_out"], rtol=1e-12, atol=1e-12)

@@ -71,3 +71,51 @@ def test_oracle_gradients_by_finite_differences():
             p = arr.copy(); p[idx] += eps; m = arr.copy(); m[idx] -= eps
             fd = (f(p, x0) - f(m, x0)) / (2 * eps) if which == 0 else (f(x1, p) - f(x1, m)) / (2 * eps)
             assert abs(fd - g[idx]) < 1e-6 * max(1.0, abs(fd))
+
+
+def _table_polynomials(d, nu, out_block, multisets):
+    """Polynomial coefficients of the table's degree-``nu`` basis elements that feed output block ``out_block``:
+    ``[n_basis, 2l+1, n_multisets]`` (one basis element per weight segment)."""
+    index = {tuple(ms): t for t, ms in enumerate(multisets.tolist())}
+    irr = d.irreps_out[out_block]
+    off = d.irreps_out.segment_offsets()[out_block]
+    segs = [s for s, (n, ob, _) in enumerate(d.weight_layout) if n == nu and ob == out_block]
+    poly = np.zeros((len(segs), irr.ir.dim, len(multisets)))
+    for (a, dd, v), c in zip(stc_ref.split_paths(d.paths), d.coeffs):
+        if dd in segs:
+            assert len(a) == nu and off <= v < off + irr.ir.dim
+            poly[segs.index(dd), v - off, index[tuple(a)]] += c
+    return poly
+
+
+@pytest.mark.parametrize("case,irr_out", [("l3", "1x0e+1x1o"), ("l2", "1x0e+1x1o+1x2e")])
+def test_table_spans_the_space_e3nn_reduces_to(golden, case, irr_out):
+    """Pin of the basis itself: for every output irrep and degree, the table's basis elements and the rows of
+    e3nn's ``ReducedTensorProducts`` change of basis (golden file, generated from the e3nn shipped inside the
+    reference) span the SAME space of polynomial maps Sym^nu(V) -> irrep: same dimension, and stacking both
+    adds no rank.  The operator built on this table therefore differs from one built on e3nn's / MACE's basis only
+    by an invertible mix of the learned weights."""
+    irr_in = str(golden[f"stc_{case}_irreps_in"][0])
+    d = symmetric_contraction(irr_in, irr_out)
+    for nu in (2, 3):
+        multisets = golden[f"stc_{case}_nu{nu}_multisets"]
+        for ob, blk in enumerate(Irreps(irr_out)):
+            ref = golden[f"stc_{case}_nu{nu}_{blk.ir}"]
+            ours = _table_polynomials(d, nu, ob, multisets)
+            assert ours.shape[0] == ref.shape[0], (nu, str(blk.ir), ours.shape, ref.shape)      # multiplicity of the irrep
+            flat = lambda p: p.reshape(p.shape[0], -1)
+            rank = lambda m: int(np.linalg.matrix_rank(m, tol=1e-9))
+            n = ref.shape[0]
+            assert rank(flat(ref)) == n and rank(flat(ours)) == n
+            assert rank(np.concatenate([flat(ref), flat(ours)])) == n
+            # and explicitly: ours = M @ ref with a well-conditioned mixing matrix M
+            M, res, *_ = np.linalg.lstsq(flat(ref).T, flat(ours).T, rcond=None)
+            np.testing.assert_allclose(flat(ref).T @ M, flat(ours).T, atol=1e-10)
+            assert np.linalg.cond(M) < 1e3
+    # degree 1 is the identity on the matching irrep (scaled to unit Frobenius norm like every basis element)
+    for s, (nu, ob, _) in enumerate(d.weight_layout):
+        if nu == 1:
+            rows = [(a, v, c) for (a, dd, v), c in zip(stc_ref.split_paths(d.paths), d.coeffs) if dd == s]
+            dim = Irreps(irr_out)[ob].ir.dim
+            assert len(rows) == dim and all(abs(c - dim ** -0.5) < 1e-12 for _, _, c in rows)
+            assert sorted(v for _, v, _ in rows) == list(range(Irreps(irr_out).segment_offsets()[ob], Irreps(irr_out).segment_offsets()[ob] + dim))
