@@ -361,3 +361,20 @@ extern "C" int fasteq_stc_double_backward(const void*, const void*, const void*,
 }
 """)
     return head + "\n".join(body) + "\n"
+
+
+def arith_ops(spec: STCSpec, direction: str, need_gx0: bool = False) -> Dict[str, int]:
+    """Floating-point instructions one (node, channel) thread executes in the generated kernel, counted in its
+    source text: ``fma(...)`` calls and explicit multiplications (the kernel body is straight-line code, so the
+    count is the executed count).  Used to state the kernels' FP32-issue utilisation."""
+    import re
+    src = emit_stc(spec, direction, need_gx0)
+    body = src[src.index("__global__"):]
+    end = body.find('extern "C"')
+    body = body[:end if end > 0 else len(body)]
+    body = re.sub(r"//[^\n]*", "", body)
+    body = re.sub(r"\[[^\]]*\]", "[]", body)                                   # subscripts hold index arithmetic only
+    body = "\n".join(ln for ln in body.splitlines() if "size_t" not in ln and "const T*" not in ln)
+    fma = len(re.findall(r"\bfma\(", body))
+    mul = len(re.findall(r"\s\*\s", body)) - len(re.findall(r"\b1\.0f? \* ", body))   # x * 1.0 is folded away by the compiler
+    return {"fma": fma, "mul": mul}

@@ -199,12 +199,18 @@ _NOALLOC_FORWARD = r"""
 //   * at most FASTEQ_NOALLOC_MAX_ROWS output rows (receivers); larger calls are refused with
 //     FASTEQ_UNSUPPORTED and nothing is launched;
 //   * edges must already be sorted by receiver (there is no room for a permutation);
-//   * the array (about 1 MB) is reserved on every GPU that loads this library until the process
-//     exits, and all calls share it.  Every entry a call reads is written earlier in the same
+//   * the array (about 1 MB) belongs to THIS module (one generated library per operator signature; a
+//     process that loads several forward modules holds one array per module) and is reserved on every
+//     GPU that loads it until the process exits; all calls into the module share it.  Every entry a call reads is written earlier in the same
 //     call, so nothing has to be cleared between calls, but two calls that overlap on the GPU
 //     (different streams, or different host threads) overwrite each other's offsets: serialise them;
 //   * the first call on each device looks up the array's device address (cudaGetSymbolAddress,
-//     with that device current).  Make that first call outside of any stream capture.
+//     with that device current).  Make that first call outside of any stream capture.  The look-up
+//     may run on several host threads at once (they store the same address);
+//   * a call that is refused (bad argument, size limit, misaligned operand) launches nothing, so it
+//     cannot disturb the offsets of a call in flight;
+//   * receiver indices outside [0, n_out_rows) are not reported: such edges belong to no row and
+//     are left out.
 // ---------------------------------------------------------------------------------------------
 #define FASTEQ_NOALLOC_MAX_ROWS 262144
 #define FASTEQ_NOALLOC_MAX_PARTS 4096
@@ -235,7 +241,7 @@ __global__ void na_partition(const int* __restrict__ seg_ptr, long long n_rows, 
   part_ptr[p] = (int)lo;
 }
 constexpr int kMaxDevices = 64;
-int* g_noalloc_addr[kMaxDevices];   // device address of g_noalloc_scratch per device, filled on first use
+std::atomic<int*> g_noalloc_addr[kMaxDevices];   // device address of g_noalloc_scratch per device, filled on first use
 }  // namespace
 
 extern "C" int fasteq_u1d_forward_noalloc(const int32_t* dst_sorted, const int32_t* x_index, int64_t n_edges,
@@ -250,18 +256,19 @@ extern "C" int fasteq_u1d_forward_noalloc(const int32_t* dst_sorted, const int32
   }
   if (n_out_rows == 0) return FASTEQ_OK;
   if (!out || (n_edges > 0 && (!dst_sorted || !w || !x || !y || (cfg::X_INDEXED && !x_index)))) return FASTEQ_INVALID;
+  // everything fasteq_u1d_forward would refuse is refused here, before anything touches the shared array
+  if (VEC == 2 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(w)) & 7u)) return FASTEQ_INVALID;
   int dev = 0, sms = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail(e);
   if (dev < 0 || dev >= kMaxDevices) return FASTEQ_UNSUPPORTED;
-  if (!g_noalloc_addr[dev]) {
+  int* seg_ptr = g_noalloc_addr[dev].load(std::memory_order_acquire);
+  if (!seg_ptr) {
     // once per device, with that device current: the symbol's name is only a host-side handle
-    int* p = nullptr;
-    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    e = cudaGetSymbolAddress((void**)&seg_ptr, g_noalloc_scratch);
     if (e != cudaSuccess) return cuda_fail(e);
-    g_noalloc_addr[dev] = p;
+    g_noalloc_addr[dev].store(seg_ptr, std::memory_order_release);
   }
-  int* seg_ptr = g_noalloc_addr[dev];
   int* part_ptr = seg_ptr + FASTEQ_NOALLOC_MAX_ROWS + 1;
   e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) return cuda_fail(e);
@@ -284,7 +291,7 @@ extern "C" int fasteq_u1d_forward_noalloc(const int32_t* dst_sorted, const int32
 
 def _prelude(spec: U1DSpec, tun: Tuning, extra_bytes: int, ncons_warps: int, emit_empty: bool = True) -> str:
     return ("// Generated by fasteq_b200.codegen.u1d -- do not edit.\n"
-            "#include <cstdio>\n#include <cstdint>\n#include <cuda_runtime.h>\n"
+            "#include <atomic>\n#include <cstdio>\n#include <cstdint>\n#include <cuda_runtime.h>\n"
             '#include "fasteq_b200.h"\n' + _cfg(spec, tun, extra_bytes, ncons_warps, emit_empty) +
             '#include "u1d_pipeline.cuh"\nusing namespace fasteq;\nusing namespace fasteq::u1d;\n'
             "using V = cfg::V;\nusing VS = VT<V>;\nconstexpr int VEC = VS::N;\nconstexpr int TPG = CT / VEC;  // threads per group\n")

@@ -46,7 +46,10 @@ extern "C" int fasteq_graph_check_sorted(const int32_t* dst, int64_t n, int32_t*
   set_flag_kernel<<<1, 1, 0, s>>>(flag, 1);
   if (n > 1) {
     long long blocks = (n + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+      sms = 128;
+    if (blocks > (long long)sms * 8) blocks = (long long)sms * 8;     // grid-stride loop: eight resident CTAs per SM
     check_sorted_kernel<<<(int)blocks, 256, 0, s>>>(dst, n, flag);
   }
   cudaError_t e = cudaGetLastError();

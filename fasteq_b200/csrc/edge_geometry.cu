@@ -53,11 +53,18 @@ __device__ __forceinline__ void envelope(T x, int p, T& env, T& denv) {
 template <typename T>
 __global__ void __launch_bounds__(256) edge_geometry_fwd_kernel(const T* __restrict__ pos, const int* __restrict__ src,
                                                                 const int* __restrict__ dst, const T* __restrict__ shift,
-                                                                long long n_edges, T r_max, int n_basis, int p,
-                                                                T* __restrict__ vec, T* __restrict__ basis) {
+                                                                long long n_edges, long long n_nodes, T r_max, int n_basis, int p,
+                                                                T* __restrict__ vec, T* __restrict__ basis, int* status) {
   const T pi = T(3.14159265358979323846);
   for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < n_edges; e += (long long)gridDim.x * blockDim.x) {
     const long long s = src[e], d = dst[e];
+    if (s < 0 || s >= n_nodes || d < 0 || d >= n_nodes) {
+      // an index outside the position array: record it, touch nothing through it, give the edge zero features
+      atomicExch(status, 2);
+      vec[3 * e] = vec[3 * e + 1] = vec[3 * e + 2] = T(0);
+      for (int n = 0; n < n_basis; ++n) basis[e * n_basis + n] = T(0);
+      continue;
+    }
     T v[3];
 #pragma unroll
     for (int k = 0; k < 3; ++k) v[k] = (pos[3 * s + k] + shift[3 * e + k]) - pos[3 * d + k];
@@ -65,8 +72,14 @@ __global__ void __launch_bounds__(256) edge_geometry_fwd_kernel(const T* __restr
     const T r = Math<T>::sqrt_(v[0] * v[0] + v[1] * v[1] + v[2] * v[2]);
     T env, denv;
     envelope(r / r_max, p, env, denv);
-    const T pref = Math<T>::sqrt_(T(2) / r_max) * env / r;
-    for (int n = 0; n < n_basis; ++n) basis[e * n_basis + n] = pref * Math<T>::sin_((n + 1) * pi * r / r_max);
+    if (r > T(0)) {
+      const T pref = Math<T>::sqrt_(T(2) / r_max) * env / r;
+      for (int n = 0; n < n_basis; ++n) basis[e * n_basis + n] = pref * Math<T>::sin_((n + 1) * pi * r / r_max);
+    } else {
+      // coincident pair: the limit sin(k r) / r -> k (env(0) = 1); the gradient of that limit vanishes
+      const T c0 = Math<T>::sqrt_(T(2) / r_max);
+      for (int n = 0; n < n_basis; ++n) basis[e * n_basis + n] = c0 * (n + 1) * pi / r_max;
+    }
   }
 }
 
@@ -74,18 +87,19 @@ template <typename T>
 __global__ void __launch_bounds__(256) edge_geometry_bwd_kernel(const T* __restrict__ pos, const int* __restrict__ src,
                                                                 const int* __restrict__ dst, const T* __restrict__ shift,
                                                                 const T* __restrict__ g_vec, const T* __restrict__ g_basis,
-                                                                long long n_edges, T r_max, int n_basis, int p,
-                                                                T* __restrict__ g_pos) {
+                                                                long long n_edges, long long n_nodes, T r_max, int n_basis, int p,
+                                                                T* __restrict__ g_pos, int* status) {
   const T pi = T(3.14159265358979323846);
   for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < n_edges; e += (long long)gridDim.x * blockDim.x) {
     const long long s = src[e], d = dst[e];
+    if (s < 0 || s >= n_nodes || d < 0 || d >= n_nodes) { atomicExch(status, 2); continue; }
     T v[3];
 #pragma unroll
     for (int k = 0; k < 3; ++k) v[k] = (pos[3 * s + k] + shift[3 * e + k]) - pos[3 * d + k];
     T g[3] = {T(0), T(0), T(0)};
     if (g_vec) { g[0] = g_vec[3 * e]; g[1] = g_vec[3 * e + 1]; g[2] = g_vec[3 * e + 2]; }
-    if (g_basis) {
-      const T r = Math<T>::sqrt_(v[0] * v[0] + v[1] * v[1] + v[2] * v[2]);
+    const T r = Math<T>::sqrt_(v[0] * v[0] + v[1] * v[1] + v[2] * v[2]);
+    if (g_basis && r > T(0)) {        // r == 0: the basis sits at its limit, whose gradient is zero
       T env, denv;
       envelope(r / r_max, p, env, denv);
       const T c0 = Math<T>::sqrt_(T(2) / r_max);
@@ -109,11 +123,28 @@ __global__ void __launch_bounds__(256) edge_geometry_bwd_kernel(const T* __restr
   }
 }
 
+__device__ int g_geom_status;   // first fault of the edge-geometry kernels (2 = index outside the position array)
+
+int* status_ptr() {
+  int* p = nullptr;
+  if (cudaGetSymbolAddress((void**)&p, g_geom_status) != cudaSuccess) return nullptr;
+  return p;
+}
+
+long long grid_cap() {   // grid-stride loops: sixteen resident CTAs of 256 threads per SM
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 128;
+  return (long long)sms * 16;
+}
+
 template <typename T>
-int run_fwd(const void* pos, const int* src, const int* dst, const void* shift, long long E, double r_max, int nb, int p, void* vec,
-            void* basis, cudaStream_t s) {
-  long long blocks = (E + 255) / 256; if (blocks > 148 * 16) blocks = 148 * 16;
-  edge_geometry_fwd_kernel<T><<<(unsigned)blocks, 256, 0, s>>>((const T*)pos, src, dst, (const T*)shift, E, (T)r_max, nb, p, (T*)vec, (T*)basis);
+int run_fwd(const void* pos, const int* src, const int* dst, const void* shift, long long E, long long N, double r_max, int nb, int p,
+            void* vec, void* basis, cudaStream_t s) {
+  int* st = status_ptr();
+  if (!st) return FASTEQ_CUDA_ERROR;
+  long long blocks = (E + 255) / 256; if (blocks > grid_cap()) blocks = grid_cap();
+  edge_geometry_fwd_kernel<T><<<(unsigned)blocks, 256, 0, s>>>((const T*)pos, src, dst, (const T*)shift, E, N, (T)r_max, nb, p, (T*)vec,
+                                                               (T*)basis, st);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }
@@ -124,9 +155,11 @@ int run_bwd(const void* pos, const int* src, const int* dst, const void* shift, 
   cudaError_t e = cudaMemsetAsync(gpos, 0, (size_t)N * 3 * sizeof(T), s);
   if (e != cudaSuccess) return cuda_fail(e);
   if (E == 0) return FASTEQ_OK;
-  long long blocks = (E + 255) / 256; if (blocks > 148 * 16) blocks = 148 * 16;
-  edge_geometry_bwd_kernel<T><<<(unsigned)blocks, 256, 0, s>>>((const T*)pos, src, dst, (const T*)shift, (const T*)gv, (const T*)gb, E,
-                                                               (T)r_max, nb, p, (T*)gpos);
+  int* st = status_ptr();
+  if (!st) return FASTEQ_CUDA_ERROR;
+  long long blocks = (E + 255) / 256; if (blocks > grid_cap()) blocks = grid_cap();
+  edge_geometry_bwd_kernel<T><<<(unsigned)blocks, 256, 0, s>>>((const T*)pos, src, dst, (const T*)shift, (const T*)gv, (const T*)gb, E, N,
+                                                               (T)r_max, nb, p, (T*)gpos, st);
   e = cudaGetLastError();
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }
@@ -134,13 +167,13 @@ int run_bwd(const void* pos, const int* src, const int* dst, const void* shift, 
 }  // namespace
 
 extern "C" int fasteq_edge_geometry_forward(int32_t dtype, const void* pos, const int32_t* src, const int32_t* dst, const void* shift,
-                                            int64_t n_edges, double r_max, int32_t n_basis, int32_t envelope_p, void* vec,
-                                            void* basis, fasteq_stream_t stream) {
-  if (n_edges < 0 || n_basis < 1 || n_basis > kMaxBasis || envelope_p < 1 || !(r_max > 0.0)) return FASTEQ_INVALID;
+                                            int64_t n_edges, int64_t n_nodes, double r_max, int32_t n_basis, int32_t envelope_p,
+                                            void* vec, void* basis, fasteq_stream_t stream) {
+  if (n_edges < 0 || n_nodes < 0 || n_basis < 1 || n_basis > kMaxBasis || envelope_p < 1 || !(r_max > 0.0)) return FASTEQ_INVALID;
   if (n_edges == 0) return FASTEQ_OK;
   if (!pos || !src || !dst || !shift || !vec || !basis) return FASTEQ_INVALID;
-  if (dtype == FASTEQ_F32) return run_fwd<float>(pos, src, dst, shift, n_edges, r_max, n_basis, envelope_p, vec, basis, (cudaStream_t)stream);
-  if (dtype == FASTEQ_F64) return run_fwd<double>(pos, src, dst, shift, n_edges, r_max, n_basis, envelope_p, vec, basis, (cudaStream_t)stream);
+  if (dtype == FASTEQ_F32) return run_fwd<float>(pos, src, dst, shift, n_edges, n_nodes, r_max, n_basis, envelope_p, vec, basis, (cudaStream_t)stream);
+  if (dtype == FASTEQ_F64) return run_fwd<double>(pos, src, dst, shift, n_edges, n_nodes, r_max, n_basis, envelope_p, vec, basis, (cudaStream_t)stream);
   return FASTEQ_INVALID;
 }
 
@@ -155,4 +188,15 @@ extern "C" int fasteq_edge_geometry_backward(int32_t dtype, const void* pos, con
   if (dtype == FASTEQ_F64)
     return run_bwd<double>(pos, src, dst, shift, grad_vec, grad_basis, n_edges, n_nodes, r_max, n_basis, envelope_p, grad_pos, (cudaStream_t)stream);
   return FASTEQ_INVALID;
+}
+
+extern "C" int fasteq_edge_geometry_device_status(int32_t* code) {
+  if (!code) return FASTEQ_INVALID;
+  int v = 0, zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_geom_status, sizeof(int));
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaMemcpyToSymbol(g_geom_status, &zero, sizeof(int));
+  if (e != cudaSuccess) return cuda_fail(e);
+  *code = v;
+  return FASTEQ_OK;
 }

@@ -136,7 +136,7 @@ class MACEStyleModel(torch.nn.Module):
         e = pos.new_zeros(pos.shape[0])
         for layer, ro in zip(self.layers, self.readouts):
             h = layer(h, species, edge_sh, edge_radial, edge_dst, edge_src, halo, edge_vec)
-            e = e + h[:, : self.channels] @ ro          # scalars are the first segment of the ir_mul row
+            e = e + (h[:, : self.channels] * ro).sum(dim=-1)     # scalars are the first segment of the ir_mul row
         return e
 
     def forward(self, pos, species, edge_src, edge_dst, edge_shift, node_graph=None, n_graphs: int = 1, forces: bool = True,

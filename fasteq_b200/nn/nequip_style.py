@@ -90,7 +90,7 @@ class NequIPStyleModel(torch.nn.Module):
         h = self.embedding[species]
         for layer in self.layers:
             h = layer(h, edge_sh, radial, edge_dst, edge_src, halo, vec if fused else None)
-        return h[:, : self.channels] @ self.readout
+        return (h[:, : self.channels] * self.readout).sum(dim=-1)     # per-atom scalar readout: elementwise + row sum
 
     def forward(self, pos, species, edge_src, edge_dst, edge_shift, forces: bool = True, halo=None, create_graph: bool = False):
         """``create_graph``: keep the forces differentiable, for a force loss."""

@@ -17,7 +17,8 @@ def _lib():
     lib = _cabi.core()
     if not _ready:
         v = C.c_void_p
-        lib.fasteq_edge_geometry_forward.argtypes = [C.c_int32, v, v, v, v, C.c_int64, C.c_double, C.c_int32, C.c_int32, v, v, v]
+        lib.fasteq_edge_geometry_forward.argtypes = [C.c_int32, v, v, v, v, C.c_int64, C.c_int64, C.c_double, C.c_int32, C.c_int32, v, v, v]
+        lib.fasteq_edge_geometry_device_status.argtypes = [C.POINTER(C.c_int32)]
         lib.fasteq_edge_geometry_backward.argtypes = [C.c_int32, v, v, v, v, v, v, C.c_int64, C.c_int64, C.c_double, C.c_int32,
                                                       C.c_int32, v, v]
         _ready = True
@@ -39,7 +40,7 @@ class _EdgeGeometry(torch.autograd.Function):
         code = 0 if pos.dtype == torch.float32 else 1
         lib = _lib()
         with torch.cuda.device(pos.device):
-            rc = lib.fasteq_edge_geometry_forward(code, pos.data_ptr(), src.data_ptr(), dst.data_ptr(), shift.data_ptr(), E, float(r_max),
+            rc = lib.fasteq_edge_geometry_forward(code, pos.data_ptr(), src.data_ptr(), dst.data_ptr(), shift.data_ptr(), E, pos.shape[0], float(r_max),
                                                   n_basis, p, vec.data_ptr(), basis.data_ptr(), torch.cuda.current_stream(pos.device).cuda_stream)
         _cabi.check(rc, lib, "fasteq_edge_geometry_forward")
         ctx.save_for_backward(pos, src, dst, shift)
@@ -74,3 +75,12 @@ def edge_geometry_usable(pos: torch.Tensor, n_basis: int) -> bool:
 def edge_geometry(pos, edge_src, edge_dst, edge_shift, r_max: float, n_basis: int, envelope_p: int):
     """``(vec [E, 3], basis [E, n_basis])``; differentiable once with respect to ``pos``."""
     return _EdgeGeometry.apply(pos, edge_src, edge_dst, edge_shift, r_max, n_basis, envelope_p)
+
+
+def edge_geometry_device_status() -> int:
+    """Reads and clears the kernels' status word (synchronises): 0, or 2 after an edge index outside the position array
+    (such an edge is skipped: zero features, no gradient)."""
+    lib = _lib()
+    v = C.c_int32(0)
+    _cabi.check(lib.fasteq_edge_geometry_device_status(C.byref(v)), lib, "fasteq_edge_geometry_device_status")
+    return int(v.value)

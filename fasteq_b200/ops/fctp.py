@@ -22,7 +22,7 @@ import torch
 from .. import _cabi
 from .eqlinear import _core, _make_problem
 
-__all__ = ["fast_fctp"]
+__all__ = ["fast_fctp", "fctp_species_groups"]
 
 _PLAN_CACHE: Dict[Tuple, Tuple] = {}
 
@@ -70,11 +70,26 @@ def _runs(meta) -> Tuple[List[Tuple[int, int, int, int]], List[float], List[int]
     return out
 
 
-def _species_groups(y: torch.Tensor, V: int):
+def fctp_species_groups(y: torch.Tensor):
+    """``(order, counts)``: the permutation that sorts the nodes by species ``argmax(y[b])`` and the host list of
+    nodes per species.  Computing it costs one host synchronisation; the species of a structure do not change from
+    step to step, so a caller can compute it once and pass it as ``meta["species_groups"]`` to ``fast_fctp``, which
+    then makes no host synchronisation at all."""
     vstar = torch.argmax(y, dim=1)
     order = torch.argsort(vstar, stable=True)
-    counts = torch.bincount(vstar, minlength=V).tolist()          # one host sync per call
+    counts = torch.bincount(vstar, minlength=y.shape[1]).tolist()
     return order, counts
+
+
+def _species_groups(y: torch.Tensor, V: int, meta):
+    pre = meta.get("species_groups")
+    if pre is not None:
+        order, counts = pre
+        counts = [int(c) for c in counts]
+        if len(counts) != V or sum(counts) != y.shape[0] or order.numel() != y.shape[0]:
+            raise ValueError("fast_fctp: meta['species_groups'] does not match y")
+        return order.to(y.device), counts
+    return fctp_species_groups(y)                                   # one host sync per call
 
 
 def _precision(dtype) -> int:
@@ -97,7 +112,7 @@ class FastFullyConnectedTensorProductPathFused(torch.autograd.Function):
             raise ValueError("fast_fctp: operand shapes do not match the meta (x [B, I*U], w [P, U, V, W], y [B, V])")
         mapping, coeff, paths = _runs(meta)
         prec = _precision(x.dtype)
-        order, counts = _species_groups(y, V)
+        order, counts = _species_groups(y, V, meta)
         xs = x.reshape(B, I, U)[order].contiguous()
         w4 = w.reshape(P, U, V, W)
         pidx = torch.tensor(paths, device=w.device)

@@ -14,6 +14,7 @@ STANDARD_CWTP = [
     ("128x0e+128x1o", 3, 3, ("f32",)),                # config 1 interaction
     ("64x0e+64x1o", 3, 3, ("f32", "f64")),
     ("32x0e+32x1o", 2, 2, ("f32", "f64")),
+    ("33x0e+33x1o", 2, 2, ("f32",)),                  # a channel tail (u not a multiple of the tile)
 ]
 
 
@@ -91,6 +92,9 @@ def build_standard_modules(verbose: bool = False) -> None:
     from .ops import spherical_harmonics as shmod
     sh_jobs = []
     for dt, kind, kw in (("f32", "mace", {}), ("f64", "mace", dict(num_species=3, channels=32, r_max=3.5)),
+                         ("f64", "mace", dict(channels=256, hidden_lmax=2)),       # benchmark configuration 2
+                         ("f32", "mace", dict(num_species=3, channels=32, r_max=3.5)),
+                         ("f32", "mace", dict(num_species=4, channels=128, r_max=4.0)),
                          ("f32", "nequip", dict(num_species=2, channels=64, lmax=2, sh_lmax=2, num_layers=4, r_max=4.0))):
         a, b, ls = model_jobs(dt, kind, **kw)
         jobs += a

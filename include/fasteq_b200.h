@@ -90,12 +90,15 @@ int fasteq_u1d_forward(const fasteq_u1d_graph* g /* host */, const void* w, cons
  * owns a fixed device arena, or a loop where an allocation's implicit synchronisation is not
  * acceptable.  Takes the receiver index itself (non-decreasing,
  * [n_edges]) and derives the CSR offsets and the per-CTA partition into an array built into the
- * module (about 1 MB, reserved on every GPU that loads the module, shared by all calls), then runs
- * the same kernel as fasteq_u1d_forward.  Limits: n_out_rows <= 262144 (else FASTEQ_UNSUPPORTED and
+ * module (about 1 MB PER MODULE, i.e. per operator signature, reserved on every GPU that loads the
+ * module, shared by all calls into it), then runs the same kernel as fasteq_u1d_forward.  Limits: n_out_rows <= 262144 (else FASTEQ_UNSUPPORTED and
  * fasteq_last_cuda_error() names the limit); scattered signatures with y not gathered; edges already
- * sorted by receiver.  Calls that overlap on the GPU race on the shared array -- serialise them.
- * The first call on each device resolves the array's device address; make it before any stream
- * capture.  Calls no cudaMalloc / cudaFree or other allocating routine. */
+ * sorted by receiver.  Calls that overlap on the GPU race on the shared array -- serialise them; a
+ * refused call launches nothing and cannot disturb a call in flight.  Receiver indices outside
+ * [0, n_out_rows) are not reported: such edges belong to no row and are left out (as with
+ * fasteq_graph_build_csr).  The first call on each device resolves the array's device address (safe
+ * from several host threads at once); make it before any stream capture.  Calls no cudaMalloc /
+ * cudaFree or other allocating routine. */
 int fasteq_u1d_forward_noalloc(const int32_t* dst_sorted, const int32_t* x_index, int64_t n_edges,
                                int64_t n_out_rows, int64_t x_rows, const void* w, const void* x, const void* y,
                                void* out, fasteq_stream_t stream);
@@ -168,13 +171,17 @@ int fasteq_core_abi_version(void);
 int fasteq_graph_check_sorted(const int32_t* dst, int64_t n_edges, int32_t* sorted_flag, fasteq_stream_t stream);
 
 /* CSR offsets of a non-decreasing receiver index: seg_ptr[r] = first position with dst >= r,
- * seg_ptr[n_rows] = n_edges.  The reference scatters with atomicAdd on the raw dst index
+ * seg_ptr[n_rows] = n_edges.  Receiver indices outside [0, n_rows) are not reported: edges with a negative
+ * index fall before row 0 and edges with an index >= n_rows after the last row, so no segment contains them
+ * and the operators silently leave them out (there is no status word for this; validate the index on the
+ * caller's side if it may be wrong).  The reference scatters with atomicAdd on the raw dst index
  * (fasteq/ops/auto_schedule/uniform1d_forward.py:351-356) and has no counterpart. */
 int fasteq_graph_build_csr(const int32_t* dst_sorted, int64_t n_edges, int64_t n_rows, int32_t* seg_ptr,
                            fasteq_stream_t stream);
 
-/* Split segments into n_parts contiguous ranges of about equal edge count:
- * part_ptr[p] = first segment whose start is >= p * n_edges / n_parts. */
+/* Split segments into n_parts contiguous ranges of about equal WORK, the work of a segment being its edge
+ * count plus one (a receiver without edges still costs a row store): part_ptr[p] = first segment s with
+ * seg_ptr[s] + s >= p * (n_edges + n_rows) / n_parts, part_ptr[n_parts] = n_rows. */
 int fasteq_graph_partition(const int32_t* seg_ptr, int64_t n_rows, int64_t n_edges, int32_t n_parts,
                            int32_t* part_ptr, fasteq_stream_t stream);
 
@@ -323,13 +330,18 @@ int fasteq_radial_chain_prepare(const float* const* w_hidden /* host */, int32_t
  * (the embedding of NequIP / MACE models, .../nequip/nn/embedding/_edge.py:174-189, cutoffs.py:17-27; the
  * reference leaves it to torch modules).  The backward takes dE/dvec and / or dE/dbasis (either may be NULL),
  * and overwrites grad_pos [n_nodes, 3] (accumulated with red.global.add over senders and receivers).
- * dtype: fasteq_dtype of pos / shift / vec / basis; n_basis <= 16. */
+ * dtype: fasteq_dtype of pos / shift / vec / basis; n_basis <= 16.  An edge whose sender or receiver index lies
+ * outside [0, n_nodes) is not followed: it gets zero features and no gradient, and the status word below reads 2
+ * (the tensor-product kernels treat the same index the same way).  A coincident pair (r = 0) gets the limit
+ * basis[e, n] = sqrt(2 / r_max) (n+1) pi / r_max and no gradient through the radial basis. */
 int fasteq_edge_geometry_forward(int32_t dtype, const void* pos, const int32_t* src, const int32_t* dst, const void* shift,
-                                 int64_t n_edges, double r_max, int32_t n_basis, int32_t envelope_p, void* vec, void* basis,
-                                 fasteq_stream_t stream);
+                                 int64_t n_edges, int64_t n_nodes, double r_max, int32_t n_basis, int32_t envelope_p, void* vec,
+                                 void* basis, fasteq_stream_t stream);
 int fasteq_edge_geometry_backward(int32_t dtype, const void* pos, const int32_t* src, const int32_t* dst, const void* shift,
                                   const void* grad_vec, const void* grad_basis, int64_t n_edges, int64_t n_nodes, double r_max,
                                   int32_t n_basis, int32_t envelope_p, void* grad_pos, fasteq_stream_t stream);
+/* Reads and clears the status word of the edge-geometry kernels (synchronises): 0, or 2 = an edge index was out of range. */
+int fasteq_edge_geometry_device_status(int32_t* code /* host */);
 /* Reads and clears the status word of the tensor-core kernels (synchronises). */
 int fasteq_tensorcore_device_status(int32_t* code /* host */);
 

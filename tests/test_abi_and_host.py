@@ -117,3 +117,22 @@ def test_op_rejects_cpu_tensors_without_a_gpu():
     with pytest.raises(RuntimeError, match="no CPU path"):
         fast_uniform1d_jit(torch.zeros(3, d.w_seg_num * 4), torch.zeros(2, 4), torch.zeros(3, 4), {1: torch.zeros(3, dtype=torch.int32)},
                            {0: torch.zeros(3, dtype=torch.int32)}, d.meta())
+
+
+def test_fixed_batch_of_benchmark_configuration_4_splits_evenly():
+    """1024 structures, 32..256 atoms each at density 0.1 / A^3; the whole-structure split over 1 / 2 / 4 / 8 ranks keeps
+    every structure exactly once and balances the estimated edge counts to a few per cent."""
+    import importlib.util
+    from fasteq_b200.graph import split_structures
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec); spec.loader.exec_module(bench)
+    atoms, side = bench.config4_structures()
+    assert atoms.shape == (1024,) and atoms.min() >= 32 and atoms.max() <= 256
+    np.testing.assert_allclose(atoms / side ** 3, 0.1, rtol=1e-12)
+    a2, _ = bench.config4_structures()
+    assert (a2 == atoms).all()                                   # the same batch at every world size
+    for world in (1, 2, 4, 8):
+        parts = split_structures(atoms * 52.0, world)
+        assert sorted(i for p in parts for i in p) == list(range(1024))
+        loads = np.array([atoms[p].sum() for p in parts], dtype=float)
+        assert loads.max() / loads.mean() < 1.02

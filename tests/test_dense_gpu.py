@@ -49,7 +49,7 @@ def test_dense_leading_dimensions_and_fallback_dtypes():
     g = torch.Generator().manual_seed(4)
     x = torch.randn(5, 31, 8, generator=g, dtype=torch.float64)
     w = torch.randn(64, 8, generator=g, dtype=torch.float64)
-    out = dense(x.cuda(), w.cuda())            # float64 goes through torch.matmul
+    out = dense(x.cuda(), w.cuda())            # float64: the FP64 FMA tile kernel of the SO3Linear family
     assert out.shape == (5, 31, 64) and _rel(out.cpu(), x @ w.t()) <= 1e-14
     out32 = dense(x.float().cuda(), w.float().cuda())
     assert out32.shape == (5, 31, 64) and _rel(out32.cpu(), x @ w.t()) <= 2e-6
@@ -72,3 +72,48 @@ def test_dense_second_order():
     got = second(dense, "cuda", torch.float32)
     for a, b in zip(got, ref):
         assert _rel(a, b) <= 1e-5
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 8), (777, 64, 64), (1500, 4352, 64), (300, 70, 33)])
+def test_float64_dense_runs_on_the_library_kernels(M, N, K, monkeypatch):
+    """FP64 (benchmark configuration 2's radial MLP): forward, both gradients and a second-order term on the FP64 FMA
+    kernels behind ``fasteq_eqlinear_forward / _dgrad / _wgrad`` -- no library GEMM: ``torch.matmul`` is made to fail
+    for CUDA operands while the layer runs."""
+    from fasteq_b200.ops import dense as dmod
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K, generator=g, dtype=torch.float64)
+    w = torch.randn(N, K, generator=g, dtype=torch.float64) / K ** 0.5
+    r = torch.randn(M, N, generator=g, dtype=torch.float64)
+    a = torch.randn(M, K, generator=g, dtype=torch.float64)
+
+    def run(fn, dev):
+        xt, wt = x.to(dev).requires_grad_(True), w.to(dev).requires_grad_(True)
+        out = fn(xt, wt)
+        gx, gw = torch.autograd.grad(out, (xt, wt), r.to(dev), create_graph=True)
+        (d2w,) = torch.autograd.grad((gx * a.to(dev)).sum(), wt)          # d/dW of <g W, a> = g^T a
+        return [t.detach().cpu() for t in (out, gx, gw, d2w)]
+
+    ref = run(lambda p, q: p @ q.t(), "cpu")
+    real = torch.Tensor.__matmul__
+
+    def guarded(self, other):
+        assert not (self.is_cuda or other.is_cuda), "a library GEMM was called on CUDA tensors"
+        return real(self, other)
+    monkeypatch.setattr(torch.Tensor, "__matmul__", guarded)
+    got = run(dmod.dense, "cuda")
+    monkeypatch.undo()
+    for p, q in zip(got, ref):
+        assert _rel(p, q) <= 1e-13
+
+
+def test_misaligned_float32_operand_takes_the_fma_kernel():
+    """An FP32 operand that is not 16-byte aligned is refused by the tensor-core kernel; the FP32 FMA kernel takes it."""
+    from fasteq_b200.ops.dense import dense
+    g = torch.Generator().manual_seed(5)
+    M, N, K = 500, 64, 64
+    buf = torch.randn(M * K + 1, generator=g).cuda()
+    x = buf[1:].view(M, K)                                  # contiguous, 4 bytes past a 16-byte boundary
+    assert x.data_ptr() % 16 == 4
+    w = (torch.randn(N, K, generator=g) / 8).cuda()
+    out = dense(x, w)
+    assert _rel(out.cpu(), x.cpu().double() @ w.cpu().double().t()) <= 2e-6

@@ -33,3 +33,30 @@ def test_edge_geometry_matches_torch(dtype, tol):
     (g3,) = torch.autograd.grad((edge_geometry(pt, src.int(), dst.int(), shift.to(dtype), 5.0, 8, 5)[1] * rb.to(dtype)).sum(), pt)
     (g3_ref,) = torch.autograd.grad((basis * rb).sum(), p64)
     assert rel(g3, g3_ref) <= tol * 8
+
+
+def test_out_of_range_indices_are_skipped_and_reported():
+    """An edge whose sender or receiver index lies outside the position array is not followed (no access through
+    it), gets zero features and no gradient, and leaves code 2 in the status word; a coincident pair (r = 0) gets the
+    finite limit of the basis and a finite (zero) radial gradient."""
+    import math
+    from fasteq_b200.ops.edge_geometry import edge_geometry, edge_geometry_device_status
+    edge_geometry_device_status()                     # clear
+    pos = torch.tensor([[0.0, 0.0, 0.0], [1.0, 0.5, 0.2], [0.3, 2.0, 1.0]], device="cuda", requires_grad=True)
+    src = torch.tensor([1, 7, 2, -1, 0], dtype=torch.int32, device="cuda")
+    dst = torch.tensor([0, 0, 9, 1, 0], dtype=torch.int32, device="cuda")      # edges 1, 2, 3 are bad; edge 4 is a coincident pair
+    shift = torch.zeros(5, 3, device="cuda")
+    vec, basis = edge_geometry(pos, src, dst, shift, 5.0, 8, 5)
+    (g,) = torch.autograd.grad(basis.sum() + vec.sum(), pos)
+    assert edge_geometry_device_status() == 2
+    assert edge_geometry_device_status() == 0         # reading clears it
+    assert torch.count_nonzero(vec[1:4]) == 0 and torch.count_nonzero(basis[1:4]) == 0
+    assert torch.isfinite(basis).all() and torch.isfinite(g).all()
+    want = torch.tensor([math.sqrt(2.0 / 5.0) * (n + 1) * math.pi / 5.0 for n in range(8)], device="cuda")
+    assert torch.allclose(basis[4], want, rtol=1e-6)
+    # the good edge alone gives the same result
+    p2 = pos.detach().clone().requires_grad_(True)
+    v1, b1 = edge_geometry(p2, src[:1], dst[:1], shift[:1], 5.0, 8, 5)
+    (g1,) = torch.autograd.grad(b1.sum() + v1.sum(), p2)
+    assert torch.equal(v1[0], vec[0]) and torch.equal(b1[0], basis[0])
+    assert torch.allclose(g, g1, rtol=1e-6, atol=1e-7)

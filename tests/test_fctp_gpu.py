@@ -70,3 +70,21 @@ def test_mace_skip_connection_shape(dtype, tol):
     rx, rw = torch.autograd.grad(ref, (xd, wd), r)
     assert float((gx.double() - rx).abs().max()) <= tol * float(rx.abs().max())
     assert float((gw.double() - rw).abs().max()) <= tol * float(rw.abs().max())
+
+
+def test_precomputed_species_groups_give_the_same_result():
+    """``meta["species_groups"]`` (computed once per structure) removes the per-call host synchronisation; the result
+    is bit-identical to the call that derives the groups itself."""
+    from fasteq_b200.ops.fctp import fast_fctp, fctp_species_groups
+    g = torch.Generator().manual_seed(6)
+    B, U, V, Wd, P, I = 300, 64, 5, 64, 2, 4
+    i_for_k, p_for_k, val = [0, 1, 2, 3], [0, 1, 1, 1], [0.3, 0.7, 0.7, 0.7]
+    x = torch.randn(B, I * U, generator=g).cuda()
+    w = (torch.randn(P * U * V * Wd, generator=g) / U ** 0.5).cuda()
+    y = torch.nn.functional.one_hot(torch.randint(0, V, (B,), generator=g), V).float().cuda()
+    meta = _meta(i_for_k, p_for_k, val, 1.0, P, U, V, Wd, I, torch.float32)
+    ref = fast_fctp(w, x, y, meta)
+    meta2 = dict(meta, species_groups=fctp_species_groups(y))
+    assert torch.equal(fast_fctp(w, x, y, meta2), ref)
+    with pytest.raises(ValueError):
+        fast_fctp(w, x, y[:-1], dict(meta, species_groups=meta2["species_groups"]))

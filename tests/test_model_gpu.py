@@ -30,6 +30,66 @@ def test_energy_and_forces_match_oracle(dtype, tol):
     assert f.sum(0).abs().max() <= 50 * tol * f.abs().max()
 
 
+def test_energy_and_forces_match_oracle_at_128_channels():
+    """The benchmark model's width (128 channels: the four-pipeline packed tensor-product kernels, the tcgen05 3xTF32
+    SO3Linear / radial GEMMs, the fused radial chain, in-kernel harmonics and fused edge geometry) on a small box,
+    FP32, against the float64 CPU oracle model."""
+    from fasteq_b200.graph import make_boxes
+    from fasteq_b200.nn.mace_style import MACEStyleModel
+    from oracle import mace_style_ref
+    torch.manual_seed(0)
+    batch = make_boxes(2, [40, 31], [8.0, 7.5], 4.0, 4, seed=9)
+    model = MACEStyleModel(num_species=4, channels=128, r_max=4.0, avg_num_neighbors=20.0)
+    pos = torch.from_numpy(batch.positions).float()
+    species = torch.from_numpy(batch.species)
+    src, dst = torch.from_numpy(batch.edge_src), torch.from_numpy(batch.edge_dst)
+    shift = torch.from_numpy(batch.edge_shift).float()
+    e_ref, f_ref = mace_style_ref.energy_and_forces(model, pos, species, src, dst, shift)
+    m = model.cuda()
+    out = m(pos.cuda(), species.cuda(), src.cuda(), dst.cuda(), shift.cuda())
+    e_err = float((out["energy"].cpu().double() - e_ref.sum()).abs() / e_ref.abs().sum())
+    f = out["forces"].cpu().double()
+    f_err = float((f - f_ref).abs().max() / f_ref.abs().max())
+    print(f"128-channel model, FP32: energy error {e_err:.2e} (relative to sum |e_atom|), force error {f_err:.2e}")
+    assert e_err <= 1e-5 and f_err <= 1e-5
+
+
+def test_cuda_graph_replay_survives_plan_cache_eviction():
+    """A captured step keeps reading its graph plan's CSR offsets and partitions.  The plan cache is a bounded LRU;
+    after more other graphs than it holds, the captured plan has left it, and only the graph object's own
+    references keep those buffers from being recycled."""
+    from fasteq_b200.graph import make_boxes
+    from fasteq_b200.nn.graphed import GraphedEnergyForces
+    from fasteq_b200.nn.mace_style import MACEStyleModel
+    from fasteq_b200.ops import uniform1d_jit as u1d
+    torch.manual_seed(0)
+    b = make_boxes(2, [20, 14], [7.0, 6.5], 3.5, 3, seed=5)
+    model = MACEStyleModel(num_species=3, channels=32, r_max=3.5, avg_num_neighbors=12.0).cuda()
+    for p in model.parameters():
+        p.requires_grad_(False)
+    t = lambda a, dt=None: torch.from_numpy(a).cuda() if dt is None else torch.from_numpy(a).to(dt).cuda()
+    pos = t(b.positions, torch.float32)
+    args = (t(b.species), t(b.edge_src), t(b.edge_dst), t(b.edge_shift, torch.float32), t(b.node_graph), b.n_graphs)
+    graphed = GraphedEnergyForces(model, pos, *args)
+    assert graphed._plans, "the capture must have recorded the plans it uses"
+    held = {id(p) for p in graphed._plans}
+    n = b.n_nodes
+    for k in range(u1d._PLAN_LIMIT + 8):            # more throw-away graphs than the cache holds
+        junk = torch.sort(torch.randint(0, n, (b.n_edges,), device="cuda")).values.int()
+        u1d.graph_plan(junk, n).partition(37)
+        del junk
+    assert not any(id(p) in held for p in u1d._PLANS.values()), "the captured plan should have been evicted"
+    # recycle whatever the allocator got back, with a pattern that would break the kernels
+    trash = [torch.full((b.n_edges + 64,), 0x7fffffff, dtype=torch.int32, device="cuda") for _ in range(64)]
+    p2 = pos + 0.01 * torch.randn(pos.shape, generator=torch.Generator().manual_seed(3)).cuda()
+    out = graphed(p2)
+    e, f = out["energy"].clone(), out["forces"].clone()
+    ref = model(p2, *args)
+    assert (e - ref["energy"]).abs().max() <= 1e-6 * ref["energy"].abs().max()
+    assert (f - ref["forces"]).abs().max() <= 1e-5 * ref["forces"].abs().max()
+    del trash
+
+
 def test_cuda_graph_replay_matches_eager():
     """A captured energy + forces step replayed with new positions equals the eager evaluation."""
     from fasteq_b200.graph import make_boxes

@@ -84,7 +84,8 @@ def test_config0_forward_backward(dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 def test_mace_layer_signature(dtype):
-    """128x0e+128x1o (x) SH l<=3 -> l<=3 (13 weight segments), receivers with no edges, unsorted dst."""
+    """64x0e+64x1o (x) SH l<=3 -> l<=3 (13 weight segments, 64-channel tiles), receivers with no edges, unsorted dst.
+    The 128-channel layouts of the same couplings are covered by tests/test_u1d_wide_gpu.py."""
     d, paths = _tp("64x0e+64x1o", 3, 3)
     _run_case(lambda dt: d.meta(dt, "cuda"), paths, d.coeff_list, (d.w_seg_num, d.x_seg_num, d.y_seg_num, d.out_seg_num),
               64, 300, 700, dtype, sort=False, seed=3)

@@ -52,6 +52,57 @@ def test_noalloc_forward_matches_regular_entry_point_twice():
         assert mod.device_status() == 0
 
 
+def _both(d, src, dst, w, x, y, n_nodes):
+    """(regular entry point through the public operator, allocation-free entry point) on the same inputs."""
+    from fasteq_b200.ops import fast_uniform1d_jit
+    from fasteq_b200.ops import uniform1d_jit as u1d
+    meta = d.meta(torch.float32, "cuda")
+    ref = fast_uniform1d_jit(w, x, y, {1: src}, {0: dst}, meta)
+    call = u1d._Call(w, x, y, {1: src}, {0: dst}, meta)
+    mod = u1d.get_module(call.spec, "fwd", tuning=u1d._tuning_for(call.spec, "fwd", (w, x, y)))
+    out = torch.full_like(ref, float("nan"))
+    nz = lambda t: t.data_ptr() if t.numel() else None
+    rc = mod.forward_noalloc(nz(dst), nz(src), int(dst.numel()), n_nodes, n_nodes, nz(w), x.data_ptr(), nz(y), out.data_ptr(),
+                             torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, mod.last_error()
+    torch.cuda.synchronize()
+    assert mod.device_status() == 0
+    return ref, out
+
+
+def test_noalloc_forward_with_empty_receivers_and_without_edges():
+    """Receivers without edges in the middle and at both ends of the range, then a call with no edge at all
+    (every row is written as zeros); each against the regular entry point."""
+    n_nodes = 90
+    d, src, dst, w, x, y = _case(n_nodes, 1200, 5)
+    keep = (dst >= 7) & (dst < 71) & (dst % 5 != 0)          # rows 0-6, 71-89 and every fifth row stay empty
+    src, dst, w, y = src[keep].contiguous(), dst[keep].contiguous(), w[keep].contiguous(), y[keep].contiguous()
+    ref, out = _both(d, src, dst, w, x, y, n_nodes)
+    assert (out - ref).abs().max().item() <= TOL * ref.abs().max().item()
+    assert torch.count_nonzero(out[71:]) == 0 and torch.count_nonzero(out[:7]) == 0 and torch.count_nonzero(out[10]) == 0
+    ref0, out0 = _both(d, src[:0], dst[:0], w[:0], x, y[:0], n_nodes)
+    assert torch.count_nonzero(ref0) == 0 and torch.count_nonzero(out0) == 0 and not torch.isnan(out0).any()
+
+
+def test_noalloc_forward_with_a_channel_tail():
+    """33 channels: the last channel tile is partial (U is not a multiple of the tile)."""
+    from fasteq_b200.descriptors import channelwise_tensor_product, full_channelwise_instructions
+    from fasteq_b200.irreps import Irreps
+    in1, sh = "33x0e+33x1o", Irreps.spherical_harmonics(2)
+    io, ins = full_channelwise_instructions(in1, sh, 2)
+    d = channelwise_tensor_product(in1, sh, io, ins)
+    g = torch.Generator().manual_seed(8)
+    n_nodes, n_edges = 40, 500
+    src = torch.randint(0, n_nodes, (n_edges,), generator=g)
+    dst, order = torch.sort(torch.randint(0, n_nodes, (n_edges,), generator=g), stable=True)
+    src = src[order].int().cuda()
+    w = torch.randn(n_edges, d.w_seg_num * 33, generator=g).cuda()
+    x = torch.randn(n_nodes, d.x_seg_num * 33, generator=g).cuda()
+    y = torch.randn(n_edges, d.y_seg_num, generator=g).cuda()
+    ref, out = _both(d, src, dst.int().cuda(), w, x, y, n_nodes)
+    assert (out - ref).abs().max().item() <= TOL * ref.abs().max().item()
+
+
 def test_noalloc_forward_refuses_oversized_graphs():
     from fasteq_b200.ops import uniform1d_jit as u1d
     d, src, dst, w, x, y = _case(16, 40, 3)
