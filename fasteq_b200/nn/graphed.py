@@ -6,7 +6,9 @@ backward, a few hundred kernel launches) into a CUDA graph and replays it, so th
 cost is one copy of the positions and one graph launch instead of the Python / launch overhead of
 every operator.  Capture needs the operator plans and generated modules to exist already, which the
 warm-up evaluations ensure.  The model's weights are taken as frozen for the life of the graph: the
-prepared (TF32-split) weight forms cached during the warm-up are captured as they are.
+prepared (TF32-split) weight forms cached during the warm-up are captured as they are.  Collectives a ``halo=``
+exchange makes (NCCL) are captured with the kernels; the capture uses the thread-local error mode so that the
+process group's watchdog thread may keep polling its events meanwhile.
 """
 from __future__ import annotations
 
@@ -33,7 +35,7 @@ class GraphedEnergyForces:
         torch.cuda.current_stream(pos.device).wait_stream(side)
         torch.cuda.synchronize(pos.device)
         self.graph = torch.cuda.CUDAGraph()
-        with _prepared.frozen_weights(), _u1d.record_plans() as plans, torch.cuda.graph(self.graph):
+        with _prepared.frozen_weights(), _u1d.record_plans() as plans, torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
             self.static_out = model(self.static_pos, *static_args, **static_kwargs)
         self._prepared = _prepared.snapshot()      # the captured kernels read these buffers
         # ... and the CSR offsets / permutations / partitions of these plans: the plan cache is a bounded LRU

@@ -80,9 +80,14 @@ class InteractionLayer(torch.nn.Module):
     def forward(self, h, species, edge_sh, edge_radial, edge_dst, edge_src, halo=None, edge_vec=None):
         up = self.linear_up(h)
         n_owned = up.shape[0]
-        if halo is not None:
-            up = halo(up)                    # owned rows, then ghost rows of the senders other ranks own
-        w = self.radial(edge_radial)
+        begin = getattr(halo, "begin", None)
+        if begin is not None:
+            up = begin(up)                   # owned rows, then ghost rows of the senders other ranks own (exchange in flight)
+        elif halo is not None:
+            up = halo(up)
+        w = self.radial(edge_radial)         # edge-local work behind the exchange
+        if begin is not None:
+            up = halo.end(up)
         # edge_vec given: the tensor-product kernel evaluates the spherical harmonics of the edge itself
         msg = self.conv_tp(up, edge_sh, w, edge_dst, edge_src, edge_vec=edge_vec)
         if msg.shape[0] != n_owned:

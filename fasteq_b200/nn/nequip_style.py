@@ -49,12 +49,19 @@ class NequIPStyleLayer(torch.nn.Module):
     def forward(self, h, edge_sh, edge_radial, edge_dst, edge_src, halo=None, edge_vec=None):
         up = self.linear_1(h)
         n_owned = up.shape[0]
-        if halo is not None:
+        begin = getattr(halo, "begin", None)
+        if begin is not None:
+            up = begin(up)                       # ghost exchange in flight ...
+        elif halo is not None:
             up = halo(up)
-        msg = self.conv_tp(up, edge_sh, self.radial(edge_radial), edge_dst, edge_src, edge_vec=edge_vec)
+        w = self.radial(edge_radial)             # ... behind the edge-local radial MLP and the node-local self-connection
+        sc = self.self_connection(h)
+        if begin is not None:
+            up = halo.end(up)
+        msg = self.conv_tp(up, edge_sh, w, edge_dst, edge_src, edge_vec=edge_vec)
         if msg.shape[0] != n_owned:
             msg = msg[:n_owned]
-        pre = self.linear_2(msg) + self.self_connection(h)      # 1 / <neighbours> is folded into linear_2's coefficients
+        pre = self.linear_2(msg) + sc            # 1 / <neighbours> is folded into linear_2's coefficients
         return gate(pre, self.gate_spec)
 
 

@@ -7,11 +7,13 @@ packages rely on an MD engine's ghost exchange, …/nequip/nn/_ghost_exchange_lm
   communication in the layer loop;
 * one large graph: ``partition_by_receiver_range`` gives every rank a contiguous range of nodes and
   all edges whose receiver is in that range, so the scatter-sum is rank-local.  Senders outside the
-  range are *ghosts*: before each interaction ``HaloExchange`` all-gathers the rows other ranks need
-  (padded export slabs, data lands in local memory before any kernel reads it) and appends the
-  ghost rows to the local ones; its backward sums the ghost gradients back onto their owners
-  (reduce-scatter).  Positions go through the same exchange, so forces on owned atoms include the
-  contributions of edges owned by other ranks.
+  range are *ghosts*: before each interaction ``HaloExchange`` sends every peer exactly the owned rows
+  that peer reads (one variable-size all-to-all: a slab partition has two neighbours, and only they
+  get data; it lands in local memory before any kernel reads it) and appends the received ghost rows
+  to the local ones; its backward sends the ghost gradients back the same way and adds them onto
+  their owners.  Positions go through the same exchange, so forces on owned atoms include the
+  contributions of edges owned by other ranks.  (``mode="gather"`` keeps the earlier form: padded
+  export slabs all-gathered to every rank, reduce-scatter in the backward.)
 """
 from __future__ import annotations
 
@@ -38,6 +40,9 @@ class LocalGraph:
     export_local: np.ndarray          # [X] owned rows (local ids) this rank exports, sorted
     max_export: int                   # slab rows per rank (max over ranks)
     ghost_slot: np.ndarray            # [G] position of each ghost in the gathered [world * max_export] slab
+    send_idx: np.ndarray = None       # [sum(send_counts)] owned rows (local ids) to send, grouped by receiving rank
+    send_counts: tuple = ()           # rows sent to each rank
+    recv_counts: tuple = ()           # ghost rows received from each rank; in rank order they ARE the ghosts in order
 
     @property
     def n_owned(self) -> int:
@@ -86,13 +91,21 @@ def partition_by_receiver_range(n_nodes: int, edge_src: np.ndarray, edge_dst: np
         for k, g in enumerate(e):
             slot_of[int(g)] = r * max_export + k
     out = []
+    # per-peer tables: ghosts are sorted by global id and ownership ranges are contiguous, so a rank's ghosts are
+    # already grouped by owner in rank order; owner q sends rank r the rows r's ghost list names, in that order
+    need = [[ghosts[owner[ghosts] == q] if len(ghosts) else ghosts for q in range(world)] for (_, _, _, _, _, ghosts) in per_rank]
     for r, (lo, hi, ids, src, dst, ghosts) in enumerate(per_rank):
         n_owned = hi - lo
-        ghost_local = {int(g): n_owned + k for k, g in enumerate(ghosts)}
-        src_local = np.array([s - lo if lo <= s < hi else ghost_local[int(s)] for s in src], dtype=np.int64)
+        ghost_pos = np.searchsorted(ghosts, src)
+        ghost_pos = np.minimum(ghost_pos, max(len(ghosts) - 1, 0))
+        inside = (src >= lo) & (src < hi)
+        src_local = np.where(inside, src - lo, n_owned + ghost_pos).astype(np.int64)
+        send = [need[q][r] - lo for q in range(world)]                    # what every rank q reads of r's rows
         out.append(LocalGraph(r, world, lo, hi, ghosts.astype(np.int64), src_local, (dst - lo).astype(np.int64), ids.astype(np.int64),
                               (exports[r] - lo).astype(np.int64), max_export,
-                              np.array([slot_of[int(g)] for g in ghosts], dtype=np.int64)))
+                              np.array([slot_of[int(g)] for g in ghosts], dtype=np.int64),
+                              np.concatenate(send).astype(np.int64) if world else np.zeros(0, np.int64),
+                              tuple(int(len(t)) for t in send), tuple(int(len(need[r][q])) for q in range(world))))
     return out
 
 
@@ -126,19 +139,77 @@ class _Halo(torch.autograd.Function):
         return gx, None, None, None, None
 
 
-class HaloExchange:
-    """``ext = halo(x_owned)``: owned rows followed by ghost rows, differentiable."""
+class _HaloA2A(torch.autograd.Function):
+    """Neighbour-only exchange: ``out = [x ; rows received]`` with one variable-size all-to-all.  The received rows,
+    taken in rank order, are the ghost rows in local order, so nothing is re-indexed on arrival.  With ``defer`` the
+    collective is left in flight and its handle is parked in ``pending``: the caller does node-local work and then
+    calls ``HaloExchange.end`` before the first use of the ghost rows."""
 
-    def __init__(self, local: LocalGraph, device, group=None):
-        self.local = local
+    @staticmethod
+    def forward(ctx, x, send_idx, send_counts, recv_counts, group, pending):
+        n_owned, n_ghost = x.shape[0], int(sum(recv_counts))
+        out = x.new_empty((n_owned + n_ghost,) + x.shape[1:])
+        out[:n_owned] = x
+        send = x.index_select(0, send_idx) if send_idx.numel() else x.new_empty((0,) + x.shape[1:])
+        work = dist.all_to_all_single(out[n_owned:], send, list(recv_counts), list(send_counts), group=group,
+                                      async_op=pending is not None)
+        if pending is not None:
+            pending.append((work, send))         # keeps the send buffer alive until the wait
+        ctx.save_for_backward(send_idx)
+        ctx.meta = (send_counts, recv_counts, group, n_owned)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        (send_idx,) = ctx.saved_tensors
+        send_counts, recv_counts, group, n_owned = ctx.meta
+        ghost_grad = grad[n_owned:].contiguous()
+        back = grad.new_empty((int(sum(send_counts)),) + grad.shape[1:])
+        dist.all_to_all_single(back, ghost_grad, list(send_counts), list(recv_counts), group=group)
+        gx = grad[:n_owned].clone()
+        if send_idx.numel():
+            gx.index_add_(0, send_idx, back)
+        return gx, None, None, None, None, None
+
+
+class HaloExchange:
+    """``ext = halo(x_owned)``: owned rows followed by ghost rows, differentiable.
+
+    ``begin`` / ``end`` split the call so that node-local work can run behind the exchange::
+
+        t = halo.begin(x_owned)        # pack + start the all-to-all
+        y = node_local_work(h)         # e.g. the self-connection, independent of the ghost rows
+        ext = halo.end(t)              # wait; ghost rows are valid from here on
+    """
+
+    def __init__(self, local: LocalGraph, device, group=None, mode: str = "alltoall"):
+        if mode not in ("alltoall", "gather"):
+            raise ValueError("mode must be 'alltoall' or 'gather'")
+        self.local, self.mode = local, mode
         self.export_idx = torch.as_tensor(local.export_local, device=device)
         self.ghost_slot = torch.as_tensor(local.ghost_slot, device=device)
+        self.send_idx = torch.as_tensor(local.send_idx if local.send_idx is not None else np.zeros(0, np.int64), device=device)
         self.group = group
+        self._pending: list = []
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         if self.local.world == 1:
             return x
-        return _Halo.apply(x, self.export_idx, self.ghost_slot, self.local.max_export, self.group)
+        if self.mode == "gather":
+            return _Halo.apply(x, self.export_idx, self.ghost_slot, self.local.max_export, self.group)
+        return _HaloA2A.apply(x, self.send_idx, self.local.send_counts, self.local.recv_counts, self.group, None)
+
+    def begin(self, x: torch.Tensor) -> torch.Tensor:
+        if self.local.world == 1 or self.mode == "gather" or (x.is_cuda and torch.cuda.is_current_stream_capturing()):
+            return self(x)
+        return _HaloA2A.apply(x, self.send_idx, self.local.send_counts, self.local.recv_counts, self.group, self._pending)
+
+    def end(self, ext: torch.Tensor) -> torch.Tensor:
+        while self._pending:
+            work, _ = self._pending.pop()
+            if work is not None:
+                work.wait()
+        return ext
 
 
 class _EngineExchange(torch.autograd.Function):
@@ -184,3 +255,9 @@ class EngineGhostExchange:
         if int(self.engine.ntotal) == int(self.engine.nlocal):
             return x
         return _EngineExchange.apply(x, self.engine)
+
+    # an engine's exchange is synchronous: begin does the whole call
+    begin = __call__
+
+    def end(self, ext: torch.Tensor) -> torch.Tensor:
+        return ext

@@ -17,7 +17,7 @@ def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
 
 
-def _toy_energy(pos_owned, feat_owned, src, dst, shift, w1, w2, halo, n_layers=2):
+def _toy_energy(pos_owned, feat_owned, src, dst, shift, w1, w2, halo, n_layers=2, split=False):
     """Two rounds of h_i <- tanh(W h_i) + sum_j exp(-|r_ij|) * (W h_j); E_i = sum(h_i^2)."""
     pos_ext = halo(pos_owned) if halo is not None else pos_owned
     vec = pos_ext[src] + shift - pos_ext[dst]
@@ -26,7 +26,12 @@ def _toy_energy(pos_owned, feat_owned, src, dst, shift, w1, w2, halo, n_layers=2
     n = pos_owned.shape[0]
     for w in (w1, w2)[:n_layers]:
         up = h @ w
-        ext = halo(up) if halo is not None else up
+        if halo is not None and split:       # node-local work between begin and end
+            t = halo.begin(up)
+            _ = torch.tanh(up)
+            ext = halo.end(t)
+        else:
+            ext = halo(up) if halo is not None else up
         msg = torch.zeros(n, up.shape[1], dtype=up.dtype).index_add(0, dst, torch.exp(-r) * ext[src])
         h = torch.tanh(up) + msg
     return (h * h).sum(dim=1)
@@ -43,7 +48,7 @@ def _problem():
     return b, feat, w1, w2
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, mode="alltoall"):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -51,18 +56,19 @@ def _worker(rank, world, port, q):
     b, feat, w1, w2 = _problem()
     parts = partition_by_receiver_range(b.n_nodes, b.edge_src, b.edge_dst, world)
     lg = parts[rank]
-    halo = HaloExchange(lg, "cpu")
+    halo = HaloExchange(lg, "cpu", mode="gather" if mode == "gather" else "alltoall")
     pos = torch.from_numpy(b.positions[lg.start:lg.stop]).requires_grad_(True)
     shift = torch.from_numpy(b.edge_shift[lg.edge_ids])
-    e = _toy_energy(pos, feat[lg.start:lg.stop], torch.from_numpy(lg.edge_src), torch.from_numpy(lg.edge_dst), shift, w1, w2, halo)
+    e = _toy_energy(pos, feat[lg.start:lg.stop], torch.from_numpy(lg.edge_src), torch.from_numpy(lg.edge_dst), shift, w1, w2, halo,
+                    split=mode == "split")
     (g,) = torch.autograd.grad(e.sum(), pos)
     q.put((rank, lg.start, lg.stop, e.detach().numpy(), g.numpy(), len(lg.ghost_global), int(len(lg.edge_ids))))
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_partitioned_energy_and_forces_match_single_process(world):
+@pytest.mark.parametrize("world,mode", [(2, "alltoall"), (3, "alltoall"), (3, "split"), (2, "gather")])
+def test_partitioned_energy_and_forces_match_single_process(world, mode):
     b, feat, w1, w2 = _problem()
     pos = torch.from_numpy(b.positions).requires_grad_(True)
     e_ref = _toy_energy(pos, feat, torch.from_numpy(b.edge_src), torch.from_numpy(b.edge_dst), torch.from_numpy(b.edge_shift), w1, w2, None)
@@ -70,7 +76,7 @@ def test_partitioned_energy_and_forces_match_single_process(world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, mode)) for r in range(world)]
     for p in procs:
         p.start()
     got = [q.get(timeout=180) for _ in range(world)]
@@ -98,6 +104,14 @@ def test_partition_tables_are_consistent():
     for p in parts:
         assert (np.diff(p.edge_dst) >= 0).all() and p.edge_dst.max() < p.n_owned
         assert p.edge_src.max() < p.n_local
+        # per-peer tables of the neighbour-only exchange: what r sends q is what q expects from r, nothing to itself,
+        # and the rows q receives, taken in rank order, are its ghosts in order
+        assert p.send_counts[p.rank] == 0 and p.recv_counts[p.rank] == 0
+        assert sum(p.recv_counts) == len(p.ghost_global) and sum(p.send_counts) == len(p.send_idx)
+        for q in parts:
+            assert p.send_counts[q.rank] == q.recv_counts[p.rank]
+        got = np.concatenate([q.start + q.send_idx[sum(q.send_counts[:p.rank]):sum(q.send_counts[:p.rank + 1])] for q in parts])
+        assert (got == p.ghost_global).all()
         # a ghost's slot points into its owner's slab
         for g, slot in zip(p.ghost_global, p.ghost_slot):
             owner = slot // p.max_export
