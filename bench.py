@@ -244,8 +244,9 @@ def halo_model_bench(args, dev, rank, world, dist):
             "config": "config 3: 4 gated layers, 64x0e+64x0o+64x1e+64x1o+64x2e+64x2o, SH l<=2, cutoff 4 A, FP32"}
 
 
-def model_bench(args, dev, rank, dist, n_boxes: int):
-    """Energy + forces of the synthetic MACE-style model of benchmark configuration 1 (FP32): atom-steps/s."""
+def model_bench(args, dev, rank, dist, n_boxes: int, quick: bool = False):
+    """Energy + forces of the synthetic MACE-style model of benchmark configuration 1 (FP32): atom-steps/s.
+    ``quick``: the eager steps only (no graph replay, no end-to-end legs), for profiling."""
     from fasteq_b200.nn.mace_style import MACEStyleModel
     torch.manual_seed(0)
     model = MACEStyleModel().to(dev)
@@ -270,6 +271,9 @@ def model_bench(args, dev, rank, dist, n_boxes: int):
     if dist is not None:
         tm = t.clone(); dist.all_reduce(tm, op=dist.ReduceOp.MAX); ms = float(tm[0])
         ts = t.clone(); dist.all_reduce(ts, op=dist.ReduceOp.SUM); atoms = float(ts[1])
+    if quick:
+        return {"metric": "MACE atom-steps/s (energy + forces)", "value": atoms * k / (ms * 1e-3), "unit": "atom-steps/s",
+                "ms_per_step": ms / k, "steps": k, "atoms": int(atoms), "edges_per_gpu": b.n_edges}
     # the same evaluation replayed from a CUDA graph (fixed neighbour list, new positions each step)
     graphed_ms = None
     try:
@@ -700,6 +704,8 @@ def main():
     ap.add_argument("--no-model", action="store_true")
     ap.add_argument("--no-halo", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the fixed batch of 1024 structures (configuration 4)")
+    ap.add_argument("--only", default=None, choices=["operators", "other_signature", "config2", "fixed_batch", "single_graph", "model"],
+                    help="run one of the side blocks alone and print its JSON (for profiling a block under ncu)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -721,6 +727,19 @@ def main():
     from fasteq_b200.ops import fast_uniform1d_jit
     from fasteq_b200.ops import uniform1d_jit as u1d
     from fasteq_b200.sh import spherical_harmonics_host
+
+    if args.only:
+        block = {"operators": lambda: operator_extras(args, dev),
+                 "other_signature": lambda: cwtp_kernel_block("config0_layout_cwtp" if args.workload == "config1_cwtp" else "config1_cwtp", dev),
+                 "config2": lambda: config2_bench(dev),
+                 "model": lambda: model_bench(args, dev, rank, dist, args.boxes or WORKLOADS[args.workload][3], quick=True),
+                 "fixed_batch": lambda: config4_sweep(args, dev, rank, world, dist),
+                 "single_graph": lambda: halo_model_bench(args, dev, rank, world, dist)}[args.only]()
+        if rank == 0:
+            print(json.dumps({"only": args.only, "n_gpus": world, "result": block}), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
 
     inp = build_inputs(args.workload, seed=rank, n_boxes=args.boxes)
     d, N, E, dtype = inp["d"], inp["N"], inp["E"], inp["dtype"]

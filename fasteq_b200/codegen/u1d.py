@@ -21,7 +21,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Tuple
 
-from .u1d_common import U1DSpec, Block, build_blocks, lit, split_out_segments
+from .u1d_common import U1DSpec, Block, build_blocks, lit, restrict_blocks, split_out_segments, split_w_segments
 from .sh import SH_DEVICE_STUB, emit_sh_device
 
 
@@ -552,12 +552,18 @@ def emit_backward(spec: U1DSpec, tun: Tuning, need_gw: bool, need_gx: bool, need
     with warp shuffles, then across warps by the producer warp when the stage is recycled.
     """
     _check_tuning(spec, tun)
-    if tun.groups != 1:
-        raise ValueError("the backward kernel uses one thread group")
+    G = tun.groups
+    if G not in (1, 2):
+        raise ValueError("the backward kernel takes one or two thread groups")
+    if G == 2 and (spec.w_shared or spec.y_vec or spec.y_indexed or not spec.x_indexed):
+        # two groups split the (weight segment, output segment) terms of one edge: each owns its grad_w rows, both add
+        # into grad_x (red.global.add) and into the per-warp partial sums of the scalar grad_y
+        raise ValueError("two backward thread groups need per-edge weights, a gathered x and a per-edge scalar y")
     blocks = build_blocks(spec)
+    owners = split_w_segments(blocks, spec.w_segs, G)          # weight segments each thread group differentiates
     tpg = tun.ct // tun.vec
-    ncons_warps = tpg // 32
-    threads = tun.pipes * (tpg + 32)
+    ncons_warps = G * tpg // 32
+    threads = tun.pipes * (G * tpg + 32)
     scalar_gy = need_gy and not spec.y_vec
     extra = ncons_warps * spec.y_segs * spec.elem_bytes if scalar_gy else 0
     extra = (extra + 15) // 16 * 16
@@ -652,7 +658,8 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
     p.run(flush, begin);
     return;
   }}
-  const int ch = (threadIdx.x - pipe * cfg::NCONS_WARPS * 32) * VEC;
+  const int ptid = threadIdx.x - pipe * cfg::NCONS_WARPS * 32;   // thread index inside the pipeline
+  const int grp = ptid / TPG, ch = (ptid % TPG) * VEC; (void)grp;
   uint32_t it = 0, nseg = 0;
 """)
     L: List[str] = []
@@ -701,12 +708,9 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
         L += [f"      V gx{j} = VS::zero();" for j in range(spec.x_segs)]
     if need_gy and spec.y_vec:
         L += [f"      V gy{k} = VS::zero();" for k in range(spec.y_segs)]
-    last_block_of_i: Dict[int, int] = {}
-    for bi, b in enumerate(blocks):
-        for t in b.terms:
-            last_block_of_i[t.i] = bi
+    used_i = sorted({t.i for b in blocks for t in b.terms})
     if need_gw:
-        L += [f"      V gw{i} = VS::zero();" for i in sorted(last_block_of_i)]
+        L += [f"      V gw{i} = VS::zero();" for i in used_i]
         if not spec.w_shared:
             L.append("      T* gwp = gw + (size_t)m.e * WSEG * U + (size_t)m.ct * CT + ch;")
     need_q = need_gx or need_gy
@@ -760,46 +764,57 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
             out.append(f"{ind}}}")
         return out
 
-    for bi, b in enumerate(blocks):
-        if _is_diagonal(b.terms):
-            L.append("      {"); L += diag_part(b, "        "); L.append("      }")
-        elif tun.two_pass or not (need_gw and need_q):
-            if need_gw:
-                L.append("      {"); L += gw_part(b, "        "); L.append("      }")
-            if need_q:
-                L.append("      {"); L += q_part(b, "        "); L.append("      }")
-        else:
-            # single pass: products and their gradients live together, grad_out / weight read once
-            L.append("      {")
-            L += [f"        const V p_{j}_{k} = vmul(x{j}, y{k});" for (j, k) in b.products]
-            L += [f"        V q_{j}_{k};" for (j, k) in b.products]
-            first_use = set()
+    for gi in range(G):
+        gblocks = blocks if G == 1 else restrict_blocks(blocks, owners[gi])
+        last_block_of_i: Dict[int, int] = {}
+        for bi, b in enumerate(gblocks):
             for t in b.terms:
-                L.append(f"        {{ const V gv = GO({t.v});")
-                L.append("          " + " ".join(_sum_expr(t.items, dt)) + f" gw{t.i} = vfma(gv, t, gw{t.i});")
-                L.append(f"          const V gp = vmul(W({t.i}), gv);")
-                for j, k, c in t.items:
-                    if (j, k) in first_use:
-                        L.append(f"          q_{j}_{k} = vfma({_vlit(c, dt)}, gp, q_{j}_{k});")
+                last_block_of_i[t.i] = bi
+        if G > 1:
+            L.append(f"      if (grp == {gi}) {{")
+        for bi, b in enumerate(gblocks):
+            if _is_diagonal(b.terms):
+                L.append("      {"); L += diag_part(b, "        "); L.append("      }")
+            elif tun.two_pass or not (need_gw and need_q):
+                if need_gw:
+                    L.append("      {"); L += gw_part(b, "        "); L.append("      }")
+                if need_q:
+                    L.append("      {"); L += q_part(b, "        "); L.append("      }")
+            else:
+                # single pass: products and their gradients live together, grad_out / weight read once
+                L.append("      {")
+                L += [f"        const V p_{j}_{k} = vmul(x{j}, y{k});" for (j, k) in b.products]
+                L += [f"        V q_{j}_{k};" for (j, k) in b.products]
+                first_use = set()
+                for t in b.terms:
+                    L.append(f"        {{ const V gv = GO({t.v});")
+                    L.append("          " + " ".join(_sum_expr(t.items, dt)) + f" gw{t.i} = vfma(gv, t, gw{t.i});")
+                    L.append(f"          const V gp = vmul(W({t.i}), gv);")
+                    for j, k, c in t.items:
+                        if (j, k) in first_use:
+                            L.append(f"          q_{j}_{k} = vfma({_vlit(c, dt)}, gp, q_{j}_{k});")
+                        else:
+                            first_use.add((j, k))
+                            L.append(f"          q_{j}_{k} = vmul({_vlit(c, dt)}, gp);")
+                    L.append("        }")
+                if need_gx:
+                    L += [f"        gx{j} = vfma(q_{j}_{k}, y{k}, gx{j});" for (j, k) in b.products]
+                if need_gy:
+                    L += [f"        gy{k} = vfma(q_{j}_{k}, x{j}, gy{k});" for (j, k) in b.products]
+                L.append("      }")
+            if need_gw:
+                for i in sorted(i for i, last in last_block_of_i.items() if last == bi):
+                    if spec.w_shared:
+                        L.append(f"      gws[{i}] = vadd(gws[{i}], gw{i});")
                     else:
-                        first_use.add((j, k))
-                        L.append(f"          q_{j}_{k} = vmul({_vlit(c, dt)}, gp);")
-                L.append("        }")
-            if need_gx:
-                L += [f"        gx{j} = vfma(q_{j}_{k}, y{k}, gx{j});" for (j, k) in b.products]
-            if need_gy:
-                L += [f"        gy{k} = vfma(q_{j}_{k}, x{j}, gy{k});" for (j, k) in b.products]
+                        L.append(f"      VS::st(gwp + {i} * U, gw{i});")
+        if need_gw and not spec.w_shared:
+            # weight segments no path touches get a zero gradient (written by the group that owns them)
+            for i in (range(spec.w_segs) if G == 1 else owners[gi]):
+                if i not in last_block_of_i:
+                    L.append(f"      VS::st(gwp + {i} * U, VS::zero());")
+        if G > 1:
             L.append("      }")
-        if need_gw:
-            for i in sorted(i for i, last in last_block_of_i.items() if last == bi):
-                if spec.w_shared:
-                    L.append(f"      gws[{i}] = vadd(gws[{i}], gw{i});")
-                else:
-                    L.append(f"      VS::st(gwp + {i} * U, gw{i});")
-    if need_gw and not spec.w_shared:
-        for i in range(spec.w_segs):
-            if i not in last_block_of_i:
-                L.append(f"      VS::st(gwp + {i} * U, VS::zero());")
     if need_gx:
         L.append("      T* gxp = gx + (size_t)m.xr * XSEG * U + (size_t)m.ct * CT + ch;")
         for j in range(spec.x_segs):

@@ -166,3 +166,36 @@ def split_out_segments(blocks: List[Block], out_segs: int, groups: int) -> List[
         owner[g].append(v)
         run += cost[v]
     return [sorted(o) for o in owner]
+
+
+def split_w_segments(blocks: List[Block], w_segs: int, groups: int) -> List[List[int]]:
+    """Partition weight segments over ``groups`` thread groups with balanced work (the backward's split: a group owns
+    the grad_w rows of its weight segments outright, so no two groups ever store the same row).  Segments are ordered
+    by the block that first uses them and cut into contiguous ranges of about equal cost."""
+    cost = [0] * w_segs
+    first = [len(blocks)] * w_segs
+    for bi, b in enumerate(blocks):
+        for t in b.terms:
+            cost[t.i] += 2 * len(t.items) + 2
+            first[t.i] = min(first[t.i], bi)
+    order = sorted(range(w_segs), key=lambda i: (first[i], i))
+    total = sum(cost)
+    owner: List[List[int]] = [[] for _ in range(groups)]
+    run, g = 0, 0
+    for i in order:
+        if g < groups - 1 and run >= total * (g + 1) / groups:
+            g += 1
+        owner[g].append(i)
+        run += cost[i]
+    return [sorted(o) for o in owner]
+
+
+def restrict_blocks(blocks: List[Block], w_owned) -> List[Block]:
+    """The blocks reduced to the terms of the weight segments in ``w_owned`` (products no term uses are dropped)."""
+    w_owned = set(w_owned)
+    out = []
+    for b in blocks:
+        ts = [t for t in b.terms if t.i in w_owned]
+        if ts:
+            out.append(Block(ts, sorted({(j, k) for t in ts for j, k, _ in t.items})))
+    return out

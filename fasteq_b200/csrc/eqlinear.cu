@@ -265,16 +265,38 @@ __global__ void __launch_bounds__(NT) eqlinear_wide_f64_kernel(const __grid_cons
   }
 }
 
-// rows of C that no group writes must read as zero
+// Rows of C that no group writes must read as zero.  The uncovered rows form at most n_groups + 1 runs; every
+// (batch entry, run) is one contiguous span of C, cleared with coalesced stores and no per-element index arithmetic.
+struct GapTable {
+  int n;
+  int start[kMaxPaths + 1], len[kMaxPaths + 1];
+};
+
 template <typename T>
-__global__ void zero_rows_kernel(T* C, long long batch, int c_rows_per_b, int N, const __grid_constant__ GroupTable tab) {
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long total = batch * c_rows_per_b * N;
-  if (idx >= total) return;
-  const int row = (int)((idx / N) % c_rows_per_b);
-  for (int g = 0; g < tab.n_groups; ++g)
-    if (row >= tab.group_c_row[g] && row < tab.group_c_row[g] + tab.group_rows[g]) return;
-  C[idx] = T(0);
+__global__ void __launch_bounds__(256) zero_gaps_kernel(T* __restrict__ C, long long batch, int c_rows_per_b, int N,
+                                                        const __grid_constant__ GapTable gaps) {
+  for (long long b = blockIdx.x; b < batch; b += gridDim.x)
+    for (int g = 0; g < gaps.n; ++g) {
+      T* p = C + ((size_t)b * c_rows_per_b + gaps.start[g]) * (size_t)N;
+      const int n = gaps.len[g] * N;
+      for (int i = threadIdx.x; i < n; i += blockDim.x) p[i] = T(0);
+    }
+}
+
+template <typename T>
+void zero_uncovered_rows(T* C, long long batch, int c_rows, int N, const GroupTable& tab, cudaStream_t s) {
+  GapTable gaps; gaps.n = 0;
+  int row = 0;                                      // groups are sorted by their first row and do not overlap
+  for (int g = 0; g <= tab.n_groups; ++g) {
+    const int next = g < tab.n_groups ? tab.group_c_row[g] : c_rows;
+    if (next > row) { gaps.start[gaps.n] = row; gaps.len[gaps.n] = next - row; ++gaps.n; }
+    if (g < tab.n_groups) row = tab.group_c_row[g] + tab.group_rows[g];
+  }
+  if (gaps.n == 0 || batch == 0) return;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 128;
+  const long long blocks = batch < (long long)sms * 8 ? batch : (long long)sms * 8;
+  zero_gaps_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(C, batch, c_rows, N, gaps);
 }
 
 int build_table(const fasteq_eqlinear_problem* p, bool dgrad, GroupTable* t, bool* covers_all) {
@@ -329,10 +351,7 @@ int launch(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const vo
   if (!w || !a || !c) return FASTEQ_INVALID;
   const int K = dgrad ? p->v : p->u, N = dgrad ? p->u : p->v;
   const int a_rows = dgrad ? p->out_rows : p->in_rows, c_rows = dgrad ? p->in_rows : p->out_rows;
-  if (!covers) {
-    const long long total = p->batch * c_rows * N;
-    zero_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, s>>>((T*)c, p->batch, c_rows, N, tab);
-  }
+  if (!covers) zero_uncovered_rows<T>((T*)c, p->batch, c_rows, N, tab, s);
   if (sizeof(T) == 8 && N >= 64 && (N % 2) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0) {
     const long long wt = tab.wide_tile_first[tab.n_groups];
     if (wt > 0x7fffffffLL) return FASTEQ_UNSUPPORTED;
@@ -397,10 +416,7 @@ int launch_tensorcore(const fasteq_eqlinear_problem* p, bool dgrad, const void* 
     pack_weights_kernel<<<(unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096), 256, 0, s>>>((const float*)w, bt, bt + total, tab, p->u, p->v, dgrad);
   }
   const float* hi = packed ? (const float*)packed : bt;
-  if (!covers) {
-    const long long tot = p->batch * c_rows * N;
-    zero_rows_kernel<float><<<(unsigned)((tot + 255) / 256), 256, 0, s>>>((float*)c, p->batch, c_rows, N, tab);
-  }
+  if (!covers) zero_uncovered_rows<float>((float*)c, p->batch, c_rows, N, tab, s);
   rc = tc::launch(t, (const float*)a, p->batch, a_rows, K, hi, hi + total, p->num_paths, N, (float*)c, c_rows, s);
   if (bt) cudaFreeAsync(bt, s);
   if (rc == FASTEQ_OK) *used = true;

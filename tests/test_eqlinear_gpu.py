@@ -162,3 +162,28 @@ def test_second_order_by_composition():
     got = second(lambda wt, xt: fast_equi_linear(d, wt, xt), "cuda")
     for a, b in zip(got, ref):
         assert _rel_fro(a.numpy(), b.numpy()) <= 1e-12
+
+
+@pytest.mark.parametrize("dtype,prec,tol", [(torch.float64, None, 1e-12), (torch.float32, "fp32", 2e-6), (torch.float32, None, 2e-5)])
+def test_rows_without_a_path_are_zero(dtype, prec, tol):
+    """Input blocks no path reads (their grad_x rows) and output blocks no path writes must come back as exact zeros,
+    in the middle and at both ends of the row range: the tensor-product output of all parities mixed down to the
+    natural-parity irreps (the benchmark's SO3Linear shape) plus an output irrep nothing feeds."""
+    from fasteq_b200.ops.eqlinear import fast_equi_linear, _descriptor_problem
+    d = linear("32x1e+32x0e+32x1o+32x2o+32x2e+32x0o", "32x3o+32x0e+32x1o+32x2e+32x4e")
+    mapping, coeff, u, v, I, J = _descriptor_problem(d)
+    assert len(d.paths) == 3 and I == 18 and J == 25
+    g = torch.Generator().manual_seed(12)
+    B = 333
+    x = torch.randn(B, I * u, generator=g, dtype=torch.float64)
+    w = torch.randn(len(d.paths) * u * v, generator=g, dtype=torch.float64)
+    r = torch.randn(B, J * v, generator=g, dtype=torch.float64)
+    xd = x.to(dtype).cuda().requires_grad_(True)
+    out = fast_equi_linear(d, w.to(dtype).cuda(), xd, compute_precision=prec)
+    (gx,) = torch.autograd.grad(out, xd, r.to(dtype).cuda())
+    ref = eqlinear_ref.eqlinear_forward(x.numpy().reshape(B, I, u), w.numpy().reshape(-1, u, v), mapping, coeff, J)
+    ref_gx = eqlinear_ref.eqlinear_dgrad(r.numpy().reshape(B, J, v), w.numpy().reshape(-1, u, v), mapping, coeff, I)
+    o3, g3 = out.detach().cpu().double().numpy().reshape(ref.shape), gx.cpu().double().numpy().reshape(ref_gx.shape)
+    assert _rel_fro(o3, ref) <= tol and _rel_fro(g3, ref_gx) <= tol
+    assert np.count_nonzero(o3[:, :7]) == 0 and np.count_nonzero(o3[:, 16:]) == 0           # 3o (rows 0-6) and 4e (rows 16-24)
+    assert np.count_nonzero(g3[:, :3]) == 0 and np.count_nonzero(g3[:, 7:12]) == 0 and np.count_nonzero(g3[:, 17:]) == 0
