@@ -56,6 +56,23 @@ def algorithmic_bytes(N, E, d, s):
     return fwd, bwd
 
 
+def fp32_floor(spec, tun, direction, needs, E, U, launch_s, dev, sm_mhz=None):
+    """FP32-pipe view of a CWTP kernel: arithmetic instructions per (edge, channel) counted in the generated source, the
+    time they need at 128 lanes per SM per clock, and the share of that rate the launch reached."""
+    from fasteq_b200.codegen import u1d as gen
+    ops = gen.arith_ops(spec, tun, direction, needs)
+    n = ops["fma"] + ops["mul"] + ops["add"]
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    if sm_mhz is None:
+        try:
+            sm_mhz = float(torch.cuda.clock_rate())
+        except Exception:
+            sm_mhz = 1965.0
+    floor_s = float(E) * U * n / (sms * 128 * sm_mhz * 1e6)
+    return {"fp32_ops_per_edge_channel": n, "fma": ops["fma"], "mul": ops["mul"], "fp32_floor_ms": floor_s * 1e3,
+            "fp32_pipe_utilisation": floor_s / launch_s, "sm_mhz": sm_mhz}
+
+
 def measured_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -485,8 +502,10 @@ def cwtp_kernel_block(workload: str, dev, seed: int = 0):
         t_b = _events_ms(lambda: u1d._run_bwd(call, r, w, x, y, (True, True, True)), 10) * 1e-3
     bf, bb = algorithmic_bytes(N, E, d, s)
     peak, kind = measured_peak()
-    tun = {dr: u1d._tuning_for(call.spec, dr, (w, x, y)) for dr in ("fwd", "bwd")}
-    return {"workload": workload, "w_segs": d.w_seg_num, "out_segs": d.out_seg_num, "cg_paths": d.num_paths, "atoms": N, "edges": E,
+    tun = {"fwd": u1d._tuning_for(call.spec, "fwd", (w, x, y)), "bwd": u1d._tuning_for(call.spec, "bwd", (w, x, y), (True, True, True))}
+    pipe = {"fwd": fp32_floor(call.spec, tun["fwd"], "fwd", (False, False, False), E, d.u_dim, t_f, dev),
+            "bwd": fp32_floor(call.spec, tun["bwd"], "bwd", (True, True, True), E, d.u_dim, t_b, dev)}
+    return {"workload": workload, "fp32_pipe": pipe, "w_segs": d.w_seg_num, "out_segs": d.out_seg_num, "cg_paths": d.num_paths, "atoms": N, "edges": E,
             "fwd": {"launch_ms": t_f * 1e3, "achieved": bf / t_f / 1e9, "frac": bf / t_f / 1e9 / peak, "algorithmic_bytes_per_launch": bf,
                     "traffic": TRAFFIC_RATIO[workload]["fwd"] * bf},
             "bwd": {"launch_ms": t_b * 1e3, "achieved": bb / t_b / 1e9, "frac": bb / t_b / 1e9 / peak, "algorithmic_bytes_per_launch": bb,
@@ -806,6 +825,12 @@ def main():
                 "unit": "GB/s", "frac": bytes_fwd / t_fwd / 1e9 / peak, "traffic": TRAFFIC_RATIO[args.workload]["fwd"] * bytes_fwd,
                 "algorithmic_bytes_per_launch": bytes_fwd,
                 "launch_ms": t_fwd * 1e3}
+    tun_f = u1d._tuning_for(call.spec, "fwd", (w, x, y))
+    tun_b = u1d._tuning_for(call.spec, "bwd", (w, x, y), (True, True, True))
+    roof["fp32_pipe"] = fp32_floor(call.spec, tun_b, "bwd", (True, True, True), E, d.u_dim, t_bwd, dev)
+    roof_fwd["fp32_pipe"] = fp32_floor(call.spec, tun_f, "fwd", (False, False, False), E, d.u_dim, t_fwd, dev)
+    roof["tuning"] = {k_: getattr(tun_b, k_) for k_ in ("pipes", "groups", "stages", "min_blocks", "two_pass")}
+    roof_fwd["tuning"] = {k_: getattr(tun_f, k_) for k_ in ("pipes", "groups", "stages", "min_blocks", "two_pass")}
     roof_both = {"achieved": (bytes_fwd + bytes_bwd) / (t_fwd + t_bwd) / 1e9,
                  "frac": (bytes_fwd + bytes_bwd) / (t_fwd + t_bwd) / 1e9 / peak,
                  "edges_per_s_kernels_only": E / (t_fwd + t_bwd)}

@@ -885,3 +885,15 @@ extern "C" int fasteq_u1d_backward(const fasteq_u1d_graph* gh, const void* go, c
 }}
 """)
     return "\n".join(src)
+
+
+def arith_ops(spec: U1DSpec, tun: Tuning, direction: str, needs=(True, True, True)) -> Dict[str, int]:
+    """Floating-point instructions the consumers execute per (edge, channel), counted in the generated source: every
+    ``vfma`` / ``vmul`` / ``vadd`` of the straight-line edge body (with two thread groups the groups' shares add up;
+    a packed instruction counts once per channel it serves).  ``fma + mul + add`` against ``SMs x 128 x clock`` is the
+    kernel's FP32-pipe floor, which for the larger signatures lies above the HBM floor."""
+    import re
+    src = emit_forward(spec, tun) if direction == "fwd" else emit_backward(spec, tun, *needs)
+    body = src[src.index("if ((m.flags & F_DATA) && live)"):]
+    body = body[:body.index("#undef W")]
+    return {"fma": len(re.findall(r"\bvfma\(", body)), "mul": len(re.findall(r"\bvmul\(", body)), "add": len(re.findall(r"\bvadd\(", body))}

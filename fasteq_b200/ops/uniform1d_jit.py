@@ -25,6 +25,7 @@ import numpy as np
 import torch
 
 from .. import _build, _cabi
+from .. import tuning as _tuning
 from ..codegen import u1d as _emit
 from ..codegen.u1d_common import U1DSpec, make_spec
 
@@ -44,7 +45,7 @@ def _dtype_str(t: torch.Tensor) -> str:
 
 def get_module(spec: U1DSpec, direction: str, needs=(False, False, False), tuning: Optional[_emit.Tuning] = None) -> _cabi.U1DModule:
     """Build (or load from the in-tree cache) the module of one signature."""
-    tun = tuning or _TUNING_OVERRIDE.get(direction) or _emit.default_tuning(spec, direction)
+    tun = tuning or _TUNING_OVERRIDE.get(direction) or _tuning.lookup(spec, direction, needs) or _emit.default_tuning(spec, direction)
     key = (spec, direction, tuple(needs), tun)
     with _lock:
         mod = _MODULES.get(key)
@@ -359,10 +360,11 @@ def _np(t, is_float=False) -> np.ndarray:
 _SPEC_CACHE: Dict[Tuple, U1DSpec] = {}
 
 
-def _tuning_for(spec: U1DSpec, direction: str, tensors) -> Optional[_emit.Tuning]:
-    """Packed two-channel modules read and write 8-byte pairs; operands at an odd 4-byte offset
-    (a contiguous view into a larger buffer) get the one-channel-per-thread module instead."""
-    tun = _TUNING_OVERRIDE.get(direction) or _emit.default_tuning(spec, direction)
+def _tuning_for(spec: U1DSpec, direction: str, tensors, needs=(False, False, False)) -> Optional[_emit.Tuning]:
+    """The launch configuration of this call: the measured winner of the signature when the tuning database has one,
+    else the heuristic default.  Packed two-channel modules read and write 8-byte pairs; operands at an odd 4-byte
+    offset (a contiguous view into a larger buffer) get the one-channel-per-thread module instead."""
+    tun = _TUNING_OVERRIDE.get(direction) or _tuning.lookup(spec, direction, needs) or _emit.default_tuning(spec, direction)
     if tun.vec == 2 and any(t is not None and t.data_ptr() % 8 for t in tensors):
         import dataclasses
         return dataclasses.replace(tun, vec=1, pipes=1, groups=max(tun.groups, 1), min_blocks=min(tun.min_blocks + 1, 3))
@@ -384,7 +386,7 @@ def _run_bwd(call: _Call, grad_out, w, x, y, needs):
     gw = torch.empty_like(w) if needs[0] else None
     gx = torch.empty_like(x) if needs[1] else None
     gy = torch.empty_like(y) if needs[2] else None
-    mod = get_module(call.spec, "bwd", needs, tuning=_tuning_for(call.spec, "bwd", (grad_out, w, x, y, gw, gx, gy)))
+    mod = get_module(call.spec, "bwd", needs, tuning=_tuning_for(call.spec, "bwd", (grad_out, w, x, y, gw, gx, gy), needs))
     ptr = lambda t: t.data_ptr() if t is not None else None
     with torch.cuda.device(dev):
         g = call.graph(mod, dev)

@@ -67,12 +67,28 @@ def test_default_tuning_is_the_four_pipeline_packed_layout(in1, parity, w_segs, 
     assert (default_tuning(spec, "fwd").stages == 10) == small
 
 
+@pytest.mark.parametrize("layout", ["four_pipelines", "tuned"])
 @pytest.mark.parametrize("fused_sh", [False, True], ids=["y_harmonics", "y_vectors"])
 @pytest.mark.parametrize("in1,parity,w_segs,out_segs,small", SIGNATURES)
-def test_wide_layout_matches_oracle(in1, parity, w_segs, out_segs, small, fused_sh):
+def test_wide_layout_matches_oracle(in1, parity, w_segs, out_segs, small, fused_sh, layout):
+    """``four_pipelines``: the heuristic layout (one CTA of four pipelines, packed arithmetic), forced; ``tuned``: whatever
+    the tuning database selects for the signature (what the benchmark and the model actually run)."""
     from fasteq_b200.ops import fast_uniform1d_jit
     from fasteq_b200.ops import uniform1d_jit as u1d
     d = _descriptor(in1, parity)
+    spec0 = make_spec(d.i_list, d.j_list, d.k_list, d.v_list, d.coeff_list, w_segs=d.w_seg_num, x_segs=d.x_seg_num,
+                      y_segs=d.y_seg_num, out_segs=d.out_seg_num, u=d.u_dim, dtype="f32")
+    if layout == "four_pipelines":
+        u1d._TUNING_OVERRIDE.update(fwd=default_tuning(spec0, "fwd"), bwd=default_tuning(spec0, "bwd"))
+    try:
+        _check_against_oracle(d, w_segs, fused_sh, layout)
+    finally:
+        u1d._TUNING_OVERRIDE.clear()
+
+
+def _check_against_oracle(d, w_segs, fused_sh, layout):
+    from fasteq_b200.ops import fast_uniform1d_jit
+    from fasteq_b200.ops import uniform1d_jit as u1d
     U, N = d.u_dim, 211
     g = torch.Generator().manual_seed(20 + w_segs)
     src, dst = _graph(N, g)
@@ -94,13 +110,15 @@ def test_wide_layout_matches_oracle(in1, parity, w_segs, out_segs, small, fused_
     out = fast_uniform1d_jit(wd, xd, y_dev, idx_in, idx_out, meta)
     gw, gx, gy = torch.autograd.grad(out, (wd, xd, y_dev), r.cuda())
 
-    # the modules that just ran are the wide ones
+    # the modules that just ran
     call = u1d._Call(wd, xd, y_dev, idx_in, idx_out, meta)
     for direction, needs in (("fwd", (False, False, False)), ("bwd", (True, True, True))):
-        tun = u1d._tuning_for(call.spec, direction, (wd, xd, y_dev))
-        assert tun.pipes == 4 and tun.vec == 2
+        tun = u1d._tuning_for(call.spec, direction, (wd, xd, y_dev), needs)
+        assert tun.vec == 2
+        if layout == "four_pipelines":
+            assert tun.pipes == 4 and tun.groups == 1
         mod = u1d.get_module(call.spec, direction, needs, tuning=tun)
-        assert mod.desc.threads == 4 * (64 + 32)
+        assert mod.desc.threads == tun.pipes * (tun.groups * 64 + 32)
         assert mod.device_status() == 0
 
     paths = list(zip(d.i_list.tolist(), d.j_list.tolist(), d.k_list.tolist(), d.v_list.tolist()))
@@ -133,3 +151,47 @@ def test_wide_layout_matches_oracle(in1, parity, w_segs, out_segs, small, fused_
     empty = torch.ones(N, dtype=torch.bool)
     empty[dst.unique()] = False
     assert torch.count_nonzero(out.detach()[empty.cuda()]) == 0
+
+
+@pytest.mark.parametrize("in1,parity,variant", [("128x0e+128x1o+128x2e", None, "groups2"), ("128x0e+128x1o", "natural", "groups2"),
+                                                ("128x0e+128x1o+128x2e", None, "groups2_two_pass"), ("64x0e+64x1o", None, "groups2"),
+                                                ("128x0e+128x1o", None, "fwd_groups2")])
+def test_two_thread_groups_match_oracle(in1, parity, variant):
+    """Launch configurations the tuner may pick: two consumer thread groups per pipeline.  In the backward each group
+    differentiates the terms of its own weight segments (its grad_w rows are its alone; both add into grad_x and into the
+    per-warp partial sums of grad_y); in the forward each group owns a share of the output segments."""
+    import dataclasses
+    from fasteq_b200.ops import fast_uniform1d_jit
+    from fasteq_b200.ops import uniform1d_jit as u1d
+    d = _descriptor(in1, parity)
+    U, N = d.u_dim, 97
+    g = torch.Generator().manual_seed(5)
+    src, dst = _graph(N, g)
+    E = int(dst.numel())
+    w = torch.randn(E, d.w_seg_num * U, generator=g)
+    x = torch.randn(N, d.x_seg_num * U, generator=g)
+    y = torch.randn(E, d.y_seg_num, generator=g)
+    r = torch.randn(N, d.out_seg_num * U, generator=g)
+    spec = make_spec(d.i_list, d.j_list, d.k_list, d.v_list, d.coeff_list, w_segs=d.w_seg_num, x_segs=d.x_seg_num,
+                     y_segs=d.y_seg_num, out_segs=d.out_seg_num, u=d.u_dim, dtype="f32")
+    direction = "fwd" if variant.startswith("fwd") else "bwd"
+    base = default_tuning(spec, direction)
+    tun = dataclasses.replace(base, groups=2, pipes=min(base.pipes, 2), two_pass=variant.endswith("two_pass"),
+                              stages=min(base.stages, 3 if direction == "bwd" else 4), min_blocks=1)
+    u1d._TUNING_OVERRIDE[direction] = tun
+    try:
+        wd, xd, yd = (t.cuda().requires_grad_(True) for t in (w, x, y))
+        out = fast_uniform1d_jit(wd, xd, yd, {1: src.int().cuda()}, {0: dst.int().cuda()}, d.meta(torch.float32, "cuda"))
+        gw, gx, gy = torch.autograd.grad(out, (wd, xd, yd), r.cuda())
+        mod = u1d.get_module(spec, direction, (True, True, True) if direction == "bwd" else (False, False, False), tuning=tun)
+        assert mod.desc.threads == tun.pipes * (2 * tun.ct // tun.vec + 32) and mod.device_status() == 0
+    finally:
+        u1d._TUNING_OVERRIDE.pop(direction, None)
+    paths = list(zip(d.i_list.tolist(), d.j_list.tolist(), d.k_list.tolist(), d.v_list.tolist()))
+    a = lambda t, s: t.double().numpy().reshape(t.shape[0], s, -1)
+    kw = dict(src_x=src.numpy(), dst=dst.numpy())
+    ref = uniform1d_ref.uniform1d_forward(a(w, d.w_seg_num), a(x, d.x_seg_num), a(y, d.y_seg_num), paths, d.coeff_list, d.out_seg_num,
+                                          num_out_rows=N, **kw)
+    rgw, rgx, rgy = uniform1d_ref.uniform1d_backward(a(r, d.out_seg_num), a(w, d.w_seg_num), a(x, d.x_seg_num), a(y, d.y_seg_num), paths,
+                                                     d.coeff_list, **kw)
+    _close(out, ref, "forward"); _close(gw, rgw, "grad_w"); _close(gx, rgx, "grad_x"); _close(gy, rgy, "grad_y")
