@@ -21,7 +21,7 @@ INCLUDE = os.path.join(ROOT, "include")
 LIB = os.path.join(PKG, "lib")
 JIT = os.path.join(LIB, "jit")
 CORE_SO = os.path.join(LIB, "libfasteq_b200_core.so")
-CORE_SOURCES = ["core.cu", "eqlinear.cu", "gemm_tf32x3.cu", "radial_chain.cu", "gate.cu", "neighbors.cu", "edge_geometry.cu"]
+CORE_SOURCES = ["core.cu", "eqlinear.cu", "eqlinear_api.cu", "gemm_tf32x3.cu", "radial_chain.cu", "gate.cu", "neighbors.cu", "edge_geometry.cu"]
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-diag-suppress", "177",

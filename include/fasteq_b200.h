@@ -272,6 +272,38 @@ int fasteq_eqlinear_dgrad_packed(const fasteq_eqlinear_problem* p /* host */, co
 int fasteq_eqlinear_wgrad(const fasteq_eqlinear_problem* p /* host */, const void* x, const void* grad_out,
                           void* grad_w, fasteq_stream_t stream);
 
+/* The same operator in the shape of the reference's backend interface: a table of function pointers per precision,
+ * field for field the EqLinearBackendApi / EqLinearProblemC / EqLinearPathC / EqLinearPlanInfo of
+ * fasteq/cuda/src/eqlinear/common/eqlinear_backend_api.h:12-27 and eqlinear_common.h:30-62 (abi_version 2), so that a
+ * dispatcher written against it (dispatch/eqlinear_dispatch.cpp:215-312) can load this library as a backend.
+ * i_dims / paths / cg are borrowed during create only.  A plan owns a device copy of the weights in the form its kernel
+ * multiplies with (create calls cudaMalloc and enqueues the preparation on `stream`), is bound to the problem's batch
+ * size B, and must be destroyed by the same table's destroy (which frees device memory and therefore waits for the
+ * device).  One plan must not be run concurrently from unsynchronised streams. */
+typedef struct fasteq_eqlinear_path_c { int32_t input_row, output_row, weight_path, rows; } fasteq_eqlinear_path_c;
+typedef struct fasteq_eqlinear_problem_c {
+  int32_t B, I, U, P, V, J;              /* batch, rows of x, channels in, paths (= weight blocks), channels out, rows of out */
+  const int32_t* i_dims;                 /* host [P]: 2l+1 per path for the dense run-length layout (used when paths is NULL) */
+  const fasteq_eqlinear_path_c* paths;   /* host [P] explicit mapping, or NULL */
+} fasteq_eqlinear_problem_c;
+typedef struct fasteq_eqlinear_plan_info { int32_t precision, forward_impl, dgrad_impl, a_view, j_rows; } fasteq_eqlinear_plan_info;
+typedef struct fasteq_eqlinear_backend_api {
+  uint32_t abi_version;                  /* 2 */
+  int32_t precision;                     /* fasteq_eqlinear_precision */
+  int (*forward_create)(const fasteq_eqlinear_problem_c* problem, const void* w, const double* cg /* host [P] */,
+                        fasteq_stream_t stream, void** plan, fasteq_eqlinear_plan_info* info /* or NULL */);
+  int (*forward_run)(void* plan, const void* x, void* out, fasteq_stream_t stream);
+  void (*forward_destroy)(void* plan);
+  int (*dgrad_create)(const fasteq_eqlinear_problem_c* problem, const void* w, const double* cg, fasteq_stream_t stream,
+                      void** plan, fasteq_eqlinear_plan_info* info);
+  int (*dgrad_run)(void* plan, const void* dy, void* dx, fasteq_stream_t stream);
+  void (*dgrad_destroy)(void* plan);
+  const char* (*status_string)(int code);
+} fasteq_eqlinear_backend_api;
+const fasteq_eqlinear_backend_api* fasteq_eqlinear_tf32_api(void);
+const fasteq_eqlinear_backend_api* fasteq_eqlinear_fp32_api(void);
+const fasteq_eqlinear_backend_api* fasteq_eqlinear_fp64_api(void);
+
 /* ------------------------------------------------------------------------- *
  * Gate non-linearity (e3nn nn.Gate) on ir_mul rows [segments, u]: input = scalar segments, one gate
  * segment per gated irrep block, then the gated irreps; output = scalar segments, gated irreps.

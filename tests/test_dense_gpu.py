@@ -25,9 +25,9 @@ def test_dense_forward_matches_float64(M, N, K):
     ref = x.double() @ w.double().t()
     out = dense(x.cuda(), w.cuda())
     assert out.shape == (M, N)
-    assert _rel(out.cpu(), ref) <= (2e-6 if K <= 128 else 2e-5), _rel(out.cpu(), ref)   # long K: the 3xTF32 bound of the reference (2e-5)
+    assert _rel(out.cpu(), ref) <= (2e-6 if K <= 128 else 1e-5), _rel(out.cpu(), ref)   # long K: measured 4e-6 at K = 1664 (the reference allows 2e-5)
     # element-wise too: a misplaced tile would hide in a norm
-    assert float((out.cpu().double() - ref).abs().max()) <= 2e-5 * float(ref.abs().max())
+    assert float((out.cpu().double() - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
     assert tensorcore_device_status() == 0
 
 

@@ -93,7 +93,7 @@ def test_symmetric_contraction_and_gate_empty_batch():
     _no_device_error()
 
 
-@pytest.mark.parametrize("dtype,tol", [(torch.float64, 1e-11), (torch.float32, 3e-5)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float64, 1e-11), (torch.float32, 1e-5)])
 def test_model_on_isolated_atoms(dtype, tol):
     """No atom has a neighbour inside the cutoff: every edge tensor is empty, the energy is the sum of the
     per-atom terms and the forces vanish; values against the CPU oracle model on the same empty graph."""
