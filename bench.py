@@ -38,6 +38,8 @@ WORKLOADS = {
     # name: (irreps_in1, SH lmax, lmax_out, boxes per GPU, dtype)
     "config1_cwtp": ("128x0e+128x1o", 3, 3, 64, torch.float32),
     "config0_layout_cwtp": ("128x0e+128x1o+128x2e", 3, 3, 64, torch.float32),
+    # the interaction of configuration 3's NequIP-style layers (64 channels, six irreps, SH l <= 2: 30 weight / 102 output segments)
+    "config3_layer_cwtp": ("64x0e+64x0o+64x1e+64x1o+64x2e+64x2o", 2, 2, 64, torch.float32),
 }
 METRIC = "ChannelwiseTP edges/s (fwd+force bwd)"
 CPU_NOTE = ("port of e3nn's uvu TensorProduct + scatter (oracle/e3nn_uvu_ref.py, pinned to e3nn 0.5.6 golden vectors at 1e-12), "
@@ -45,7 +47,8 @@ CPU_NOTE = ("port of e3nn's uvu TensorProduct + scatter (oracle/e3nn_uvu_ref.py,
 # DRAM bytes (dram__bytes_read + dram__bytes_write) over algorithmic bytes, from one ncu capture per kernel
 # on a 16-box case of the same workload; traffic grows in proportion to the edge count (every term
 # is per edge or per node and the generator fixes edges per node), so the ratio carries to a full launch.
-TRAFFIC_RATIO = {"config1_cwtp": {"fwd": 1.013, "bwd": 1.035}, "config0_layout_cwtp": {"fwd": 1.060, "bwd": 1.176}}
+TRAFFIC_RATIO = {"config1_cwtp": {"fwd": 1.013, "bwd": 1.035}, "config0_layout_cwtp": {"fwd": 1.060, "bwd": 1.176},
+                 "config3_layer_cwtp": {"fwd": 1.0, "bwd": 1.0}}
 
 
 def algorithmic_bytes(N, E, d, s):
@@ -489,7 +492,7 @@ def cwtp_kernel_block(workload: str, dev, seed: int = 0):
     inp = build_inputs(workload, seed=seed)
     d, N, E, dtype = inp["d"], inp["N"], inp["E"], inp["dtype"]
     s = 4 if dtype == torch.float32 else 8
-    y = torch.from_numpy(spherical_harmonics_host(3, inp["vec"].numpy(), normalize=True)).to(dtype).contiguous().to(dev)
+    y = torch.from_numpy(spherical_harmonics_host(WORKLOADS[workload][1], inp["vec"].numpy(), normalize=True)).to(dtype).contiguous().to(dev)
     w, x, r = inp["w"].to(dev), inp["x"].to(dev), inp["r"].to(dev)
     src, dst = inp["src"].to(dev), inp["dst"].to(dev)
     meta = d.meta(dtype, dev)
@@ -763,7 +766,7 @@ def main():
     inp = build_inputs(args.workload, seed=rank, n_boxes=args.boxes)
     d, N, E, dtype = inp["d"], inp["N"], inp["E"], inp["dtype"]
     s = 4 if dtype == torch.float32 else 8
-    y_host = torch.from_numpy(spherical_harmonics_host(3, inp["vec"].numpy(), normalize=True)).to(dtype).contiguous()
+    y_host = torch.from_numpy(spherical_harmonics_host(WORKLOADS[args.workload][1], inp["vec"].numpy(), normalize=True)).to(dtype).contiguous()
     meta = d.meta(dtype, dev)
     host = {k: inp[k].contiguous().pin_memory() for k in ("w", "x", "r", "src", "dst")}
     host["y"] = y_host.pin_memory()

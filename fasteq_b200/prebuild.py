@@ -83,6 +83,9 @@ def build_standard_modules(verbose: bool = False) -> None:
                          y_segs=d.y_seg_num, out_segs=d.out_seg_num, u=d.u_dim, dtype="f32")
         for sp in (spec, dataclasses.replace(spec, y_sh=((0, 1, 2, 3), True, "component"))):
             jobs += [(sp, "fwd", (False, False, False)), (sp, "bwd", (True, True, True))]
+            # ... and on the heuristic four-pipeline layout, which those tests force next to the tuned one
+            from .codegen.u1d import default_tuning
+            jobs += [(sp, "fwd", (False, False, False), default_tuning(sp, "fwd")), (sp, "bwd", (True, True, True), default_tuning(sp, "bwd"))]
     stc_jobs = []
     for a, b, dtypes in STANDARD_STC:
         for dt in dtypes:

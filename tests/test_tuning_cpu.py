@@ -1,0 +1,56 @@
+"""The per-signature tuning layer on the CPU: candidate generation respects one SM's shared memory and thread limits, the
+tracked database decodes, names only standard signatures, and the operator front-end picks its entries up."""
+import dataclasses
+
+import pytest
+
+from fasteq_b200 import tuning
+from fasteq_b200.codegen import u1d as gen
+from fasteq_b200.prebuild import cwtp_spec
+
+
+@pytest.mark.parametrize("in1,lmax,dtype", [("128x0e+128x1o+128x2e", 3, "f32"), ("128x0e+128x1o", 3, "f32"), ("64x0e+64x1o", 3, "f64"),
+                                            ("33x0e+33x1o", 2, "f32")])
+def test_candidates_fit_one_sm(in1, lmax, dtype):
+    spec = cwtp_spec(in1, lmax, lmax, dtype)
+    for direction, needs in (("fwd", (False, False, False)), ("bwd", (True, True, True))):
+        cands = tuning.candidates(spec, direction, needs)
+        assert cands[0] == gen.default_tuning(spec, direction)              # the heuristic default is always timed first
+        assert len(cands) == len(set(cands)) and 1 <= len(cands) <= 24
+        for t in cands:
+            assert tuning.smem_bytes(spec, t, direction, needs[2]) * t.min_blocks <= 227 * 1024 or t == cands[0]
+            assert t.pipes * (t.groups * (t.ct // t.vec) + 32) <= 1024
+            if direction == "bwd" and t.groups == 2:
+                gen.emit_backward(spec, t, *needs)                           # the generator accepts what the tuner proposes
+
+
+def test_smem_model_matches_the_generated_constants():
+    """``tuning.smem_bytes`` mirrors the SMEM_BYTES expression of the generated source (checked by evaluating it)."""
+    import re
+    spec = cwtp_spec("128x0e+128x1o", 3, 3, "f32")
+    for direction in ("fwd", "bwd"):
+        t = gen.default_tuning(spec, direction)
+        src = gen.emit_forward(spec, t) if direction == "fwd" else gen.emit_backward(spec, t, True, True, True)
+        assert "constexpr int SMEM_BYTES = cfg::PIPES * PIPE_BYTES;" in src
+        stage = gen._stage_bytes(spec, t.ct, 0 if direction == "fwd" else (2 * 16 * 4 + 15) // 16 * 16)
+        want = t.pipes * (256 + t.stages * stage + (0 if direction == "fwd" else (spec.out_segs * t.ct * 4 + 127) // 128 * 128))
+        assert tuning.smem_bytes(spec, t, direction, True) == want
+
+
+def test_database_entries_decode_and_are_used():
+    db = tuning.load_db()
+    if not db:
+        pytest.skip("no tuning database in this checkout")
+    keys = {tuning._key(spec, d, needs): (spec, d, needs) for _, spec, d, needs in tuning.sweep_jobs()}
+    for k, entry in db.items():
+        assert k in keys, f"entry {entry.get('label')} belongs to no standard signature"
+        spec, d, needs = keys[k]
+        t = tuning.lookup(spec, d, needs)
+        assert isinstance(t, gen.Tuning) and t in tuning.candidates(spec, d, needs)
+        assert entry["ms"] <= entry["default_ms"] * 1.0001                     # the winner is never slower than the default it was timed against
+        # the front-end resolves the same configuration, also for the variant with in-kernel harmonics
+        from fasteq_b200.ops import uniform1d_jit as u1d
+        assert u1d._tuning_for(spec, d, (), needs) == t
+        if spec.y_segs == 16 and not spec.y_vec:
+            fused = dataclasses.replace(spec, y_sh=((0, 1, 2, 3), True, "component"))
+            assert tuning.lookup(fused, d, needs) == t
