@@ -35,6 +35,7 @@ class Tuning:
     two_pass: bool = False  # backward: evaluate a block once for grad_w and once for grad_x / grad_y
     pipes: int = 1     # independent producer/consumer pipelines per CTA (keeps all four SM sub-partitions busy)
     go_smem: bool = True   # backward: stage the receiver's grad_out row in shared memory (else read it through L1)
+    prefetch: int = 0      # ring-fuls by which the producer asks rows into L2 ahead of the stage fills (0 = no prefetch)
 
 
 def default_tuning(spec: U1DSpec, direction: str) -> Tuning:
@@ -121,6 +122,7 @@ using T = {spec.ctype};
 using V = {vtype};   // what one thread carries per segment: one channel, or two packed FP32 channels
 constexpr int U = {spec.u}, CT = {tun.ct}, WSEG = {spec.w_segs}, XSEG = {spec.x_segs}, YSEG = {spec.y_segs}, OSEG = {spec.out_segs};
 constexpr int STAGES = {tun.stages}, GROUPS = {tun.groups}, PIPES = {tun.pipes}, NCONS_WARPS = {ncons_warps}, STAGE_EXTRA_BYTES = {extra_bytes};
+constexpr int PREFETCH = {tun.prefetch};
 constexpr bool EMIT_EMPTY_ROWS = {b(emit_empty)}, BEGIN_PER_SEGMENT = {b(not emit_empty)};
 constexpr bool Y_VEC = {b(spec.y_vec)}, W_SHARED = {b(spec.w_shared)}, X_INDEXED = {b(spec.x_indexed)}, Y_INDEXED = {b(spec.y_indexed)}, SCATTERED = {b(spec.scattered)};
 constexpr bool Y_SH = {b(bool(spec.y_sh))};   // the y operand holds edge vectors [rows, 3]; the producer evaluates their harmonics

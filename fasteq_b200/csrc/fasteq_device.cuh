@@ -85,6 +85,12 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
       : "memory");
 }
 
+// Ask the TMA engine to bring [gmem_src, gmem_src + bytes) into L2 (no destination, no completion to wait for):
+// 16-byte aligned address, size a multiple of 16 bytes.  Used by the producers to run ahead of their ring.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gmem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem_src), "r"(bytes) : "memory");
+}
+
 // 1-D bulk copy shared -> global, tracked by the per-thread bulk async-group.
 __device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"

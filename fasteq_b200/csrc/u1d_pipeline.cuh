@@ -8,7 +8,7 @@
 // shared memory.
 //
 // The including file must define namespace cfg { T, U, CT, WSEG, XSEG, YSEG,
-// OSEG, STAGES, PIPES, Y_VEC, W_SHARED, X_INDEXED, Y_INDEXED, SCATTERED, Y_SH, NCONS_WARPS,
+// OSEG, STAGES, PIPES, PREFETCH, Y_VEC, W_SHARED, X_INDEXED, Y_INDEXED, SCATTERED, Y_SH, NCONS_WARPS,
 // STAGE_EXTRA_BYTES, EMIT_EMPTY_ROWS, BEGIN_PER_SEGMENT } and namespace fasteq_sh { eval, vjp }
 // (spherical harmonics of an edge vector and their vector-Jacobian product; stubs unless Y_SH).
 #pragma once
@@ -150,6 +150,19 @@ struct Producer {
     __syncwarp();
   }
 
+  // this lane's edge: its weight row and its gathered x row (the tile's share of them) towards L2
+  __device__ __forceinline__ void prefetch_rows(int e, int xr, int yr, int ct) {
+    (void)yr;
+    if (FULL_ROW) {
+      if (!cfg::W_SHARED) bulk_prefetch_l2(w + (size_t)e * WSEG * U, (uint32_t)(WSEG * U * sizeof(T)));
+      bulk_prefetch_l2(x + (size_t)xr * XSEG * U, (uint32_t)(XSEG * U * sizeof(T)));
+    } else {
+      const uint32_t piece = (uint32_t)(valid_of(ct) * sizeof(T));
+      if (!cfg::W_SHARED) for (int s = 0; s < WSEG; ++s) bulk_prefetch_l2(w + (size_t)e * WSEG * U + (size_t)s * U + ct * CT, piece);
+      for (int s = 0; s < XSEG; ++s) bulk_prefetch_l2(x + (size_t)xr * XSEG * U + (size_t)s * U + ct * CT, piece);
+    }
+  }
+
   // Y_SH: the y operand is the edge vector; its harmonics are evaluated here, into the stage's y row
   __device__ __forceinline__ void sh_row(unsigned char* st, int yr) {
     const T* v = y + (size_t)yr * 3;
@@ -205,9 +218,16 @@ struct Producer {
   __device__ __forceinline__ void fill_batch(int m, int me, int mx, int my, int row, int ct, bool first, bool last,
                                              bool each_is_segment, Flush&& flush, Begin&& begin) {
     if (g.bulk_ok && !(each_is_segment && cfg::BEGIN_PER_SEGMENT)) {
+      // L2 prefetch, PREFETCH ring-fuls ahead of the stage fills: the ring bounds the bytes this pipeline has in
+      // flight towards shared memory; rows asked into L2 early shorten the latency of the copies that follow
+      if (cfg::PREFETCH > 0 && lane < m && lane < cfg::PREFETCH * STAGES) prefetch_rows(me, mx, my, ct);
       for (int base = 0; base < m; base += STAGES) {
         const int n = (m - base) < STAGES ? (m - base) : STAGES;
         const int l = lane - base;
+        if (cfg::PREFETCH > 0) {
+          const int pl = l - cfg::PREFETCH * STAGES;
+          if (pl >= 0 && pl < STAGES && lane < m) prefetch_rows(me, mx, my, ct);
+        }
         if (l >= 0 && l < n) {
           int flags = F_DATA;
           if (each_is_segment || (first && lane == 0)) flags |= F_FIRST;
