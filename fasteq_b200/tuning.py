@@ -101,9 +101,9 @@ def candidates(spec: U1DSpec, direction: str, needs=(True, True, True)) -> List[
     if direction == "bwd":
         for groups in ((1, 2) if two_groups_ok else (1,)):
             add(base.pipes, groups, base.min_blocks, True, lambda fit: (fit,))         # two passes over a block: fewer live registers
-    # L2 prefetch one, two and four ring-fuls ahead, on top of the default and of the deepest-ring variants of its shape
+    # L2 prefetch one and two ring-fuls ahead, on top of the default and of the deepest-ring variants of its shape
     for tun in [t for t in out if (t.pipes, t.groups, t.min_blocks, t.two_pass) == (base.pipes, base.groups, base.min_blocks, False)]:
-        for pf in (1, 2, 4):
+        for pf in (1, 2):
             out.append(dataclasses.replace(tun, prefetch=pf))
     return out
 
@@ -137,7 +137,7 @@ def _graph(n_boxes: int):
 
 
 def sweep(spec: U1DSpec, direction: str, needs=(True, True, True), n_boxes: int = 64, launches: int = 8, repeats: int = 3,
-          margin: float = 0.02, verbose: bool = False) -> dict:
+          margin: float = 0.03, verbose: bool = False) -> dict:
     """Time every candidate's kernel alone (CUDA events around ``launches`` back-to-back launches after two warm-up
     launches; the best of ``repeats`` such bursts) and return the database entry of the fastest.  The heuristic default
     keeps its place unless a candidate beats it by more than ``margin`` (run-to-run noise is a few per cent)."""
@@ -150,6 +150,17 @@ def sweep(spec: U1DSpec, direction: str, needs=(True, True, True), n_boxes: int 
     N, E, w, x, y, r, src, dst = _inputs(spec, n_boxes, dev)
     plan = u1d.graph_plan(dst, N)
     results = []
+    runners = {}
+    bufs: Dict[str, object] = {}       # outputs shared by all candidates
+
+    def burst(run):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(launches):
+            run()
+        b.record(); torch.cuda.synchronize()
+        return a.elapsed_time(b) / launches
+
     for tun in candidates(spec, direction, needs):
         try:
             mod = u1d.get_module(spec, direction, needs if direction == "bwd" else (False, False, False), tuning=tun)
@@ -162,26 +173,21 @@ def sweep(spec: U1DSpec, direction: str, needs=(True, True, True), n_boxes: int 
         n_parts = max(1, min(u1d._sm_count(dev) * int(mod.desc.ctas_per_sm), N))
         gph.part_ptr, gph.n_parts = plan.partition(n_parts).data_ptr(), n_parts
         stream = torch.cuda.current_stream(dev).cuda_stream
+        # (the closures bind this candidate's module and graph record: they are called again in the confirmation phase)
         if direction == "fwd":
-            out = torch.empty(N, spec.out_segs * spec.u, dtype=x.dtype, device=dev)
-            run = lambda: mod.forward(gph, w.data_ptr(), x.data_ptr(), y.data_ptr(), out.data_ptr(), stream)
+            out = bufs.setdefault("out", torch.empty(N, spec.out_segs * spec.u, dtype=x.dtype, device=dev))
+            run = lambda mod=mod, gph=gph: mod.forward(gph, w.data_ptr(), x.data_ptr(), y.data_ptr(), out.data_ptr(), stream)
         else:
-            gw = torch.empty_like(w) if needs[0] else None
-            gx = torch.empty_like(x) if needs[1] else None
-            gy = torch.empty_like(y) if needs[2] else None
+            gw = bufs.setdefault("gw", torch.empty_like(w)) if needs[0] else None
+            gx = bufs.setdefault("gx", torch.empty_like(x)) if needs[1] else None
+            gy = bufs.setdefault("gy", torch.empty_like(y)) if needs[2] else None
             ptr = lambda t: t.data_ptr() if t is not None else None
-            run = lambda: mod.backward(gph, r.data_ptr(), w.data_ptr(), x.data_ptr(), y.data_ptr(), ptr(gw), ptr(gx), ptr(gy), stream)
+            run = lambda mod=mod, gph=gph: mod.backward(gph, r.data_ptr(), w.data_ptr(), x.data_ptr(), y.data_ptr(), ptr(gw), ptr(gx), ptr(gy), stream)
         try:
             run(); run(); torch.cuda.synchronize()
-            ms = float("inf")
-            for _ in range(repeats):
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                for _ in range(launches):
-                    run()
-                b.record(); torch.cuda.synchronize()
-                ms = min(ms, a.elapsed_time(b) / launches)
+            ms = min(burst(run) for _ in range(repeats))
             status = mod.device_status()
+            runners[tun] = run
         except Exception as exc:
             results.append({"tuning": dataclasses.asdict(tun), "failed": str(exc)[-200:]})
             continue
@@ -194,9 +200,20 @@ def sweep(spec: U1DSpec, direction: str, needs=(True, True, True), n_boxes: int 
         raise RuntimeError("no candidate ran")
     best = min(good, key=lambda r_: r_["ms"])
     default_ms = results[0].get("ms")
-    if default_ms is not None and results[0].get("device_status") == 0 and best["ms"] > default_ms * (1.0 - margin):
-        best = results[0]
-    return {"tuning": best["tuning"], "ms": best["ms"], "default_ms": default_ms, "edges": E, "atoms": N,
+    default_ok = default_ms is not None and results[0].get("device_status") == 0
+    if default_ok and best is not results[0]:
+        # confirmation: the GPU's clocks and temperature drift over a sweep, so the challenger and the default are timed
+        # again in alternation; the default keeps its place unless it loses by more than the margin here too
+        tb, td = _emit.Tuning(**best["tuning"]), _emit.Tuning(**results[0]["tuning"])
+        b_ms = d_ms = float("inf")
+        for _ in range(3):
+            d_ms = min(d_ms, burst(runners[td])); b_ms = min(b_ms, burst(runners[tb]))
+        best = dict(best, ms=b_ms, confirmed_against_default_ms=d_ms)
+        default_ms = min(default_ms, d_ms)
+        if b_ms > default_ms * (1.0 - margin):          # must beat the default's best time of either phase
+            best = dict(results[0], ms=default_ms)
+    return {"tuning": best["tuning"], "ms": best["ms"], "default_ms": default_ms, "confirmed_against_default_ms": best.get("confirmed_against_default_ms"),
+            "edges": E, "atoms": N,
             "gpu": torch.cuda.get_device_name(dev), "direction": direction, "needs": [bool(n) for n in needs],
             "signature": {"u": spec.u, "dtype": spec.dtype, "w_segs": spec.w_segs, "x_segs": spec.x_segs, "y_segs": spec.y_segs,
                           "out_segs": spec.out_segs, "paths": len(spec.paths)},
