@@ -256,10 +256,19 @@ def halo_model_bench(args, dev, rank, world, dist):
         replay = dict(checksums(o2), ms_per_step=float(msr[0]) / k, value=b.n_nodes * k / (float(msr[0]) * 1e-3), unit="atom-steps/s")
     else:
         replay = {"failed": why or "capture failed on another rank"}
+    eager_ms = float(ms[0]) / k
+    # the block's figure: the replayed step where the capture succeeded and reproduces the eager checksums (a molecular-dynamics
+    # run replays between neighbour-list rebuilds), else the eager step; both are printed
+    replay_ok = "ms_per_step" in replay and abs(replay["energy"] - chk["energy"]) <= 1e-5 * abs(chk["energy"]) \
+        and abs(replay["force_l2"] - chk["force_l2"]) <= 1e-5 * chk["force_l2"]
+    best_ms = min(eager_ms, replay["ms_per_step"]) if replay_ok else eager_ms
     return {"metric": "NequIP-style atom-steps/s, one 20,000-atom graph, receiver-range partition + halo", "scaling": "strong",
-            "value": b.n_nodes * k / (float(ms[0]) * 1e-3), "unit": "atom-steps/s", "ms_per_step": float(ms[0]) / k,
+            "value": b.n_nodes / (best_ms * 1e-3), "unit": "atom-steps/s", "ms_per_step": best_ms,
+            "mode": "cuda_graph_replay" if (replay_ok and replay["ms_per_step"] < eager_ms) else "eager",
+            "eager_ms_per_step": eager_ms, "eager_exchange": "all-gather of padded export slabs (least host work)" if world > 1 else None,
             "energy": chk["energy"], "force_l2": chk["force_l2"], "force_l1": chk["force_l1"], "cuda_graph_replay": replay,
-            "exchange": "per layer one variable-size all-to-all to the ranks that read this rank's rows (forward) and back (force pass)",
+            "replay_exchange": ("per layer one variable-size all-to-all to the ranks that read this rank's rows (forward) and back "
+                                "(force pass), captured with the kernels") if world > 1 else None,
             "atoms": b.n_nodes, "edges": b.n_edges, "owned": lg.n_owned, "ghosts": int(len(lg.ghost_global)),
             "config": "config 3: 4 gated layers, 64x0e+64x0o+64x1e+64x1o+64x2e+64x2o, SH l<=2, cutoff 4 A, FP32"}
 

@@ -182,9 +182,14 @@ class HaloExchange:
         ext = halo.end(t)              # wait; ghost rows are valid from here on
     """
 
-    def __init__(self, local: LocalGraph, device, group=None, mode: str = "alltoall"):
-        if mode not in ("alltoall", "gather"):
-            raise ValueError("mode must be 'alltoall' or 'gather'")
+    def __init__(self, local: LocalGraph, device, group=None, mode: str = "auto"):
+        """``mode``: ``"alltoall"`` (neighbour-only exchange: least data), ``"gather"`` (padded slabs to every rank: one
+        collective call, least host work) or ``"auto"``: the all-to-all while a CUDA graph is being captured -- a replayed
+        step is bound by the GPU, so bytes matter -- and the gather in eager execution on CUDA, where at a few thousand
+        atoms per rank the step is bound by the host's launch rate and a variable-size all-to-all (one send / receive
+        pair per peer) costs several times the host time of a single all-gather.  Both deliver the same ghost rows."""
+        if mode not in ("alltoall", "gather", "auto"):
+            raise ValueError("mode must be 'alltoall', 'gather' or 'auto'")
         self.local, self.mode = local, mode
         self.export_idx = torch.as_tensor(local.export_local, device=device)
         self.ghost_slot = torch.as_tensor(local.ghost_slot, device=device)
@@ -192,15 +197,20 @@ class HaloExchange:
         self.group = group
         self._pending: list = []
 
+    def _gathers(self, x: torch.Tensor) -> bool:
+        if self.mode != "auto":
+            return self.mode == "gather"
+        return x.is_cuda and not torch.cuda.is_current_stream_capturing()
+
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         if self.local.world == 1:
             return x
-        if self.mode == "gather":
+        if self._gathers(x):
             return _Halo.apply(x, self.export_idx, self.ghost_slot, self.local.max_export, self.group)
         return _HaloA2A.apply(x, self.send_idx, self.local.send_counts, self.local.recv_counts, self.group, None)
 
     def begin(self, x: torch.Tensor) -> torch.Tensor:
-        if self.local.world == 1 or self.mode == "gather" or (x.is_cuda and torch.cuda.is_current_stream_capturing()):
+        if self.local.world == 1 or self._gathers(x) or (x.is_cuda and torch.cuda.is_current_stream_capturing()):
             return self(x)
         return _HaloA2A.apply(x, self.send_idx, self.local.send_counts, self.local.recv_counts, self.group, self._pending)
 

@@ -56,7 +56,7 @@ def _worker(rank, world, port, q, mode="alltoall"):
     b, feat, w1, w2 = _problem()
     parts = partition_by_receiver_range(b.n_nodes, b.edge_src, b.edge_dst, world)
     lg = parts[rank]
-    halo = HaloExchange(lg, "cpu", mode="gather" if mode == "gather" else "alltoall")
+    halo = HaloExchange(lg, "cpu", mode={"gather": "gather", "auto": "auto"}.get(mode, "alltoall"))
     pos = torch.from_numpy(b.positions[lg.start:lg.stop]).requires_grad_(True)
     shift = torch.from_numpy(b.edge_shift[lg.edge_ids])
     e = _toy_energy(pos, feat[lg.start:lg.stop], torch.from_numpy(lg.edge_src), torch.from_numpy(lg.edge_dst), shift, w1, w2, halo,
@@ -67,7 +67,7 @@ def _worker(rank, world, port, q, mode="alltoall"):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,mode", [(2, "alltoall"), (3, "alltoall"), (3, "split"), (2, "gather")])
+@pytest.mark.parametrize("world,mode", [(2, "alltoall"), (3, "alltoall"), (3, "split"), (2, "gather"), (2, "auto")])
 def test_partitioned_energy_and_forces_match_single_process(world, mode):
     b, feat, w1, w2 = _problem()
     pos = torch.from_numpy(b.positions).requires_grad_(True)

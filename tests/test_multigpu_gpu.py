@@ -17,7 +17,7 @@ def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, mode):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -31,7 +31,7 @@ def _worker(rank, world, port, q):
     model = MACEStyleModel(num_species=2, channels=32, r_max=3.5, avg_num_neighbors=12.0).double().to(dev)
     b = make_boxes(1, 80, 9.0, 3.5, 2, seed=11)
     lg = partition_by_receiver_range(b.n_nodes, b.edge_src, b.edge_dst, world)[rank]
-    halo = HaloExchange(lg, dev)
+    halo = HaloExchange(lg, dev, mode=mode)
     t = lambda a: torch.from_numpy(a).to(dev)
     out = model(t(b.positions[lg.start:lg.stop]), t(b.species[lg.start:lg.stop]), t(lg.edge_src), t(lg.edge_dst),
                 t(b.edge_shift[lg.edge_ids]), halo=halo)
@@ -46,13 +46,16 @@ def _worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-def test_two_gpu_halo_matches_single_gpu():
+@pytest.mark.parametrize("mode", ["auto", "alltoall"])
+def test_two_gpu_halo_matches_single_gpu(mode):
+    """``auto``: padded slabs all-gathered (the eager default on CUDA); ``alltoall``: the neighbour-only exchange with the
+    collective left in flight behind node-local work (``begin`` / ``end``)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, mode)) for r in range(2)]
     for p in procs:
         p.start()
     got = [q.get(timeout=600) for _ in range(2)]
