@@ -40,6 +40,16 @@ class U1DSpec:
     y_sh: tuple = ()            # (degrees, normalize, normalization): y rows are edge vectors [rows, 3] and the
                                 # kernel evaluates their spherical harmonics itself (scalar-y mode only)
 
+    def __hash__(self) -> int:
+        # specs key the module and tuning caches on every operator call; the path table has hundreds of entries, so its
+        # hash is computed once per object
+        h = self.__dict__.get("_hash")
+        if h is None:
+            h = hash((self.paths, self.w_segs, self.x_segs, self.y_segs, self.out_segs, self.u, self.dtype, self.y_vec,
+                      self.w_shared, self.x_indexed, self.y_indexed, self.scattered, self.y_sh))
+            object.__setattr__(self, "_hash", h)
+        return h
+
     @property
     def ctype(self) -> str:
         return "float" if self.dtype == "f32" else "double"

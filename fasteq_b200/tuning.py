@@ -43,9 +43,21 @@ def load_db() -> Dict[str, dict]:
     return _db
 
 
+_LOOKUPS: Dict[Tuple, Optional[_emit.Tuning]] = {}
+
+
 def lookup(spec: U1DSpec, direction: str, needs=(False, False, False)) -> Optional[_emit.Tuning]:
     """The stored winner of this signature, or ``None``.  A signature with in-kernel spherical harmonics shares the
-    entry of the same signature without them (the consumer code is identical)."""
+    entry of the same signature without them (the consumer code is identical).  Answers are memoised: the database
+    key hashes the whole path table, which must not happen on every operator call."""
+    memo = (spec, direction, tuple(bool(n) for n in needs))
+    if memo in _LOOKUPS:
+        return _LOOKUPS[memo]
+    out = _LOOKUPS[memo] = _lookup(spec, direction, needs)
+    return out
+
+
+def _lookup(spec: U1DSpec, direction: str, needs) -> Optional[_emit.Tuning]:
     db = load_db()
     for sp in (spec, dataclasses.replace(spec, y_sh=()) if spec.y_sh else None):
         if sp is None:
