@@ -256,6 +256,30 @@ def halo_model_bench(args, dev, rank, world, dist):
         replay = dict(checksums(o2), ms_per_step=float(msr[0]) / k, value=b.n_nodes * k / (float(msr[0]) * 1e-3), unit="atom-steps/s")
     else:
         replay = {"failed": why or "capture failed on another rank"}
+    breakdown = None
+    if getattr(args, "breakdown", False):
+        # rank 0's device time of an eager step by kernel family (every rank profiles, so that all stay in step)
+        from torch.profiler import ProfilerActivity, profile
+        n_prof = 5
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(n_prof):
+                run()
+            torch.cuda.synchronize()
+        fam = {"tensor product (fasteq_u1d_*)": 0.0, "NCCL": 0.0, "tcgen05 GEMMs + radial chain": 0.0, "gate": 0.0, "edge geometry": 0.0,
+               "framework kernels (pack / unpack, adds, fills, reductions)": 0.0}
+        launches = 0
+        for e in prof.key_averages():
+            if e.device_type.name != "CUDA" or e.device_time_total <= 0:
+                continue
+            name, t_us = e.key, e.device_time_total / n_prof
+            launches += e.count
+            key = ("tensor product (fasteq_u1d_*)" if "fasteq_u1d" in name else "NCCL" if "nccl" in name.lower() else
+                   "tcgen05 GEMMs + radial chain" if ("gemm_tf32x3" in name or "radial_chain" in name or "eqlinear" in name or "pack_weights" in name) else
+                   "gate" if "gate" in name else "edge geometry" if "edge_geometry" in name else
+                   "framework kernels (pack / unpack, adds, fills, reductions)")
+            fam[key] += t_us
+        breakdown = {"device_us_per_step": {k_: round(v, 1) for k_, v in fam.items()}, "device_us_total": round(sum(fam.values()), 1),
+                     "launches_per_step": launches / n_prof, "rank": rank, "note": "eager step, torch profiler (CUPTI kernel records)"}
     eager_ms = float(ms[0]) / k
     # the block's figure: the replayed step where the capture succeeded and reproduces the eager checksums (a molecular-dynamics
     # run replays between neighbour-list rebuilds), else the eager step; both are printed
@@ -265,7 +289,7 @@ def halo_model_bench(args, dev, rank, world, dist):
     return {"metric": "NequIP-style atom-steps/s, one 20,000-atom graph, receiver-range partition + halo", "scaling": "strong",
             "value": b.n_nodes / (best_ms * 1e-3), "unit": "atom-steps/s", "ms_per_step": best_ms,
             "mode": "cuda_graph_replay" if (replay_ok and replay["ms_per_step"] < eager_ms) else "eager",
-            "eager_ms_per_step": eager_ms, "eager_exchange": "all-gather of padded export slabs (least host work)" if world > 1 else None,
+            "breakdown": breakdown, "eager_ms_per_step": eager_ms, "eager_exchange": "all-gather of padded export slabs (least host work)" if world > 1 else None,
             "energy": chk["energy"], "force_l2": chk["force_l2"], "force_l1": chk["force_l1"], "cuda_graph_replay": replay,
             "replay_exchange": ("per layer one variable-size all-to-all to the ranks that read this rank's rows (forward) and back "
                                 "(force pass), captured with the kernels") if world > 1 else None,
@@ -736,6 +760,8 @@ def main():
     ap.add_argument("--no-halo", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the fixed batch of 1024 structures (configuration 4)")
     ap.add_argument("--no-sustained", action="store_true", help="skip the > 1 s repeat of the headline loop")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="with --only single_graph: rank 0's device time per step by kernel family (torch profiler, CUPTI)")
     ap.add_argument("--only", default=None, choices=["operators", "other_signature", "config2", "fixed_batch", "single_graph", "model"],
                     help="run one of the side blocks alone and print its JSON (for profiling a block under ncu)")
     args = ap.parse_args()
