@@ -45,47 +45,51 @@ template <typename T> __device__ __forceinline__ T act_d(int code, T x) {
   }
 }
 
+// One thread per (node, channel): it walks the row's segments, so the index arithmetic (one 64-bit division) and each
+// gate's activation are paid once per thread instead of once per element, and every element is touched exactly once.
+// Consecutive threads hold consecutive channels: each segment access of a warp is one contiguous 128-byte line.
 template <typename T>
-__global__ void gate_fwd_kernel(const T* __restrict__ x, T* __restrict__ out, long long batch, int u, const __grid_constant__ GateTable t) {
-  const long long total = batch * t.n_out * u;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)(i % u);
-    const int so = (int)((i / u) % t.n_out);
-    const long long b = i / ((long long)u * t.n_out);
-    const T* row = x + (size_t)b * t.n_in * u;
-    if (so < t.n_scalar) {
-      out[i] = T(t.cst[so]) * act_f<T>(t.act[so], row[(size_t)so * u + c]);
-    } else {
-      const int si = so + t.n_gate;                 // gated input segment
-      const int g = t.gate_of[si];
-      out[i] = T(t.cst[g]) * act_f<T>(t.act[g], row[(size_t)g * u + c]) * row[(size_t)si * u + c];
-    }
+__global__ void __launch_bounds__(256) gate_fwd_kernel(const T* __restrict__ x, T* __restrict__ out, long long batch, int u,
+                                                       const __grid_constant__ GateTable t) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= batch * u) return;
+  const long long b = i / u;
+  const int c = (int)(i - b * u);
+  const T* row = x + (size_t)b * t.n_in * u + c;
+  T* orow = out + (size_t)b * t.n_out * u + c;
+  for (int s = 0; s < t.n_scalar; ++s) orow[(size_t)s * u] = T(t.cst[s]) * act_f<T>(t.act[s], row[(size_t)s * u]);
+  for (int k = 0; k < t.n_gate; ++k) {
+    const int g = t.n_scalar + k;
+    const T a = T(t.cst[g]) * act_f<T>(t.act[g], row[(size_t)g * u]);
+    const int s0 = t.first_gated[g];
+    for (int m = 0; m < t.n_gated[g]; ++m) orow[(size_t)(s0 + m - t.n_gate) * u] = a * row[(size_t)(s0 + m) * u];
   }
 }
 
 template <typename T>
-__global__ void gate_bwd_kernel(const T* __restrict__ x, const T* __restrict__ go, T* __restrict__ gx, long long batch, int u,
-                                const __grid_constant__ GateTable t) {
-  const long long total = batch * t.n_in * u;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)(i % u);
-    const int si = (int)((i / u) % t.n_in);
-    const long long b = i / ((long long)u * t.n_in);
-    const T* row = x + (size_t)b * t.n_in * u;
-    const T* grow = go + (size_t)b * t.n_out * u;
-    if (si < t.n_scalar) {
-      gx[i] = grow[(size_t)si * u + c] * T(t.cst[si]) * act_d<T>(t.act[si], row[(size_t)si * u + c]);
-    } else if (si < t.n_scalar + t.n_gate) {
-      T acc = T(0);
-      for (int m = 0; m < t.n_gated[si]; ++m) {
-        const int sg = t.first_gated[si] + m;
-        acc += grow[(size_t)(sg - t.n_gate) * u + c] * row[(size_t)sg * u + c];
-      }
-      gx[i] = acc * T(t.cst[si]) * act_d<T>(t.act[si], row[(size_t)si * u + c]);
-    } else {
-      const int g = t.gate_of[si];
-      gx[i] = grow[(size_t)(si - t.n_gate) * u + c] * T(t.cst[g]) * act_f<T>(t.act[g], row[(size_t)g * u + c]);
+__global__ void __launch_bounds__(256) gate_bwd_kernel(const T* __restrict__ x, const T* __restrict__ go, T* __restrict__ gx,
+                                                       long long batch, int u, const __grid_constant__ GateTable t) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= batch * u) return;
+  const long long b = i / u;
+  const int c = (int)(i - b * u);
+  const T* row = x + (size_t)b * t.n_in * u + c;
+  const T* grow = go + (size_t)b * t.n_out * u + c;
+  T* gxr = gx + (size_t)b * t.n_in * u + c;
+  for (int s = 0; s < t.n_scalar; ++s)
+    gxr[(size_t)s * u] = grow[(size_t)s * u] * T(t.cst[s]) * act_d<T>(t.act[s], row[(size_t)s * u]);
+  for (int k = 0; k < t.n_gate; ++k) {
+    const int g = t.n_scalar + k;
+    const T xg = row[(size_t)g * u];
+    const T a = T(t.cst[g]) * act_f<T>(t.act[g], xg);
+    const int s0 = t.first_gated[g];
+    T acc = T(0);
+    for (int m = 0; m < t.n_gated[g]; ++m) {
+      const T gv = grow[(size_t)(s0 + m - t.n_gate) * u];
+      acc += gv * row[(size_t)(s0 + m) * u];
+      gxr[(size_t)(s0 + m) * u] = gv * a;
     }
+    gxr[(size_t)g * u] = acc * T(t.cst[g]) * act_d<T>(t.act[g], xg);
   }
 }
 
@@ -177,8 +181,9 @@ extern "C" int fasteq_gate_forward(const fasteq_gate_problem* p, const void* x, 
   if (rc != FASTEQ_OK) return rc;
   if (p->batch == 0) return FASTEQ_OK;
   if (!x || !out) return FASTEQ_INVALID;
-  const long long total = p->batch * t.n_out * p->u;
-  const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
+  const long long total = p->batch * p->u;                     // one thread per (node, channel)
+  if ((total + 255) / 256 > 0x7fffffffLL) return FASTEQ_UNSUPPORTED;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
   if (p->dtype == FASTEQ_F32) gate_fwd_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)x, (float*)out, p->batch, p->u, t);
   else gate_fwd_kernel<double><<<blocks, 256, 0, (cudaStream_t)stream>>>((const double*)x, (double*)out, p->batch, p->u, t);
   cudaError_t e = cudaGetLastError();
@@ -191,8 +196,9 @@ extern "C" int fasteq_gate_backward(const fasteq_gate_problem* p, const void* x,
   if (rc != FASTEQ_OK) return rc;
   if (p->batch == 0) return FASTEQ_OK;
   if (!x || !grad_out || !grad_x) return FASTEQ_INVALID;
-  const long long total = p->batch * t.n_in * p->u;
-  const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
+  const long long total = p->batch * p->u;                     // one thread per (node, channel)
+  if ((total + 255) / 256 > 0x7fffffffLL) return FASTEQ_UNSUPPORTED;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
   if (p->dtype == FASTEQ_F32) gate_bwd_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)x, (const float*)grad_out, (float*)grad_x, p->batch, p->u, t);
   else gate_bwd_kernel<double><<<blocks, 256, 0, (cudaStream_t)stream>>>((const double*)x, (const double*)grad_out, (double*)grad_x, p->batch, p->u, t);
   cudaError_t e = cudaGetLastError();
