@@ -1,4 +1,5 @@
-// SO3Linear (eqlinear) forward and grad_x as one grouped GEMM kernel, FP32 / FP64 FMA path.
+// SO3Linear (eqlinear) forward and grad_x as one grouped GEMM kernel: FP32 on the FMA pipe, FP64 on the tensor cores
+// (DMMA) with the FMA kernel as the path for odd extents and unaligned operands.
 //
 //   C[b, c_row[g] + t, :] = sum_{q in group g} coeff[q] * A[b, a_row[q] + t, :] @ op(W[q])
 //
@@ -35,7 +36,7 @@ struct GroupTable {
   float path_coeff_f[kMaxPaths];
   double path_coeff_d[kMaxPaths];
   long long tile_first[kMaxPaths + 1];  // prefix of row tiles per group
-  long long wide_tile_first[kMaxPaths + 1];  // the same for 128-row tiles
+  long long wide_tile_first[kMaxPaths + 1];  // the same for the 128-row tiles of the FP64 tensor-core kernel
 };
 
 template <typename T> __device__ __forceinline__ T coeff_of(const GroupTable& t, int q);
@@ -150,119 +151,200 @@ __global__ void __launch_bounds__(NT) eqlinear_kernel(const __grid_constant__ Gr
 }
 
 // ------------------------------------------------------------------------------------------------
-// FP64 variant with a 128 x 128 tile and 8 x 8 outputs per thread: the 64 x 64 kernel above spends two
-// shared-memory wavefronts per FMA wavefront in FP64 (4 x 4 outputs per 8 operand loads), this one a
-// quarter of that.  A thread owns rows {32 i + 2 ty + r} and columns {32 j + 2 tx + c} (i, j < 4; r, c < 2),
-// so that every operand load is one conflict-free 16-byte access per quarter warp.  Global tiles are
-// fetched one step ahead into registers.  Plain (non-blocked) summation: FP64 has the head-room.
-constexpr int WM = 128, WN = 128, WK = 8;
+// FP64 on the tensor cores: the same grouped product with mma.sync m8n8k4 (DMMA), the FP64 tensor path of this part
+// (tcgen05 has no FP64 kind; the reference's FP64 back-end is DMMA as well,
+// fasteq/cuda/src/eqlinear/backends/fp64/direct_gemm_f64_tma.cu:204).  CTA tile 128 x 64, eight warps of 32 x 32
+// (sixteen 8 x 8 accumulator tiles = 32 doubles per thread), two CTAs per SM so that one CTA's stores overlap the
+// other's products.  Operands stream global -> shared memory through a four-stage cp.async ring of 8-wide k-steps
+// (16-byte copies, zero fill outside the problem), one barrier per step.
+//
+// A CTA owns one 128-row tile and a range of 64-column blocks.  When the tile's whole reduction (paths x K) is at most
+// 64 wide, its A operand stays in shared memory across the column blocks ("stationary": the radial MLP's last layer
+// multiplies [E, 64] by [64, 4352], so each row of A is read from HBM once instead of 68 times) and only W tiles (L2
+// resident) move through the ring; otherwise A streams through the ring as well.
+//
+// Shared-memory pitches are 4 or 12 (mod 16) doubles, so the sixteen 8-byte fragment loads of a half warp hit sixteen
+// different banks.  Fragment layout of m8n8k4.f64: a = A[lane / 4][lane % 4], b = B[lane % 4][lane / 4],
+// c0, c1 = C[lane / 4][2 (lane % 4) + {0, 1}].  The path coefficient multiplies the A fragments, or the accumulators
+// in the epilogue when all paths of the group share it.
+constexpr int DM = 128, DN = 64, DK = 8, DS = 4;
+constexpr int PA = DK + 4;                      // pitch of a streamed A buffer [row][k] and of a transposed W buffer [n][k]
+constexpr int PW = DN + 4;                      // pitch of a W buffer [k][n]
+constexpr int W_BUF = DK * PW > DN * PA ? DK * PW : DN * PA;
+constexpr int DMMA_MAX_STATIONARY_STEPS = 8;
+
+__device__ __forceinline__ void dmma_8x8x4(double (&c)[2], double a, double b) {
+  asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};"
+               : "+d"(c[0]), "+d"(c[1]) : "d"(a), "d"(b));
+}
+// 16-byte asynchronous copy; `bytes` (0 or 16) of the source are read, the rest of the destination is zero
+__device__ __forceinline__ void cp_async16(double* smem_dst, const double* gmem_src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
 
 template <bool TRANS>
-__global__ void __launch_bounds__(NT) eqlinear_wide_f64_kernel(const __grid_constant__ GroupTable tab, const double* __restrict__ A,
-                                                               const double* __restrict__ W, double* __restrict__ C, long long batch,
-                                                               int a_rows_per_b, int c_rows_per_b, int K, int N, int u, int v) {
-  __shared__ double sA[2][WK][WM + 2];
-  __shared__ double sW[2][WK][WN + 2];
-  const long long tile = blockIdx.x;
+__global__ void __launch_bounds__(NT, 2) eqlinear_dmma_f64_kernel(const __grid_constant__ GroupTable tab, const double* __restrict__ A,
+                                                                  const double* __restrict__ W, double* __restrict__ C, long long batch,
+                                                                  int a_rows_per_b, int c_rows_per_b, int K, int N, int u, int v,
+                                                                  int col_splits, int stationary) {
+  extern __shared__ __align__(16) double dsm[];
+  const long long tile = blockIdx.x / col_splits;
+  const int split = blockIdx.x % col_splits;
   int g = 0;
   while (g + 1 < tab.n_groups && tile >= tab.wide_tile_first[g + 1]) ++g;
-  const long long row0 = (tile - tab.wide_tile_first[g]) * WM;
+  const long long row0 = (tile - tab.wide_tile_first[g]) * DM;
   const int gi = tab.group_rows[g];
   const long long n_rows = batch * gi;
-  const int n0 = blockIdx.y * WN;
-  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
-  double acc[8][8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[i][j] = 0.0;
-
-  // A loader: thread -> (row = tid / 2, four consecutive k starting at 4 * (tid % 2))
-  const int lrow = threadIdx.x / 2, lk = (threadIdx.x % 2) * 4;
-  const long long ar = row0 + lrow;
-  const bool avalid = ar < n_rows;
-  const size_t abase = avalid ? ((size_t)(ar / gi) * a_rows_per_b + (size_t)(ar % gi)) * (size_t)K : 0;
-  // W loader: TRANS (W used as [k = v index][n = u index], contiguous in k): like A; else contiguous in n
-  const int wn_t = threadIdx.x / 2, wk_t = (threadIdx.x % 2) * 4;     // TRANS
-  const int wk_n = threadIdx.x / 32, wn_n = (threadIdx.x % 32) * 4;   // not TRANS
-
   const int q0 = tab.group_first[g], q1 = tab.group_first[g + 1];
-  const int k_steps = (K + WK - 1) / WK;
-  const int total_steps = (q1 - q0) * k_steps;
-  double ra[4], rw[4];
-  auto fetch = [&](int step) {
-    const int q = q0 + step / k_steps, k0 = (step % k_steps) * WK;
+  const int k_steps = (K + DK - 1) / DK;
+  const int tile_steps = (q1 - q0) * k_steps;
+  const int ncb = (N + DN - 1) / DN, per = (ncb + col_splits - 1) / col_splits;
+  const int cb0 = split * per, cb1 = min(ncb, cb0 + per);
+  if (cb0 >= cb1 || tile_steps == 0) return;
+  const int total = (cb1 - cb0) * tile_steps;
+  const int pitch_a = stationary ? tile_steps * DK + 4 : PA;
+  double* sA = dsm;
+  double* sW = dsm + (stationary ? DM * pitch_a : DS * DM * PA);
+
+  bool uniform = true;
+  for (int q = q0 + 1; q < q1; ++q) uniform = uniform && tab.path_coeff_d[q] == tab.path_coeff_d[q0];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = (warp & 3) * 32, wn = (warp >> 2) * 32;      // this warp's 32 x 32 corner of the tile
+  const int fg = lane >> 2, ft = lane & 3;
+
+  // copy roles.  A step: 128 rows x 4 chunks of two doubles, two chunks per thread (rows tid / 4 and 64 + tid / 4).
+  const int a_kc = (tid & 3) * 2;
+  size_t a_off[2];
+  bool a_ok[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const long long ar = row0 + (tid >> 2) + 64 * e;
+    a_ok[e] = ar < n_rows;
+    a_off[e] = a_ok[e] ? ((size_t)(ar / gi) * a_rows_per_b + (size_t)(ar % gi)) * (size_t)K : 0;
+  }
+  // W step: one chunk per thread; [n][k] rows of the stored block when TRANS, else [k][n]
+  const int w_r = TRANS ? (tid >> 2) : (tid >> 5);          // n (TRANS) or k
+  const int w_c = TRANS ? (tid & 3) * 2 : (tid & 31) * 2;   // k (TRANS) or n
+
+  int i_cbl = 0, i_step = 0, i_q = q0, i_k0 = 0;            // the step the next issue() loads
+  auto issue = [&](int flat) {
+    if (flat < total) {
+      if (!stationary || i_cbl == 0) {
+        double* dst = stationary ? sA + i_step * DK : sA + (flat % DS) * (DM * PA);
+        const double* aq = A + (size_t)tab.path_a_row[i_q] * K + i_k0 + a_kc;
+        const bool kin = i_k0 + a_kc < K;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const bool ok = a_ok[e] && kin;
+          cp_async16(dst + ((tid >> 2) + 64 * e) * pitch_a + a_kc, ok ? aq + a_off[e] : A, ok ? 16 : 0);
+        }
+      }
+      double* wd = sW + (flat % DS) * W_BUF;
+      const double* wq = W + (size_t)tab.path_w[i_q] * u * v;
+      const int n0 = (cb0 + i_cbl) * DN;
+      if (TRANS) {
+        const bool ok = n0 + w_r < N && i_k0 + w_c < K;
+        cp_async16(wd + w_r * PA + w_c, ok ? wq + (size_t)(n0 + w_r) * v + i_k0 + w_c : W, ok ? 16 : 0);
+      } else {
+        const bool ok = i_k0 + w_r < K && n0 + w_c < N;
+        cp_async16(wd + w_r * PW + w_c, ok ? wq + (size_t)(i_k0 + w_r) * v + n0 + w_c : W, ok ? 16 : 0);
+      }
+      i_k0 += DK;
+      if (i_k0 >= K) { i_k0 = 0; ++i_q; }
+      if (++i_step == tile_steps) { i_step = 0; i_q = q0; ++i_cbl; }
+    }
+    cp_async_commit();
+  };
+
+  double acc[4][4][2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+
+#pragma unroll
+  for (int s = 0; s < DS - 1; ++s) issue(s);
+  int cbl = 0, step = 0, q = q0, k0 = 0;
+  for (int flat = 0; flat < total; ++flat) {
+    cp_async_wait<DS - 2>();
+    __syncthreads();                     // step `flat` has landed for every thread; the buffer of step flat - 1 is free
+    issue(flat + DS - 1);
+    const double* as = (stationary ? sA + step * DK : sA + (flat % DS) * (DM * PA)) + (wm + fg) * pitch_a + ft;
+    const double* ws = sW + (flat % DS) * W_BUF + (TRANS ? (wn + fg) * PA + ft : ft * PW + wn + fg);
     const double cq = tab.path_coeff_d[q];
-    const double* aq = A + (size_t)tab.path_a_row[q] * K;
-    const double* wq = W + (size_t)tab.path_w[q] * u * v;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int k = k0 + lk + e;
-      ra[e] = (avalid && k < K) ? cq * aq[abase + k] : 0.0;       // the path coefficient rides on the A operand
-    }
-    if (TRANS) {
+    for (int kk = 0; kk < DK; kk += 4) {
+      double a[4], b[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int k = k0 + wk_t + e, n = n0 + wn_t;
-        rw[e] = (k < K && n < N) ? wq[(size_t)n * v + k] : 0.0;
+      for (int i = 0; i < 4; ++i) a[i] = as[8 * i * pitch_a + kk];
+      if (!uniform) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] *= cq;
       }
-    } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int k = k0 + wk_n, n = n0 + wn_n + e;
-        rw[e] = (k < K && n < N) ? wq[(size_t)k * v + n] : 0.0;
-      }
+      for (int j = 0; j < 4; ++j) b[j] = TRANS ? ws[8 * j * PA + kk] : ws[kk * PW + 8 * j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dmma_8x8x4(acc[i][j], a[i], b[j]);
     }
-  };
-  auto stash = [&](int buf) {
-#pragma unroll
-    for (int e = 0; e < 4; ++e) sA[buf][lk + e][lrow] = ra[e];
-    if (TRANS) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) sW[buf][wk_t + e][wn_t] = rw[e];
-    } else {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) sW[buf][wk_n][wn_n + e] = rw[e];
-    }
-  };
-  if (total_steps > 0) { fetch(0); stash(0); }
-  __syncthreads();
-  for (int step = 0; step < total_steps; ++step) {
-    const int buf = step & 1;
-    if (step + 1 < total_steps) fetch(step + 1);
-#pragma unroll
-    for (int k = 0; k < WK; ++k) {
-      double a[8], b[8];
+    k0 += DK;
+    if (k0 >= K) { k0 = 0; ++q; }
+    if (++step == tile_steps) {
+      const double scale = uniform ? tab.path_coeff_d[q0] : 1.0;
+      const int n0 = (cb0 + cbl) * DN;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const double2 t = *reinterpret_cast<const double2*>(&sA[buf][k][32 * i + 2 * ty]);
-        a[2 * i] = t.x; a[2 * i + 1] = t.y;
+        const long long rr = row0 + wm + 8 * i + fg;
+        double* crow = C + ((size_t)(rr / gi) * c_rows_per_b + tab.group_c_row[g] + (int)(rr % gi)) * (size_t)N;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int n = n0 + wn + 8 * j + 2 * ft;      // even, and N is even: n < N covers n + 1
+          if (rr < n_rows && n < N) *reinterpret_cast<double2*>(crow + n) = make_double2(scale * acc[i][j][0], scale * acc[i][j][1]);
+          acc[i][j][0] = acc[i][j][1] = 0.0;
+        }
       }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const double2 t = *reinterpret_cast<const double2*>(&sW[buf][k][32 * j + 2 * tx]);
-        b[2 * j] = t.x; b[2 * j + 1] = t.y;
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = fma(a[i], b[j], acc[i][j]);
-    }
-    if (step + 1 < total_steps) stash(buf ^ 1);
-    __syncthreads();
-  }
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const long long rr = row0 + 32 * (i / 2) + 2 * ty + (i & 1);
-    if (rr >= n_rows) continue;
-    double* crow = C + ((size_t)(rr / gi) * c_rows_per_b + tab.group_c_row[g] + (int)(rr % gi)) * (size_t)N;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int n = n0 + 32 * j + 2 * tx;
-      if (n + 1 < N) *reinterpret_cast<double2*>(crow + n) = make_double2(acc[i][2 * j], acc[i][2 * j + 1]);
-      else if (n < N) crow[n] = acc[i][2 * j];
+      step = 0; q = q0; ++cbl;
     }
   }
+  cp_async_wait<0>();
+}
+
+// Launch geometry of the DMMA kernel: stationary A when every group's reduction fits, column blocks split over CTAs
+// only as far as needed to fill the device twice over.
+template <bool TRANS>
+int launch_dmma(const GroupTable& tab, const fasteq_eqlinear_problem* p, const double* a, const double* w, double* c, int a_rows, int c_rows,
+                int K, int N, cudaStream_t s) {
+  const long long wt = tab.wide_tile_first[tab.n_groups];
+  if (wt == 0) return FASTEQ_OK;
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  const int k_steps = (K + DK - 1) / DK, ncb = (N + DN - 1) / DN;
+  int max_steps = 0;
+  for (int g = 0; g < tab.n_groups; ++g) max_steps = std::max(max_steps, (tab.group_first[g + 1] - tab.group_first[g]) * k_steps);
+  const int stationary = max_steps <= DMMA_MAX_STATIONARY_STEPS ? 1 : 0;
+  const long long want = (2LL * sms + wt - 1) / wt;
+  const int col_splits = (int)std::min<long long>(ncb, std::max<long long>(1, want));
+  if (wt * col_splits > 0x7fffffffLL) return FASTEQ_UNSUPPORTED;
+  const size_t smem = sizeof(double) * ((stationary ? (size_t)DM * (max_steps * DK + 4) : (size_t)DS * DM * PA) + (size_t)DS * W_BUF);
+  static bool raised[64] = {};
+  if (dev < 64 && !raised[dev]) {
+    e = cudaFuncSetAttribute(eqlinear_dmma_f64_kernel<TRANS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)(sizeof(double) * ((size_t)DM * (DMMA_MAX_STATIONARY_STEPS * DK + 4) + (size_t)DS * W_BUF)));
+    if (e != cudaSuccess) return cuda_fail(e);
+    raised[dev] = true;
+  } else if (dev >= 64) {
+    return FASTEQ_UNSUPPORTED;
+  }
+  eqlinear_dmma_f64_kernel<TRANS><<<(unsigned)(wt * col_splits), NT, smem, s>>>(tab, a, w, c, p->batch, a_rows, c_rows, K, N, p->u, p->v,
+                                                                               col_splits, stationary);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
 }
 
 // Rows of C that no group writes must read as zero.  The uncovered rows form at most n_groups + 1 runs; every
@@ -352,14 +434,11 @@ int launch(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const vo
   const int K = dgrad ? p->v : p->u, N = dgrad ? p->u : p->v;
   const int a_rows = dgrad ? p->out_rows : p->in_rows, c_rows = dgrad ? p->in_rows : p->out_rows;
   if (!covers) zero_uncovered_rows<T>((T*)c, p->batch, c_rows, N, tab, s);
-  if (sizeof(T) == 8 && N >= 64 && (N % 2) == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) == 0) {
-    const long long wt = tab.wide_tile_first[tab.n_groups];
-    if (wt > 0x7fffffffLL) return FASTEQ_UNSUPPORTED;
-    dim3 wgrid((unsigned)wt, (unsigned)((N + WN - 1) / WN));
-    if (dgrad) eqlinear_wide_f64_kernel<true><<<wgrid, NT, 0, s>>>(tab, (const double*)a, (const double*)w, (double*)c, p->batch, a_rows, c_rows, K, N, p->u, p->v);
-    else       eqlinear_wide_f64_kernel<false><<<wgrid, NT, 0, s>>>(tab, (const double*)a, (const double*)w, (double*)c, p->batch, a_rows, c_rows, K, N, p->u, p->v);
-    cudaError_t we = cudaGetLastError();
-    return we == cudaSuccess ? FASTEQ_OK : cuda_fail(we);
+  if (sizeof(T) == 8 && N >= 8 && (N % 2) == 0 && (K % 2) == 0 &&
+      ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(c)) & 15u) == 0) {
+    // FP64 on the tensor cores (DMMA); its 16-byte copies need even K and N and 16-byte aligned operands
+    return dgrad ? launch_dmma<true>(tab, p, (const double*)a, (const double*)w, (double*)c, a_rows, c_rows, K, N, s)
+                 : launch_dmma<false>(tab, p, (const double*)a, (const double*)w, (double*)c, a_rows, c_rows, K, N, s);
   }
   const long long tiles = tab.tile_first[tab.n_groups];
   if (tiles > 0x7fffffffLL) return FASTEQ_UNSUPPORTED;
