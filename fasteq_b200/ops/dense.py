@@ -2,11 +2,11 @@
 
 FP32 data: tcgen05 tensor cores with 3xTF32 arithmetic (relative error near 1e-6); the gradient with respect
 to ``x`` uses the same kernel.  FP64 data, FP32 shapes the tensor-core kernel does not take (a dimension that is
-not a multiple of four, operands that are not 16-byte aligned) and every weight gradient go through the FMA tile
-kernels of the SO3Linear family: a plain GEMM is its one-path, one-row case (``fasteq_eqlinear_forward`` /
-``_dgrad`` / ``_wgrad`` with ``u = K``, ``v = N``), so no library GEMM is called on CUDA tensors.  The reference
-has persistent DMMA kernels for the FP64 case (fasteq/cuda/src/eqlinear/backends/fp64/direct_gemm_f64_tma.cu:204);
-on B200 FP64 tensor and vector peaks are equal, and the 128 x 128 FP64 FMA tile kernel is used instead.
+not a multiple of four, operands that are not 16-byte aligned) and every weight gradient go through the kernels of
+the SO3Linear family: a plain GEMM is its one-path, one-row case (``fasteq_eqlinear_forward`` / ``_dgrad`` /
+``_wgrad`` with ``u = K``, ``v = N``), so no library GEMM is called on CUDA tensors.  FP64 forward and grad_x with
+even extents run on the FP64 tensor cores (DMMA, as the reference's FP64 back-end does:
+fasteq/cuda/src/eqlinear/backends/fp64/direct_gemm_f64_tma.cu:204); the rest run on FMA tile kernels.
 CPU tensors (the oracle's territory) fall through to ``torch.matmul``.
 """
 from __future__ import annotations
@@ -58,7 +58,7 @@ def _fma_call(name: str, prob, p0, p1, out) -> None:
 
 
 def _fma_gemm(a: torch.Tensor, w_kn: torch.Tensor) -> torch.Tensor:
-    """``a [M, K] @ w_kn [K, N]`` on the FP32 / FP64 FMA tile kernel (the one-path SO3Linear)."""
+    """``a [M, K] @ w_kn [K, N]`` on the one-path SO3Linear kernels (FP32: FMA tiles; FP64: DMMA, or FMA tiles for odd extents)."""
     a, w_kn = a.contiguous(), w_kn.contiguous()
     M, K = a.shape
     out = torch.empty((M, w_kn.shape[1]), dtype=a.dtype, device=a.device)
@@ -88,7 +88,7 @@ def _fma_wgrad(x: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
 
 
 def _matmul_nt(a: torch.Tensor, bt: torch.Tensor) -> torch.Tensor:
-    """``a [M, K] @ bt[N, K]^T`` on this library's FMA kernels (CUDA) or torch (CPU)."""
+    """``a [M, K] @ bt[N, K]^T`` on this library's one-path SO3Linear kernels (CUDA) or torch (CPU)."""
     if a.is_cuda and a.dtype in (torch.float32, torch.float64) and a.dtype == bt.dtype:
         return _fma_gemm(a, bt.t())
     return a @ bt.t()
@@ -191,7 +191,7 @@ def dense(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 
 
 class _DenseFMA(torch.autograd.Function):
-    """``y = x W^T`` on the FP32 / FP64 FMA tile kernels, differentiable to every order (each gradient is
+    """``y = x W^T`` on the one-path SO3Linear kernels (FP32 FMA tiles, FP64 DMMA), differentiable to every order (each gradient is
     another call of ``dense`` / the row reduction, which autograd differentiates again)."""
 
     @staticmethod

@@ -229,7 +229,7 @@ int fasteq_neighbors_fill(const fasteq_nl_problem* p /* host */, void* work, int
 typedef enum fasteq_eqlinear_precision {
   FASTEQ_EQLIN_TF32X3 = 0,   /* FP32 data, 3xTF32 split on tensor cores (error < 2e-5 rel. Frobenius) */
   FASTEQ_EQLIN_FP32 = 1,     /* FP32 data, FP32 FMA */
-  FASTEQ_EQLIN_FP64 = 2      /* FP64 data, FP64 FMA */
+  FASTEQ_EQLIN_FP64 = 2      /* FP64 data: DMMA (even extents, 16-byte aligned operands) or FP64 FMA */
 } fasteq_eqlinear_precision;
 
 typedef struct fasteq_eqlinear_problem {

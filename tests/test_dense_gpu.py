@@ -74,11 +74,13 @@ def test_dense_second_order():
         assert _rel(a, b) <= 1e-5
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 64, 8), (777, 64, 64), (1500, 4352, 64), (300, 70, 33)])
+@pytest.mark.parametrize("M,N,K", [(1, 64, 8), (777, 64, 64), (1500, 4352, 64), (300, 70, 33), (130, 26, 10), (4000, 72, 200)])
 def test_float64_dense_runs_on_the_library_kernels(M, N, K, monkeypatch):
-    """FP64 (benchmark configuration 2's radial MLP): forward, both gradients and a second-order term on the FP64 FMA
-    kernels behind ``fasteq_eqlinear_forward / _dgrad / _wgrad`` -- no library GEMM: ``torch.matmul`` is made to fail
-    for CUDA operands while the layer runs."""
+    """FP64 (benchmark configuration 2's radial MLP): forward, both gradients and a second-order term on the kernels
+    behind ``fasteq_eqlinear_forward / _dgrad / _wgrad`` -- no library GEMM: ``torch.matmul`` is made to fail for CUDA
+    operands while the layer runs.  Even extents take the tensor-core (DMMA) kernel: a reduction of at most 64 keeps
+    the A tile in shared memory across column blocks (1500 x 4352 x 64 forward), longer ones stream it (the same
+    case's grad_x with K = 4352, and K = 200 with a partial column block); odd extents take the FMA kernel."""
     from fasteq_b200.ops import dense as dmod
     g = torch.Generator().manual_seed(M + N)
     x = torch.randn(M, K, generator=g, dtype=torch.float64)
