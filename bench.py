@@ -59,9 +59,10 @@ def algorithmic_bytes(N, E, d, s):
     return fwd, bwd
 
 
-def fp32_floor(spec, tun, direction, needs, E, U, launch_s, dev, sm_mhz=None):
-    """FP32-pipe view of a CWTP kernel: arithmetic instructions per (edge, channel) counted in the generated source, the
-    time they need at 128 lanes per SM per clock, and the share of that rate the launch reached."""
+def fp32_floor(spec, tun, direction, needs, E, U, launch_s, dev, sm_mhz=None, lanes=128, tag="fp32"):
+    """Arithmetic-pipe view of a CWTP kernel: arithmetic instructions per (edge, channel) counted in the generated source,
+    the time they need at ``lanes`` per SM per clock (128 for FP32, 64 for FP64), and the share of that rate the launch
+    reached."""
     from fasteq_b200.codegen import u1d as gen
     ops = gen.arith_ops(spec, tun, direction, needs)
     n = ops["fma"] + ops["mul"] + ops["add"]
@@ -71,9 +72,9 @@ def fp32_floor(spec, tun, direction, needs, E, U, launch_s, dev, sm_mhz=None):
             sm_mhz = float(torch.cuda.clock_rate())
         except Exception:
             sm_mhz = 1965.0
-    floor_s = float(E) * U * n / (sms * 128 * sm_mhz * 1e6)
-    return {"fp32_ops_per_edge_channel": n, "fma": ops["fma"], "mul": ops["mul"], "fp32_floor_ms": floor_s * 1e3,
-            "fp32_pipe_utilisation": floor_s / launch_s, "sm_mhz": sm_mhz}
+    floor_s = float(E) * U * n / (sms * lanes * sm_mhz * 1e6)
+    return {f"{tag}_ops_per_edge_channel": n, "fma": ops["fma"], "mul": ops["mul"], f"{tag}_floor_ms": floor_s * 1e3,
+            f"{tag}_pipe_utilisation": floor_s / launch_s, "sm_mhz": sm_mhz}
 
 
 def measured_peak():
@@ -553,8 +554,8 @@ def cwtp_kernel_block(workload: str, dev, seed: int = 0):
                             "two_pass": t.two_pass} for dr, t in tun.items()}}
 
 
-def config2_bench(dev):
-    """benchmark configuration 2 at its stated size: 32 periodic boxes x 384 atoms (side 15.6 A, cutoff 5 A), hidden
+def config2_bench(dev, boxes=None):
+    """benchmark configuration 2 at its stated size (``boxes`` shrinks it for a profiler capture): 32 periodic boxes x 384 atoms (side 15.6 A, cutoff 5 A), hidden
     256x0e+256x1o+256x2e, SH l <= 3, correlation 3, 2 layers, FP64, energy + forces.  Also the FP64 tensor-product
     kernels of the second interaction layer alone against the HBM roofline."""
     from fasteq_b200.graph import make_boxes
@@ -565,7 +566,7 @@ def config2_bench(dev):
     model = MACEStyleModel(channels=256, hidden_lmax=2).double().to(dev)
     for prm in model.parameters():
         prm.requires_grad_(False)
-    b = make_boxes(32, 384, 15.6, 5.0, 4, seed=0)
+    b = make_boxes(boxes or 32, 384, 15.6, 5.0, 4, seed=0)
     t = lambda a: torch.from_numpy(a).to(dev)
     args = (t(b.positions), t(b.species), t(b.edge_src), t(b.edge_dst), t(b.edge_shift), t(b.node_graph), b.n_graphs)
     run = lambda: model(*args)
@@ -576,7 +577,7 @@ def config2_bench(dev):
     ms = _events_ms(run, k)
     res = {"metric": "MACE atom-steps/s (energy + forces), FP64", "value": b.n_nodes / (ms * 1e-3), "unit": "atom-steps/s",
            "ms_per_step": ms, "steps": k, "atoms": b.n_nodes, "edges": b.n_edges, "dtype": "f64",
-           "config": "config 2: 32 boxes x 384 atoms, side 15.6 A, 2 layers, 256x0e+256x1o+256x2e, SH l<=3, correlation 3, FP64",
+           "config": f"config 2: {boxes or 32} boxes x 384 atoms, side 15.6 A, 2 layers, 256x0e+256x1o+256x2e, SH l<=3, correlation 3, FP64",
            "energy_finite": bool(torch.isfinite(out["energy"]).all()), "forces_finite": bool(torch.isfinite(out["forces"]).all())}
     del out
     # the layer-2 tensor product (17 weight / 71 output segments, 256 channels) in FP64, kernels alone
@@ -595,10 +596,15 @@ def config2_bench(dev):
         t_b = _events_ms(lambda: u1d._run_bwd(call, r, w, x, y, (True, True, True)), 5) * 1e-3
     bf, bb = algorithmic_bytes(N, E, d, 8)
     peak, kind = measured_peak()
-    res["cwtp_layer2_f64"] = {"w_segs": d.w_seg_num, "out_segs": d.out_seg_num, "u": U, "bound": "hbm", "unit": "GB/s", "peak": peak,
-                              "peak_kind": kind,
-                              "fwd": {"launch_ms": t_f * 1e3, "achieved": bf / t_f / 1e9, "frac": bf / t_f / 1e9 / peak},
-                              "bwd": {"launch_ms": t_b * 1e3, "achieved": bb / t_b / 1e9, "frac": bb / t_b / 1e9 / peak}}
+    needs = (True, True, True)
+    tun_f = u1d._tuning_for(call.spec, "fwd", (w, x, y, r))
+    tun_b = u1d._tuning_for(call.spec, "bwd", (r, w, x, y), needs)
+    res["cwtp_layer2_f64"] = {"w_segs": d.w_seg_num, "out_segs": d.out_seg_num, "u": U, "bound": "fp64 pipe (64 lanes per SM per clock)",
+                              "unit": "GB/s", "peak": peak, "peak_kind": kind,
+                              "fwd": {"launch_ms": t_f * 1e3, "achieved": bf / t_f / 1e9, "frac": bf / t_f / 1e9 / peak,
+                                      **fp32_floor(call.spec, tun_f, "fwd", None, E, U, t_f, dev, lanes=64, tag="fp64")},
+                              "bwd": {"launch_ms": t_b * 1e3, "achieved": bb / t_b / 1e9, "frac": bb / t_b / 1e9 / peak,
+                                      **fp32_floor(call.spec, tun_b, "bwd", needs, E, U, t_b, dev, lanes=64, tag="fp64")}}
     return res
 
 
@@ -789,7 +795,7 @@ def main():
     if args.only:
         block = {"operators": lambda: operator_extras(args, dev),
                  "other_signature": lambda: cwtp_kernel_block("config0_layout_cwtp" if args.workload == "config1_cwtp" else "config1_cwtp", dev),
-                 "config2": lambda: config2_bench(dev),
+                 "config2": lambda: config2_bench(dev, args.boxes),
                  "model": lambda: model_bench(args, dev, rank, dist, args.boxes or WORKLOADS[args.workload][3], quick=True),
                  "fixed_batch": lambda: config4_sweep(args, dev, rank, world, dist),
                  "single_graph": lambda: halo_model_bench(args, dev, rank, world, dist)}[args.only]()

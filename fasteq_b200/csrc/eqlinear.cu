@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(NT) eqlinear_kernel(const __grid_constant__ Gr
 // (tcgen05 has no FP64 kind; the reference's FP64 back-end is DMMA as well,
 // fasteq/cuda/src/eqlinear/backends/fp64/direct_gemm_f64_tma.cu:204).  CTA tile 128 x 64, eight warps of 32 x 32
 // (sixteen 8 x 8 accumulator tiles = 32 doubles per thread), two CTAs per SM so that one CTA's stores overlap the
-// other's products.  Operands stream global -> shared memory through a four-stage cp.async ring of 8-wide k-steps
+// other's products.  Operands stream global -> shared memory through a DS-stage cp.async ring of DK-wide k-steps
 // (16-byte copies, zero fill outside the problem), one barrier per step.
 //
 // A CTA owns one 128-row tile and a range of 64-column blocks.  When the tile's whole reduction (paths x K) is at most
@@ -167,11 +167,9 @@ __global__ void __launch_bounds__(NT) eqlinear_kernel(const __grid_constant__ Gr
 // different banks.  Fragment layout of m8n8k4.f64: a = A[lane / 4][lane % 4], b = B[lane % 4][lane / 4],
 // c0, c1 = C[lane / 4][2 (lane % 4) + {0, 1}].  The path coefficient multiplies the A fragments, or the accumulators
 // in the epilogue when all paths of the group share it.
-constexpr int DM = 128, DN = 64, DK = 8, DS = 4;
-constexpr int PA = DK + 4;                      // pitch of a streamed A buffer [row][k] and of a transposed W buffer [n][k]
+constexpr int DM = 128, DN = 64;
 constexpr int PW = DN + 4;                      // pitch of a W buffer [k][n]
-constexpr int W_BUF = DK * PW > DN * PA ? DK * PW : DN * PA;
-constexpr int DMMA_MAX_STATIONARY_STEPS = 8;
+constexpr int DMMA_MAX_STATIONARY_K = 64;
 
 __device__ __forceinline__ void dmma_8x8x4(double (&c)[2], double a, double b) {
   asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};"
@@ -184,11 +182,14 @@ __device__ __forceinline__ void cp_async16(double* smem_dst, const double* gmem_
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int PENDING> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
 
-template <bool TRANS>
+template <bool TRANS, int DK, int DS>
 __global__ void __launch_bounds__(NT, 2) eqlinear_dmma_f64_kernel(const __grid_constant__ GroupTable tab, const double* __restrict__ A,
                                                                   const double* __restrict__ W, double* __restrict__ C, long long batch,
                                                                   int a_rows_per_b, int c_rows_per_b, int K, int N, int u, int v,
                                                                   int col_splits, int stationary) {
+  constexpr int PA = DK + 4;                    // pitch of a streamed A buffer [row][k] and of a transposed W buffer [n][k]
+  constexpr int W_BUF = DK * PW > DN * PA ? DK * PW : DN * PA;
+  constexpr int CPR = DK / 2;                   // 16-byte chunks per row of a k-step
   extern __shared__ __align__(16) double dsm[];
   const long long tile = blockIdx.x / col_splits;
   const int split = blockIdx.x % col_splits;
@@ -215,19 +216,22 @@ __global__ void __launch_bounds__(NT, 2) eqlinear_dmma_f64_kernel(const __grid_c
   const int wm = (warp & 3) * 32, wn = (warp >> 2) * 32;      // this warp's 32 x 32 corner of the tile
   const int fg = lane >> 2, ft = lane & 3;
 
-  // copy roles.  A step: 128 rows x 4 chunks of two doubles, two chunks per thread (rows tid / 4 and 64 + tid / 4).
-  const int a_kc = (tid & 3) * 2;
-  size_t a_off[2];
-  bool a_ok[2];
+  // copy roles.  A step: 128 rows x CPR chunks of two doubles; a thread copies chunk (tid % CPR) of rows tid / CPR + e * (NT / CPR).
+  constexpr int A_PER = DM * CPR / NT, A_ROWS = NT / CPR;
+  const int a_kc = (tid % CPR) * 2, a_r = tid / CPR;
+  size_t a_off[A_PER];
+  bool a_ok[A_PER];
 #pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    const long long ar = row0 + (tid >> 2) + 64 * e;
+  for (int e = 0; e < A_PER; ++e) {
+    const long long ar = row0 + a_r + A_ROWS * e;
     a_ok[e] = ar < n_rows;
     a_off[e] = a_ok[e] ? ((size_t)(ar / gi) * a_rows_per_b + (size_t)(ar % gi)) * (size_t)K : 0;
   }
-  // W step: one chunk per thread; [n][k] rows of the stored block when TRANS, else [k][n]
-  const int w_r = TRANS ? (tid >> 2) : (tid >> 5);          // n (TRANS) or k
-  const int w_c = TRANS ? (tid & 3) * 2 : (tid & 31) * 2;   // k (TRANS) or n
+  // W step: DK x 64 doubles = DK * 32 chunks; [n][k] rows of the stored block when TRANS, else [k][n]
+  constexpr int W_PER = DK * 32 / NT;
+  const int w_r = TRANS ? (tid / CPR) : (tid >> 5);            // n (TRANS) or k
+  const int w_c = TRANS ? (tid % CPR) * 2 : (tid & 31) * 2;    // k (TRANS) or n
+  constexpr int W_RSTEP = TRANS ? NT / CPR : NT / 32;          // rows between a thread's chunks
 
   int i_cbl = 0, i_step = 0, i_q = q0, i_k0 = 0;            // the step the next issue() loads
   auto issue = [&](int flat) {
@@ -237,20 +241,24 @@ __global__ void __launch_bounds__(NT, 2) eqlinear_dmma_f64_kernel(const __grid_c
         const double* aq = A + (size_t)tab.path_a_row[i_q] * K + i_k0 + a_kc;
         const bool kin = i_k0 + a_kc < K;
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
+        for (int e = 0; e < A_PER; ++e) {
           const bool ok = a_ok[e] && kin;
-          cp_async16(dst + ((tid >> 2) + 64 * e) * pitch_a + a_kc, ok ? aq + a_off[e] : A, ok ? 16 : 0);
+          cp_async16(dst + (a_r + A_ROWS * e) * pitch_a + a_kc, ok ? aq + a_off[e] : A, ok ? 16 : 0);
         }
       }
       double* wd = sW + (flat % DS) * W_BUF;
       const double* wq = W + (size_t)tab.path_w[i_q] * u * v;
       const int n0 = (cb0 + i_cbl) * DN;
-      if (TRANS) {
-        const bool ok = n0 + w_r < N && i_k0 + w_c < K;
-        cp_async16(wd + w_r * PA + w_c, ok ? wq + (size_t)(n0 + w_r) * v + i_k0 + w_c : W, ok ? 16 : 0);
-      } else {
-        const bool ok = i_k0 + w_r < K && n0 + w_c < N;
-        cp_async16(wd + w_r * PW + w_c, ok ? wq + (size_t)(i_k0 + w_r) * v + n0 + w_c : W, ok ? 16 : 0);
+#pragma unroll
+      for (int e = 0; e < W_PER; ++e) {
+        const int r = w_r + W_RSTEP * e;
+        if (TRANS) {
+          const bool ok = n0 + r < N && i_k0 + w_c < K;
+          cp_async16(wd + r * PA + w_c, ok ? wq + (size_t)(n0 + r) * v + i_k0 + w_c : W, ok ? 16 : 0);
+        } else {
+          const bool ok = i_k0 + r < K && n0 + w_c < N;
+          cp_async16(wd + r * PW + w_c, ok ? wq + (size_t)(i_k0 + r) * v + n0 + w_c : W, ok ? 16 : 0);
+        }
       }
       i_k0 += DK;
       if (i_k0 >= K) { i_k0 = 0; ++i_q; }
@@ -315,7 +323,7 @@ __global__ void __launch_bounds__(NT, 2) eqlinear_dmma_f64_kernel(const __grid_c
 
 // Launch geometry of the DMMA kernel: stationary A when every group's reduction fits, column blocks split over CTAs
 // only as far as needed to fill the device twice over.
-template <bool TRANS>
+template <bool TRANS, int DK, int DS>
 int launch_dmma(const GroupTable& tab, const fasteq_eqlinear_problem* p, const double* a, const double* w, double* c, int a_rows, int c_rows,
                 int K, int N, cudaStream_t s) {
   const long long wt = tab.wide_tile_first[tab.n_groups];
@@ -327,21 +335,22 @@ int launch_dmma(const GroupTable& tab, const fasteq_eqlinear_problem* p, const d
   const int k_steps = (K + DK - 1) / DK, ncb = (N + DN - 1) / DN;
   int max_steps = 0;
   for (int g = 0; g < tab.n_groups; ++g) max_steps = std::max(max_steps, (tab.group_first[g + 1] - tab.group_first[g]) * k_steps);
-  const int stationary = max_steps <= DMMA_MAX_STATIONARY_STEPS ? 1 : 0;
+  constexpr int PA = DK + 4, W_BUF = DK * PW > DN * PA ? DK * PW : DN * PA;
+  const int stationary = max_steps * DK <= DMMA_MAX_STATIONARY_K ? 1 : 0;
   const long long want = (2LL * sms + wt - 1) / wt;
   const int col_splits = (int)std::min<long long>(ncb, std::max<long long>(1, want));
   if (wt * col_splits > 0x7fffffffLL) return FASTEQ_UNSUPPORTED;
   const size_t smem = sizeof(double) * ((stationary ? (size_t)DM * (max_steps * DK + 4) : (size_t)DS * DM * PA) + (size_t)DS * W_BUF);
   static bool raised[64] = {};
   if (dev < 64 && !raised[dev]) {
-    e = cudaFuncSetAttribute(eqlinear_dmma_f64_kernel<TRANS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)(sizeof(double) * ((size_t)DM * (DMMA_MAX_STATIONARY_STEPS * DK + 4) + (size_t)DS * W_BUF)));
+    const size_t most = std::max((size_t)DM * (DMMA_MAX_STATIONARY_K + 4), (size_t)DS * DM * PA) + (size_t)DS * W_BUF;
+    e = cudaFuncSetAttribute(eqlinear_dmma_f64_kernel<TRANS, DK, DS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(double) * most));
     if (e != cudaSuccess) return cuda_fail(e);
     raised[dev] = true;
   } else if (dev >= 64) {
     return FASTEQ_UNSUPPORTED;
   }
-  eqlinear_dmma_f64_kernel<TRANS><<<(unsigned)(wt * col_splits), NT, smem, s>>>(tab, a, w, c, p->batch, a_rows, c_rows, K, N, p->u, p->v,
+  eqlinear_dmma_f64_kernel<TRANS, DK, DS><<<(unsigned)(wt * col_splits), NT, smem, s>>>(tab, a, w, c, p->batch, a_rows, c_rows, K, N, p->u, p->v,
                                                                                col_splits, stationary);
   e = cudaGetLastError();
   return e == cudaSuccess ? FASTEQ_OK : cuda_fail(e);
@@ -437,8 +446,9 @@ int launch(const fasteq_eqlinear_problem* p, bool dgrad, const void* w, const vo
   if (sizeof(T) == 8 && N >= 8 && (N % 2) == 0 && (K % 2) == 0 &&
       ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(c)) & 15u) == 0) {
     // FP64 on the tensor cores (DMMA); its 16-byte copies need even K and N and 16-byte aligned operands
-    return dgrad ? launch_dmma<true>(tab, p, (const double*)a, (const double*)w, (double*)c, a_rows, c_rows, K, N, s)
-                 : launch_dmma<false>(tab, p, (const double*)a, (const double*)w, (double*)c, a_rows, c_rows, K, N, s);
+    // k-steps of 8 through a four-deep ring; 16-wide steps and rings of two or three measured within 3 % of it
+    return dgrad ? launch_dmma<true, 8, 4>(tab, p, (const double*)a, (const double*)w, (double*)c, a_rows, c_rows, K, N, s)
+                 : launch_dmma<false, 8, 4>(tab, p, (const double*)a, (const double*)w, (double*)c, a_rows, c_rows, K, N, s);
   }
   const long long tiles = tab.tile_first[tab.n_groups];
   if (tiles > 0x7fffffffLL) return FASTEQ_UNSUPPORTED;
