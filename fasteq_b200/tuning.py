@@ -91,8 +91,8 @@ def candidates(spec: U1DSpec, direction: str, needs=(True, True, True)) -> List[
     wpg = base.ct // (32 * base.vec)
     two_groups_ok = direction == "fwd" or not (spec.w_shared or spec.y_vec or spec.y_indexed or not spec.x_indexed)
 
-    def add(pipes, groups, mb, two_pass, depths):
-        probe = dataclasses.replace(base, pipes=pipes, groups=groups, min_blocks=mb, two_pass=two_pass, stages=2)
+    def add(pipes, groups, mb, two_pass, depths, go_smem=True):
+        probe = dataclasses.replace(base, pipes=pipes, groups=groups, min_blocks=mb, two_pass=two_pass, stages=2, go_smem=go_smem)
         if pipes * groups * wpg > 16 or pipes * (groups * (probe.ct // probe.vec) + 32) > 1024:
             return
         per_stage = (smem_bytes(spec, dataclasses.replace(probe, stages=3), direction, needs[2]) -
@@ -106,10 +106,13 @@ def candidates(spec: U1DSpec, direction: str, needs=(True, True, True)) -> List[
             if tun not in out:
                 out.append(tun)
 
-    for pipes in sorted({2, 4, base.pipes}):
+    for pipes in sorted({2, 3, 4, base.pipes}):
         for groups in ((1, 2) if two_groups_ok else (1,)):
             for mb in (1, 2):
                 add(pipes, groups, mb, False, lambda fit: (fit, base.stages))          # deepest ring that fits, and the default depth
+                if direction == "bwd" and spec.dtype == "f64":
+                    # FP64 rows are twice as large: without the staged grad_out row more pipelines (consumer warps) fit
+                    add(pipes, groups, mb, False, lambda fit: (fit, base.stages), go_smem=False)
     if direction == "bwd":
         for groups in ((1, 2) if two_groups_ok else (1,)):
             add(base.pipes, groups, base.min_blocks, True, lambda fit: (fit,))         # two passes over a block: fewer live registers
