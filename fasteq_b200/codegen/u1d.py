@@ -349,13 +349,27 @@ def _load_xy(spec: U1DSpec, ind: str) -> List[str]:
 
 # --------------------------------------------------------------------------- forward
 
-def _diagonal_runs(terms) -> Dict[Tuple[int, int, float], List[Tuple[int, int]]]:
-    """For a block whose terms all have one product: (i, j, c) -> [(k, v), ...].  Such a block (an
-    l1 = 0 or l2 = 0 coupling) needs one multiply ``c * w[i] * x[j]`` per run and one FMA per output."""
-    runs: Dict[Tuple[int, int, float], List[Tuple[int, int]]] = {}
+def _diagonal_runs(terms) -> List[Tuple[str, int, int, float, List[Tuple[int, int]]]]:
+    """For a block whose terms all have one product: runs ``(kind, i, shared, c, [(other, v), ...])``.  ``kind`` "x":
+    the outputs ``v`` share ``c * w[i] * x[shared]`` and differ in ``y[other]`` (an l1 = 0 coupling); "y": they share
+    ``c * w[i] * y[shared]`` and differ in ``x[other]`` (l2 = 0).  One multiply per run and one FMA per output forward;
+    backward, the sum over the run's outputs is formed once before it meets the shared operand."""
+    by_ic: Dict[Tuple[int, float], List[Tuple[int, int, int]]] = {}
     for t in terms:
         (j, k, c), = t.items
-        runs.setdefault((t.i, j, c), []).append((k, t.v))
+        by_ic.setdefault((t.i, c), []).append((j, k, t.v))
+    runs = []
+    for (i, c), jkv in by_ic.items():
+        if len({j for j, _, _ in jkv}) <= len({k for _, k, _ in jkv}):
+            groups: Dict[int, List[Tuple[int, int]]] = {}
+            for j, k, v in jkv:
+                groups.setdefault(j, []).append((k, v))
+            runs += [("x", i, j, c, kv) for j, kv in groups.items()]
+        else:
+            groups = {}
+            for j, k, v in jkv:
+                groups.setdefault(k, []).append((j, v))
+            runs += [("y", i, k, c, jv) for k, jv in groups.items()]
     return runs
 
 
@@ -369,11 +383,12 @@ def _emit_block_fwd(spec: U1DSpec, b: Block, owned: set, slot_of: Dict[int, int]
         return []
     if _is_diagonal(terms):
         L = [ind + "{"]
-        for (i, j, c), kv in _diagonal_runs(terms).items():
-            sexpr = f"vmul(W({i}), x{j})" if c == 1.0 else f"vmul(vmul({_vlit(c, spec.dtype)}, W({i})), x{j})"
+        for kind, i, sh, c, ov in _diagonal_runs(terms):
+            shared, other = ("x", "y") if kind == "x" else ("y", "x")
+            sexpr = f"vmul(W({i}), {shared}{sh})" if c == 1.0 else f"vmul(vmul({_vlit(c, spec.dtype)}, W({i})), {shared}{sh})"
             L.append(f"{ind}  {{ const V s = {sexpr};")
-            for k, v in kv:
-                L.append(f"{ind}    acc{slot_of[v]} = vfma(s, y{k}, acc{slot_of[v]});")
+            for o, v in ov:
+                L.append(f"{ind}    acc{slot_of[v]} = vfma(s, {other}{o}, acc{slot_of[v]});")
             L.append(f"{ind}  }}")
         L.append(ind + "}")
         return L
@@ -744,25 +759,31 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
         return decl + out + tail
 
     def diag_part(b: Block, ind: str) -> List[str]:
+        # out[v] += c * w[i] * S * O[v] with S the run's shared operand (x[j] or y[k]) and O[v] the other one:
+        #   d = sum_v go[v] * O[v];  gw[i] += c * S * d;  gS += c * w[i] * d;  gO[v] += (c * w[i] * S) * go[v]
         out = []
-        for (i, j, c), kv in _diagonal_runs(b.terms).items():
+        for kind, i, sh, c, ov in _diagonal_runs(b.terms):
+            S, O = (f"x{sh}", "y") if kind == "x" else (f"y{sh}", "x")
+            need_gs, need_go = (need_gx, need_gy) if kind == "x" else (need_gy, need_gx)
+            gS = ("gx" if kind == "x" else "gy") + str(sh)
+            gO = "gy" if kind == "x" else "gx"
             out.append(f"{ind}{{")
-            if need_gw or need_gx:
-                k0, v0 = kv[0]
-                out.append(f"{ind}  V d = vmul(GO({v0}), y{k0});")
-                for k, v in kv[1:]:
-                    out.append(f"{ind}  d = vfma(GO({v}), y{k}, d);")
+            if need_gw or need_gs:
+                o0, v0 = ov[0]
+                out.append(f"{ind}  V d = vmul(GO({v0}), {O}{o0});")
+                for o, v in ov[1:]:
+                    out.append(f"{ind}  d = vfma(GO({v}), {O}{o}, d);")
             cw = f"W({i})" if c == 1.0 else f"vmul({_vlit(c, dt)}, W({i}))"
             out.append(f"{ind}  const V cw = {cw};")
             if need_gw:
-                cx = f"x{j}" if c == 1.0 else f"vmul({_vlit(c, dt)}, x{j})"
-                out.append(f"{ind}  gw{i} = vfma({cx}, d, gw{i});")
-            if need_gx:
-                out.append(f"{ind}  gx{j} = vfma(cw, d, gx{j});")
-            if need_gy:
-                out.append(f"{ind}  const V s = vmul(cw, x{j});")
-                for k, v in kv:
-                    out.append(f"{ind}  gy{k} = vfma(s, GO({v}), gy{k});")
+                cs = S if c == 1.0 else f"vmul({_vlit(c, dt)}, {S})"
+                out.append(f"{ind}  gw{i} = vfma({cs}, d, gw{i});")
+            if need_gs:
+                out.append(f"{ind}  {gS} = vfma(cw, d, {gS});")
+            if need_go:
+                out.append(f"{ind}  const V s = vmul(cw, {S});")
+                for o, v in ov:
+                    out.append(f"{ind}  {gO}{o} = vfma(s, GO({v}), {gO}{o});")
             out.append(f"{ind}}}")
         return out
 

@@ -138,9 +138,18 @@ def build_blocks(spec: U1DSpec) -> List[Block]:
         if not t.items:
             continue
         groups.setdefault(find((t.items[0][0], t.items[0][1])), []).append(t)
-    blocks = []
-    for root in sorted(groups, key=lambda r: min((t.i, t.v) for t in groups[r])):
+    # one-product terms of the same weight segment (an l1 = 0 or l2 = 0 coupling: every output component is one product)
+    # form ONE block, so that the emitters can sum over the components before they touch the shared operand
+    merged: Dict[Tuple[int, int], List[Term]] = {}
+    for root in sorted(groups):
         ts = groups[root]
+        if all(len(t.items) == 1 for t in ts):
+            merged.setdefault((-1, ts[0].i), []).extend(ts)
+        else:
+            merged[root] = ts
+    blocks = []
+    for root in sorted(merged, key=lambda r: min((t.i, t.v) for t in merged[r])):
+        ts = sorted(merged[root], key=lambda t: (t.i, t.v))
         prods = sorted({(j, k) for t in ts for j, k, _ in t.items})
         blocks.append(Block(ts, prods))
     return blocks

@@ -29,7 +29,7 @@ from .. import tuning as _tuning
 from ..codegen import u1d as _emit
 from ..codegen.u1d_common import U1DSpec, make_spec
 
-_EMITTER_VERSION = "u1d-v1"
+_EMITTER_VERSION = "u1d-v2"
 _MODULES: Dict[Tuple, _cabi.U1DModule] = {}
 _TUNING_OVERRIDE: Dict[str, _emit.Tuning] = {}
 _lock = threading.Lock()
