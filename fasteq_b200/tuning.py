@@ -110,8 +110,8 @@ def candidates(spec: U1DSpec, direction: str, needs=(True, True, True)) -> List[
         for groups in ((1, 2) if two_groups_ok else (1,)):
             for mb in (1, 2):
                 add(pipes, groups, mb, False, lambda fit: (fit, base.stages))          # deepest ring that fits, and the default depth
-                if direction == "bwd" and spec.dtype == "f64":
-                    # FP64 rows are twice as large: without the staged grad_out row more pipelines (consumer warps) fit
+                if direction == "bwd":
+                    # without the staged grad_out row (read through L1 instead) deeper rings and more pipelines fit
                     add(pipes, groups, mb, False, lambda fit: (fit, base.stages), go_smem=False)
     if direction == "bwd":
         for groups in ((1, 2) if two_groups_ok else (1,)):
@@ -277,8 +277,9 @@ def main(argv=None) -> None:
     ap.add_argument("--boxes", type=int, default=64, help="boxes of 192 atoms in the timing graph (64 = the benchmark's size)")
     ap.add_argument("--compile-only", action="store_true", help="build every candidate (no GPU needed), time nothing")
     ap.add_argument("--match", default=None, help="only signatures whose label contains this text")
+    ap.add_argument("--direction", default=None, choices=["fwd", "bwd"], help="only this direction")
     args = ap.parse_args(argv)
-    jobs = [j for j in sweep_jobs() if args.match is None or args.match in j[0]]
+    jobs = [j for j in sweep_jobs() if (args.match is None or args.match in j[0]) and args.direction in (None, j[2])]
     if args.compile_only:
         from concurrent.futures import ThreadPoolExecutor
         from .ops.uniform1d_jit import get_module
