@@ -106,7 +106,7 @@ def candidates(spec: U1DSpec, direction: str, needs=(True, True, True)) -> List[
             if tun not in out:
                 out.append(tun)
 
-    for pipes in sorted({2, 3, 4, base.pipes}):
+    for pipes in sorted({2, 3, 4, 5, 6, base.pipes}):
         for groups in ((1, 2) if two_groups_ok else (1,)):
             for mb in (1, 2):
                 add(pipes, groups, mb, False, lambda fit: (fit, base.stages))          # deepest ring that fits, and the default depth
