@@ -136,3 +136,11 @@ def test_fixed_batch_of_benchmark_configuration_4_splits_evenly():
         assert sorted(i for p in parts for i in p) == list(range(1024))
         loads = np.array([atoms[p].sum() for p in parts], dtype=float)
         assert loads.max() / loads.mean() < 1.02
+
+
+def test_device_status_helper_needs_no_gpu():
+    """``fasteq_b200.status.device_status`` reads every loaded kernel family's status word; without CUDA it reports nothing."""
+    import torch
+    from fasteq_b200.status import device_status
+    if not torch.cuda.is_available():
+        assert device_status() == {}

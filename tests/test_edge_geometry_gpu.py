@@ -60,3 +60,16 @@ def test_out_of_range_indices_are_skipped_and_reported():
     (g1,) = torch.autograd.grad(b1.sum() + v1.sum(), p2)
     assert torch.equal(v1[0], vec[0]) and torch.equal(b1[0], basis[0])
     assert torch.allclose(g, g1, rtol=1e-6, atol=1e-7)
+
+
+def test_device_status_helper_reports_and_clears():
+    """``fasteq_b200.status.device_status`` names the family whose status word is set and clears it."""
+    from fasteq_b200.ops.edge_geometry import edge_geometry
+    from fasteq_b200.status import device_status
+    device_status()                                   # clear whatever earlier tests left
+    pos = torch.zeros(3, 3, device="cuda")
+    bad = torch.tensor([5], dtype=torch.int32, device="cuda")
+    ok = torch.tensor([0], dtype=torch.int32, device="cuda")
+    edge_geometry(pos, bad, ok, torch.zeros(1, 3, device="cuda"), 5.0, 8, 5)
+    assert device_status() == {"edge geometry": 2}
+    assert device_status() == {}
