@@ -36,6 +36,7 @@ class Tuning:
     pipes: int = 1     # independent producer/consumer pipelines per CTA (keeps all four SM sub-partitions busy)
     go_smem: bool = True   # backward: stage the receiver's grad_out row in shared memory (else read it through L1)
     prefetch: int = 0      # ring-fuls by which the producer asks rows into L2 ahead of the stage fills (0 = no prefetch)
+    go_tmem: bool = False  # backward: park the receiver's grad_out row in tensor memory (one lane per thread) instead
 
 
 def default_tuning(spec: U1DSpec, direction: str) -> Tuning:
@@ -321,6 +322,24 @@ def _check_tuning(spec: U1DSpec, tun: Tuning) -> None:
         raise ValueError("packed arithmetic needs FP32 and an even channel count")
     if tun.ct % (32 * tun.vec):
         raise ValueError("ct must be a multiple of 32 * vec")
+    if tun.go_tmem:
+        if tun.go_smem or tun.groups != 1 or spec.dtype != "f32" or spec.u % tun.ct:
+            raise ValueError("the tensor-memory gradient row needs FP32, whole channel tiles, one thread group and no shared-memory tile")
+        if tmem_columns(spec, tun) > 512:
+            raise ValueError("the gradient rows of this layout do not fit 512 columns of tensor memory")
+        if tun.stages > 13:
+            raise ValueError("at most 13 stages beside the tensor-memory slot")
+
+
+def tmem_columns(spec: U1DSpec, tun: Tuning) -> int:
+    """Tensor-memory columns the ``go_tmem`` layout allocates: consumer warps with the same warp index modulo four share
+    a lane quarter and stack their rows (vec * out_segs 32-bit columns each); allocations are powers of two >= 32."""
+    ncons = tun.pipes * tun.groups * (tun.ct // tun.vec) // 32
+    need = (ncons + 3) // 4 * tun.vec * spec.out_segs
+    cols = 32
+    while cols < need:
+        cols *= 2
+    return cols
 
 
 def _vlit(c: float, dtype: str) -> str:
@@ -589,6 +608,8 @@ def emit_backward(spec: U1DSpec, tun: Tuning, need_gw: bool, need_gx: bool, need
     src.append(f"""
 constexpr int NTHREADS = {threads};
 constexpr int NGO = {1 if tun.go_smem else 0};                                 // grad_out row buffers in shared memory (0: read through L1)
+constexpr bool GO_TMEM = {'true' if tun.go_tmem else 'false'};                 // ... or parked in tensor memory, one lane per consumer thread
+constexpr uint32_t TMEM_COLS = {tmem_columns(spec, tun) if tun.go_tmem else 0};
 constexpr int GO_BYTES = round_up(OSEG * CT * (int)sizeof(T), 128);
 constexpr int PIPE_BYTES = BAR_BYTES + STAGES * STAGE_BYTES + NGO * GO_BYTES;
 constexpr int SMEM_BYTES = cfg::PIPES * PIPE_BYTES;
@@ -610,6 +631,16 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
   }}
   __syncthreads();
   const int warp_all = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // tensor-memory gradient rows: warp 0 allocates, everyone reads the base address from the last word of the first
+  // barrier block (free when no gradient tile lives in shared memory)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_all + BAR_BYTES - 4);
+  if (GO_TMEM) {{
+    if (warp_all == 0) scratch_tmem_alloc(tmem_slot, TMEM_COLS);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }}
+  const uint32_t tmem_base = GO_TMEM ? *tmem_slot : 0u;
   const bool is_producer = warp_all >= cfg::PIPES * cfg::NCONS_WARPS;
   const int pipe = is_producer ? warp_all - cfg::PIPES * cfg::NCONS_WARPS : warp_all / cfg::NCONS_WARPS;
   const int warp = warp_all - pipe * cfg::NCONS_WARPS;           // consumer warp index inside the pipeline
@@ -678,6 +709,10 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
   const int ptid = threadIdx.x - pipe * cfg::NCONS_WARPS * 32;   // thread index inside the pipeline
   const int grp = ptid / TPG, ch = (ptid % TPG) * VEC; (void)grp;
   uint32_t it = 0, nseg = 0;
+  // this thread's gradient row in tensor memory: lane = 32 * (warp % 4) + lane id, the consumer warps of one lane quarter
+  // stacked VEC * OSEG columns apart
+  const uint32_t tmem_go = tmem_base + ((uint32_t)(32 * (warp_all & 3)) << 16) + (uint32_t)((warp_all >> 2) * VEC * OSEG);
+  (void)tmem_go;
 """)
     L: List[str] = []
     if spec.w_shared and need_gw:
@@ -695,7 +730,14 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
     const int valid = (U % CT == 0) ? CT : ((U - m.ct * CT) < CT ? (U - m.ct * CT) : CT);
     const bool live = ch < valid;
     const int gb = nseg % (NGO ? NGO : 1);
-    if (NGO && (m.flags & F_FIRST) && !mbar_wait(&go_full[gb], (nseg / (NGO ? NGO : 1)) & 1u, g.status)) break;""")
+    if (NGO && (m.flags & F_FIRST) && !mbar_wait(&go_full[gb], (nseg / (NGO ? NGO : 1)) & 1u, g.status)) break;
+    if (GO_TMEM && (m.flags & F_FIRST)) {
+      // a new receiver (or channel tile): its grad_out row moves from global memory into this thread's tensor-memory lane
+      const T* grow = go + (size_t)m.row * OSEG * U + (size_t)m.ct * CT + ch;
+#pragma unroll
+      for (int v = 0; v < OSEG; ++v) scratch_tmem_st(tmem_go + (uint32_t)(VEC * v), VS::ldg(grow + (size_t)v * U));
+      scratch_tmem_wait_st();
+    }""")
     if spec.w_shared and need_gw:
         L.append("    if ((m.flags & (F_DATA | F_DONE)) && (m.ct != gws_ct || (m.flags & F_DONE))) {")
         L.append("      if (ch < ((U - gws_ct * CT) < CT ? (U - gws_ct * CT) : CT)) {")
@@ -719,7 +761,10 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
     else:
         L.append("      const T* sw = reinterpret_cast<const T*>(st + OFF_W) + ch;")
         L.append("#define W(i) VS::ld(sw + (i) * CT)")
-    L.append("#define GO(v) VS::ld(sgo + (v) * CT)" if tun.go_smem else "#define GO(v) VS::ldg(sgo + (size_t)(v) * U)")
+    if tun.go_tmem:
+        L.append("#define GO(v) go_##v")       # loaded from tensor memory at the head of each block
+    else:
+        L.append("#define GO(v) VS::ld(sgo + (v) * CT)" if tun.go_smem else "#define GO(v) VS::ldg(sgo + (size_t)(v) * U)")
     L += _load_xy(spec, "      ")
     if need_gx:
         L += [f"      V gx{j} = VS::zero();" for j in range(spec.x_segs)]
@@ -796,6 +841,14 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
         if G > 1:
             L.append(f"      if (grp == {gi}) {{")
         for bi, b in enumerate(gblocks):
+            if tun.go_tmem:
+                # the block's grad_out values: issued together, released by one wait that names them
+                vs = sorted({t.v for t in b.terms})
+                L.append("      {")
+                L.append("      V " + ", ".join(f"go_{v}" for v in vs) + ";")
+                L += [f"      scratch_tmem_ld(tmem_go + {v}u * VEC, go_{v});" for v in vs]
+                L.append(f"      scratch_tmem_wait_ld(go_{vs[0]});")
+                L += [f"      scratch_tmem_pin(go_{v});" for v in vs[1:]]
             if _is_diagonal(b.terms):
                 L.append("      {"); L += diag_part(b, "        "); L.append("      }")
             elif tun.two_pass or not (need_gw and need_q):
@@ -824,6 +877,8 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
                     L += [f"        gx{j} = vfma(q_{j}_{k}, y{k}, gx{j});" for (j, k) in b.products]
                 if need_gy:
                     L += [f"        gy{k} = vfma(q_{j}_{k}, x{j}, gy{k});" for (j, k) in b.products]
+                L.append("      }")
+            if tun.go_tmem:
                 L.append("      }")
             if need_gw:
                 for i in sorted(i for i, last in last_block_of_i.items() if last == bi):
@@ -862,6 +917,15 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
     if (m.flags & F_LAST) ++nseg;
     ++it;
     if (m.flags & F_DONE) break;
+  }
+  if (GO_TMEM) {
+    // every consumer warp is done with its lanes (also after a wait that gave up): warp 0 returns the columns
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"r"(cfg::PIPES * cfg::NCONS_WARPS * 32) : "memory");
+    if (warp_all == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      scratch_tmem_free(tmem_base, TMEM_COLS);
+    }
   }
 }""")
     src.append("\n".join(L))

@@ -172,6 +172,40 @@ template <> struct VT<float2> {
   static __device__ __forceinline__ void red(float* p, float2 v) { red_add2(p, v); }
 };
 
+// ---- tensor memory as per-thread scratch.  A thread of warp w can reach lanes 32 * (w % 4) .. + 31 of tensor memory,
+// one lane per thread and up to 512 32-bit columns in it: values a thread parks there come back to the same thread, so no
+// ordering against other threads is needed beyond the wait on its own stores / loads.  All of these are warp-collective.
+__device__ __forceinline__ void scratch_tmem_alloc(uint32_t* smem_slot, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(columns) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void scratch_tmem_free(uint32_t base, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void scratch_tmem_st(uint32_t addr, float v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(addr), "r"(__float_as_uint(v)) : "memory");
+}
+__device__ __forceinline__ void scratch_tmem_st(uint32_t addr, float2 v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(__float_as_uint(v.x)), "r"(__float_as_uint(v.y)) : "memory");
+}
+__device__ __forceinline__ void scratch_tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// the loaded registers are valid only after scratch_tmem_wait_ld(...) has been given them
+__device__ __forceinline__ void scratch_tmem_ld(uint32_t addr, float& v) {
+  uint32_t r;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(addr) : "memory");
+  v = __uint_as_float(r);
+}
+__device__ __forceinline__ void scratch_tmem_ld(uint32_t addr, float2& v) {
+  uint32_t r0, r1;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr) : "memory");
+  v = make_float2(__uint_as_float(r0), __uint_as_float(r1));
+}
+// the wait names the values it releases, so that no use of them can be scheduled ahead of it
+__device__ __forceinline__ void scratch_tmem_wait_ld(float& a) { asm volatile("tcgen05.wait::ld.sync.aligned;" : "+f"(a)::"memory"); }
+__device__ __forceinline__ void scratch_tmem_wait_ld(float2& a) { asm volatile("tcgen05.wait::ld.sync.aligned;" : "+f"(a.x), "+f"(a.y)::"memory"); }
+__device__ __forceinline__ void scratch_tmem_pin(float& a) { asm volatile("" : "+f"(a)::"memory"); }
+__device__ __forceinline__ void scratch_tmem_pin(float2& a) { asm volatile("" : "+f"(a.x), "+f"(a.y)::"memory"); }
+
 template <typename T>
 __device__ __forceinline__ T warp_sum(T v) {
 #pragma unroll

@@ -86,6 +86,8 @@ def build_standard_modules(verbose: bool = False) -> None:
             # ... and on the heuristic four-pipeline layout, which those tests force next to the tuned one
             from .codegen.u1d import default_tuning
             jobs += [(sp, "fwd", (False, False, False), default_tuning(sp, "fwd")), (sp, "bwd", (True, True, True), default_tuning(sp, "bwd"))]
+            # ... and on the backward layout that parks the grad_out row in tensor memory
+            jobs.append((sp, "bwd", (True, True, True), dataclasses.replace(default_tuning(sp, "bwd"), go_smem=False, go_tmem=True, stages=6)))
     stc_jobs = []
     for a, b, dtypes in STANDARD_STC:
         for dt in dtypes:

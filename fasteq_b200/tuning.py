@@ -24,7 +24,7 @@ from .codegen import u1d as _emit
 from .codegen.u1d_common import U1DSpec
 
 DB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tuning_db.json")
-_FIELDS = ("ct", "groups", "stages", "min_blocks", "vec", "two_pass", "pipes", "go_smem", "prefetch")
+_FIELDS = ("ct", "groups", "stages", "min_blocks", "vec", "two_pass", "pipes", "go_smem", "prefetch", "go_tmem")
 _db: Optional[Dict[str, dict]] = None
 
 
@@ -91,8 +91,14 @@ def candidates(spec: U1DSpec, direction: str, needs=(True, True, True)) -> List[
     wpg = base.ct // (32 * base.vec)
     two_groups_ok = direction == "fwd" or not (spec.w_shared or spec.y_vec or spec.y_indexed or not spec.x_indexed)
 
-    def add(pipes, groups, mb, two_pass, depths, go_smem=True):
-        probe = dataclasses.replace(base, pipes=pipes, groups=groups, min_blocks=mb, two_pass=two_pass, stages=2, go_smem=go_smem)
+    def add(pipes, groups, mb, two_pass, depths, go_smem=True, go_tmem=False):
+        probe = dataclasses.replace(base, pipes=pipes, groups=groups, min_blocks=mb, two_pass=two_pass, stages=2, go_smem=go_smem,
+                                    go_tmem=go_tmem)
+        if go_tmem:
+            try:
+                _emit._check_tuning(spec, probe)
+            except ValueError:
+                return
         if pipes * groups * wpg > 16 or pipes * (groups * (probe.ct // probe.vec) + 32) > 1024:
             return
         per_stage = (smem_bytes(spec, dataclasses.replace(probe, stages=3), direction, needs[2]) -
@@ -113,6 +119,9 @@ def candidates(spec: U1DSpec, direction: str, needs=(True, True, True)) -> List[
                 if direction == "bwd":
                     # without the staged grad_out row (read through L1 instead) deeper rings and more pipelines fit
                     add(pipes, groups, mb, False, lambda fit: (fit, base.stages), go_smem=False)
+                    if groups == 1 and mb == 1:
+                        # ... or parked in tensor memory (one lane per consumer thread): the same room, no L1 traffic
+                        add(pipes, groups, mb, False, lambda fit: (fit, max(2, fit - 1), base.stages), go_smem=False, go_tmem=True)
     if direction == "bwd":
         for groups in ((1, 2) if two_groups_ok else (1,)):
             add(base.pipes, groups, base.min_blocks, True, lambda fit: (fit,))         # two passes over a block: fewer live registers
@@ -155,7 +164,8 @@ def sweep(spec: U1DSpec, direction: str, needs=(True, True, True), n_boxes: int 
           margin: float = 0.03, verbose: bool = False) -> dict:
     """Time every candidate's kernel alone (CUDA events around ``launches`` back-to-back launches after two warm-up
     launches; the best of ``repeats`` such bursts) and return the database entry of the fastest.  The heuristic default
-    keeps its place unless a candidate beats it by more than ``margin`` (run-to-run noise is a few per cent)."""
+    keeps its place unless a candidate beats it by more than ``margin`` in five alternating bursts of the two
+    (run-to-run noise is a few per cent)."""
     import torch
     from . import _cabi
     from .ops import uniform1d_jit as u1d
@@ -208,7 +218,7 @@ def sweep(spec: U1DSpec, direction: str, needs=(True, True, True), n_boxes: int 
             continue
         results.append({"tuning": dataclasses.asdict(tun), "ms": ms, "device_status": status})
         if verbose:
-            print(f"  {direction} pipes={tun.pipes} groups={tun.groups} stages={tun.stages} ctas={tun.min_blocks} two_pass={tun.two_pass} prefetch={tun.prefetch}: {ms:.4f} ms",
+            print(f"  {direction} pipes={tun.pipes} groups={tun.groups} stages={tun.stages} ctas={tun.min_blocks} two_pass={tun.two_pass} prefetch={tun.prefetch} go={'smem' if tun.go_smem else ('tmem' if tun.go_tmem else 'l1')}: {ms:.4f} ms",
                   flush=True)
     good = [r_ for r_ in results if "ms" in r_ and r_["device_status"] == 0]
     if not good:
@@ -221,12 +231,16 @@ def sweep(spec: U1DSpec, direction: str, needs=(True, True, True), n_boxes: int 
         # again in alternation; the default keeps its place unless it loses by more than the margin here too
         tb, td = _emit.Tuning(**best["tuning"]), _emit.Tuning(**results[0]["tuning"])
         b_ms = d_ms = float("inf")
-        for _ in range(3):
+        for _ in range(5):
             d_ms = min(d_ms, burst(runners[td])); b_ms = min(b_ms, burst(runners[tb]))
         best = dict(best, ms=b_ms, confirmed_against_default_ms=d_ms)
+        if verbose:
+            print(f"  confirmation: challenger {b_ms:.4f} ms, default {d_ms:.4f} ms (first pass {default_ms:.4f} ms)", flush=True)
+        # the verdict rests on the alternation alone: both were timed in the same thermal state there, while the first
+        # pass timed the default on a cooler GPU than the candidates after it
+        if b_ms > d_ms * (1.0 - margin):
+            best = dict(results[0], ms=min(default_ms, d_ms))
         default_ms = min(default_ms, d_ms)
-        if b_ms > default_ms * (1.0 - margin):          # must beat the default's best time of either phase
-            best = dict(results[0], ms=default_ms)
     return {"tuning": best["tuning"], "ms": best["ms"], "default_ms": default_ms, "confirmed_against_default_ms": best.get("confirmed_against_default_ms"),
             "edges": E, "atoms": N,
             "gpu": torch.cuda.get_device_name(dev), "direction": direction, "needs": [bool(n) for n in needs],

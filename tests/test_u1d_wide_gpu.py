@@ -67,12 +67,14 @@ def test_default_tuning_is_the_four_pipeline_packed_layout(in1, parity, w_segs, 
     assert (default_tuning(spec, "fwd").stages == 10) == small
 
 
-@pytest.mark.parametrize("layout", ["four_pipelines", "tuned"])
+@pytest.mark.parametrize("layout", ["four_pipelines", "tuned", "tensor_memory"])
 @pytest.mark.parametrize("fused_sh", [False, True], ids=["y_harmonics", "y_vectors"])
 @pytest.mark.parametrize("in1,parity,w_segs,out_segs,small", SIGNATURES)
 def test_wide_layout_matches_oracle(in1, parity, w_segs, out_segs, small, fused_sh, layout):
     """``four_pipelines``: the heuristic layout (one CTA of four pipelines, packed arithmetic), forced; ``tuned``: whatever
-    the tuning database selects for the signature (what the benchmark and the model actually run)."""
+    the tuning database selects for the signature (what the benchmark and the model actually run); ``tensor_memory``: the
+    backward with the receiver's grad_out row parked in tensor memory (one lane per consumer thread) and the shared memory
+    it frees given to deeper rings."""
     from fasteq_b200.ops import fast_uniform1d_jit
     from fasteq_b200.ops import uniform1d_jit as u1d
     d = _descriptor(in1, parity)
@@ -80,10 +82,17 @@ def test_wide_layout_matches_oracle(in1, parity, w_segs, out_segs, small, fused_
                       y_segs=d.y_seg_num, out_segs=d.out_seg_num, u=d.u_dim, dtype="f32")
     if layout == "four_pipelines":
         u1d._TUNING_OVERRIDE.update(fwd=default_tuning(spec0, "fwd"), bwd=default_tuning(spec0, "bwd"))
+    elif layout == "tensor_memory":
+        u1d._TUNING_OVERRIDE.update(bwd=tensor_memory_tuning(spec0))
     try:
         _check_against_oracle(d, w_segs, fused_sh, layout)
     finally:
         u1d._TUNING_OVERRIDE.clear()
+
+
+def tensor_memory_tuning(spec):
+    import dataclasses
+    return dataclasses.replace(default_tuning(spec, "bwd"), go_smem=False, go_tmem=True, stages=6)
 
 
 def _check_against_oracle(d, w_segs, fused_sh, layout):
@@ -117,6 +126,8 @@ def _check_against_oracle(d, w_segs, fused_sh, layout):
         assert tun.vec == 2
         if layout == "four_pipelines":
             assert tun.pipes == 4 and tun.groups == 1
+        if layout == "tensor_memory" and direction == "bwd":
+            assert tun.go_tmem and not tun.go_smem and tun.pipes == 4 and tun.stages == 6
         mod = u1d.get_module(call.spec, direction, needs, tuning=tun)
         assert mod.desc.threads == tun.pipes * (tun.groups * 64 + 32)
         assert mod.device_status() == 0
