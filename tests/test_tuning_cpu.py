@@ -47,7 +47,10 @@ def test_database_entries_decode_and_are_used():
         spec, d, needs = keys[k]
         t = tuning.lookup(spec, d, needs)
         assert isinstance(t, gen.Tuning) and t in tuning.candidates(spec, d, needs)
-        assert entry["ms"] <= entry["default_ms"] * 1.0001                     # the winner is never slower than the default it was timed against
+        # the winner is never slower than the default it was timed against: in alternation with it when it was a
+        # challenger (the first pass times the default on a cooler GPU than the candidates after it)
+        against = entry.get("confirmed_against_default_ms") or entry["default_ms"]
+        assert entry["ms"] <= against * 1.0001
         # the front-end resolves the same configuration, also for the variant with in-kernel harmonics
         from fasteq_b200.ops import uniform1d_jit as u1d
         assert u1d._tuning_for(spec, d, (), needs) == t
