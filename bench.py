@@ -77,6 +77,11 @@ def fp32_floor(spec, tun, direction, needs, E, U, launch_s, dev, sm_mhz=None, la
             f"{tag}_pipe_utilisation": floor_s / launch_s, "sm_mhz": sm_mhz}
 
 
+def _go_home(tun):
+    """Where a backward layout keeps the receiver's grad_out row."""
+    return "shared memory" if tun.go_smem else ("tensor memory" if tun.go_tmem else "global memory through L1")
+
+
 def measured_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -551,7 +556,7 @@ def cwtp_kernel_block(workload: str, dev, seed: int = 0):
                         "frac_of_nominal_8TBs": (bf + bb) / (t_f + t_b) / 8e12, "edges_per_s": E / (t_f + t_b)},
             "unit": "GB/s", "peak": peak, "peak_kind": kind, "bound": "hbm",
             "tuning": {dr: {"pipes": t.pipes, "groups": t.groups, "stages": t.stages, "vec": t.vec, "ctas_per_sm": t.min_blocks,
-                            "two_pass": t.two_pass} for dr, t in tun.items()}}
+                            "two_pass": t.two_pass, "grad_out_row": _go_home(t)} for dr, t in tun.items()}}
 
 
 def config2_bench(dev, boxes=None):
@@ -875,6 +880,7 @@ def main():
     roof["fp32_pipe"] = fp32_floor(call.spec, tun_b, "bwd", (True, True, True), E, d.u_dim, t_bwd, dev)
     roof_fwd["fp32_pipe"] = fp32_floor(call.spec, tun_f, "fwd", (False, False, False), E, d.u_dim, t_fwd, dev)
     roof["tuning"] = {k_: getattr(tun_b, k_) for k_ in ("pipes", "groups", "stages", "min_blocks", "two_pass")}
+    roof["tuning"]["grad_out_row"] = _go_home(tun_b)
     roof_fwd["tuning"] = {k_: getattr(tun_f, k_) for k_ in ("pipes", "groups", "stages", "min_blocks", "two_pass")}
     roof_both = {"achieved": (bytes_fwd + bytes_bwd) / (t_fwd + t_bwd) / 1e9,
                  "frac": (bytes_fwd + bytes_bwd) / (t_fwd + t_bwd) / 1e9 / peak,
