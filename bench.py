@@ -47,7 +47,7 @@ CPU_NOTE = ("port of e3nn's uvu TensorProduct + scatter (oracle/e3nn_uvu_ref.py,
 # DRAM bytes (dram__bytes_read + dram__bytes_write) over algorithmic bytes, from one ncu capture per kernel
 # on a 16-box case of the same workload; traffic grows in proportion to the edge count (every term
 # is per edge or per node and the generator fixes edges per node), so the ratio carries to a full launch.
-TRAFFIC_RATIO = {"config1_cwtp": {"fwd": 1.009, "bwd": 1.041}, "config0_layout_cwtp": {"fwd": 1.063, "bwd": 1.174},
+TRAFFIC_RATIO = {"config1_cwtp": {"fwd": 1.009, "bwd": 1.040}, "config0_layout_cwtp": {"fwd": 1.063, "bwd": 1.131},
                  "config3_layer_cwtp": {"fwd": 1.039, "bwd": 1.134}}
 
 
