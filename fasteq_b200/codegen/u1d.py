@@ -323,8 +323,8 @@ def _check_tuning(spec: U1DSpec, tun: Tuning) -> None:
     if tun.ct % (32 * tun.vec):
         raise ValueError("ct must be a multiple of 32 * vec")
     if tun.go_tmem:
-        if tun.go_smem or tun.groups != 1 or spec.dtype != "f32" or spec.u % tun.ct:
-            raise ValueError("the tensor-memory gradient row needs FP32, whole channel tiles, one thread group and no shared-memory tile")
+        if tun.go_smem or tun.groups != 1 or spec.u % tun.ct:
+            raise ValueError("the tensor-memory gradient row needs whole channel tiles, one thread group and no shared-memory tile")
         if tmem_columns(spec, tun) > 512:
             raise ValueError("the gradient rows of this layout do not fit 512 columns of tensor memory")
         if tun.stages > 13:
@@ -333,9 +333,10 @@ def _check_tuning(spec: U1DSpec, tun: Tuning) -> None:
 
 def tmem_columns(spec: U1DSpec, tun: Tuning) -> int:
     """Tensor-memory columns the ``go_tmem`` layout allocates: consumer warps with the same warp index modulo four share
-    a lane quarter and stack their rows (vec * out_segs 32-bit columns each); allocations are powers of two >= 32."""
+    a lane quarter and stack their rows (vec * out_segs values of one or two 32-bit columns each); allocations are powers
+    of two >= 32."""
     ncons = tun.pipes * tun.groups * (tun.ct // tun.vec) // 32
-    need = (ncons + 3) // 4 * tun.vec * spec.out_segs
+    need = (ncons + 3) // 4 * tun.vec * spec.out_segs * (spec.elem_bytes // 4)
     cols = 32
     while cols < need:
         cols *= 2
@@ -610,6 +611,7 @@ constexpr int NTHREADS = {threads};
 constexpr int NGO = {1 if tun.go_smem else 0};                                 // grad_out row buffers in shared memory (0: read through L1)
 constexpr bool GO_TMEM = {'true' if tun.go_tmem else 'false'};                 // ... or parked in tensor memory, one lane per consumer thread
 constexpr uint32_t TMEM_COLS = {tmem_columns(spec, tun) if tun.go_tmem else 0};
+constexpr uint32_t GO_COLS = VEC * (uint32_t)(sizeof(T) / 4);                  // 32-bit columns one segment of a thread's row takes
 constexpr int GO_BYTES = round_up(OSEG * CT * (int)sizeof(T), 128);
 constexpr int PIPE_BYTES = BAR_BYTES + STAGES * STAGE_BYTES + NGO * GO_BYTES;
 constexpr int SMEM_BYTES = cfg::PIPES * PIPE_BYTES;
@@ -710,8 +712,8 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
   const int grp = ptid / TPG, ch = (ptid % TPG) * VEC; (void)grp;
   uint32_t it = 0, nseg = 0;
   // this thread's gradient row in tensor memory: lane = 32 * (warp % 4) + lane id, the consumer warps of one lane quarter
-  // stacked VEC * OSEG columns apart
-  const uint32_t tmem_go = tmem_base + ((uint32_t)(32 * (warp_all & 3)) << 16) + (uint32_t)((warp_all >> 2) * VEC * OSEG);
+  // stacked GO_COLS * OSEG columns apart
+  const uint32_t tmem_go = tmem_base + ((uint32_t)(32 * (warp_all & 3)) << 16) + (uint32_t)(warp_all >> 2) * GO_COLS * OSEG;
   (void)tmem_go;
 """)
     L: List[str] = []
@@ -735,7 +737,7 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
       // a new receiver (or channel tile): its grad_out row moves from global memory into this thread's tensor-memory lane
       const T* grow = go + (size_t)m.row * OSEG * U + (size_t)m.ct * CT + ch;
 #pragma unroll
-      for (int v = 0; v < OSEG; ++v) scratch_tmem_st(tmem_go + (uint32_t)(VEC * v), VS::ldg(grow + (size_t)v * U));
+      for (int v = 0; v < OSEG; ++v) scratch_tmem_st(tmem_go + GO_COLS * (uint32_t)v, VS::ldg(grow + (size_t)v * U));
       scratch_tmem_wait_st();
     }""")
     if spec.w_shared and need_gw:
@@ -846,7 +848,7 @@ fasteq_u1d_bwd_kernel(const Graph g, const T* __restrict__ go, const T* __restri
                 vs = sorted({t.v for t in b.terms})
                 L.append("      {")
                 L.append("      V " + ", ".join(f"go_{v}" for v in vs) + ";")
-                L += [f"      scratch_tmem_ld(tmem_go + {v}u * VEC, go_{v});" for v in vs]
+                L += [f"      scratch_tmem_ld(tmem_go + {v}u * GO_COLS, go_{v});" for v in vs]
                 L.append(f"      scratch_tmem_wait_ld(go_{vs[0]});")
                 L += [f"      scratch_tmem_pin(go_{v});" for v in vs[1:]]
             if _is_diagonal(b.terms):

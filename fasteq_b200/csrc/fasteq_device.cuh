@@ -188,6 +188,10 @@ __device__ __forceinline__ void scratch_tmem_st(uint32_t addr, float v) {
 __device__ __forceinline__ void scratch_tmem_st(uint32_t addr, float2 v) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(__float_as_uint(v.x)), "r"(__float_as_uint(v.y)) : "memory");
 }
+__device__ __forceinline__ void scratch_tmem_st(uint32_t addr, double v) {
+  const unsigned long long b = (unsigned long long)__double_as_longlong(v);
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(addr), "r"((uint32_t)b), "r"((uint32_t)(b >> 32)) : "memory");
+}
 __device__ __forceinline__ void scratch_tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // the loaded registers are valid only after scratch_tmem_wait_ld(...) has been given them
 __device__ __forceinline__ void scratch_tmem_ld(uint32_t addr, float& v) {
@@ -200,9 +204,16 @@ __device__ __forceinline__ void scratch_tmem_ld(uint32_t addr, float2& v) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr) : "memory");
   v = make_float2(__uint_as_float(r0), __uint_as_float(r1));
 }
+__device__ __forceinline__ void scratch_tmem_ld(uint32_t addr, double& v) {
+  uint32_t r0, r1;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr) : "memory");
+  v = __longlong_as_double((long long)(((unsigned long long)r1 << 32) | r0));
+}
 // the wait names the values it releases, so that no use of them can be scheduled ahead of it
 __device__ __forceinline__ void scratch_tmem_wait_ld(float& a) { asm volatile("tcgen05.wait::ld.sync.aligned;" : "+f"(a)::"memory"); }
 __device__ __forceinline__ void scratch_tmem_wait_ld(float2& a) { asm volatile("tcgen05.wait::ld.sync.aligned;" : "+f"(a.x), "+f"(a.y)::"memory"); }
+__device__ __forceinline__ void scratch_tmem_wait_ld(double& a) { asm volatile("tcgen05.wait::ld.sync.aligned;" : "+d"(a)::"memory"); }
+__device__ __forceinline__ void scratch_tmem_pin(double& a) { asm volatile("" : "+d"(a)::"memory"); }
 __device__ __forceinline__ void scratch_tmem_pin(float& a) { asm volatile("" : "+f"(a)::"memory"); }
 __device__ __forceinline__ void scratch_tmem_pin(float2& a) { asm volatile("" : "+f"(a.x), "+f"(a.y)::"memory"); }
 

@@ -206,3 +206,42 @@ def test_two_thread_groups_match_oracle(in1, parity, variant):
     rgw, rgx, rgy = uniform1d_ref.uniform1d_backward(a(r, d.out_seg_num), a(w, d.w_seg_num), a(x, d.x_seg_num), a(y, d.y_seg_num), paths,
                                                      d.coeff_list, **kw)
     _close(out, ref, "forward"); _close(gw, rgw, "grad_w"); _close(gx, rgx, "grad_x"); _close(gy, rgy, "grad_y")
+
+
+@pytest.mark.parametrize("in1,u_pipes", [("64x0e+64x1o", 4), ("128x0e+128x1o+128x2e", 3)])
+def test_float64_backward_with_the_gradient_row_in_tensor_memory(in1, u_pipes):
+    """FP64 on the tensor-memory layout (a double takes two 32-bit columns of the thread's lane; 64-channel tiles, so a
+    pipeline has two consumer warps), all three gradients against the oracle at 1e-12."""
+    import dataclasses
+    from fasteq_b200.ops import fast_uniform1d_jit
+    from fasteq_b200.ops import uniform1d_jit as u1d
+    d = _descriptor(in1, None)
+    U, N = d.u_dim, 97
+    g = torch.Generator().manual_seed(8)
+    src, dst = _graph(N, g)
+    E = int(dst.numel())
+    w = torch.randn(E, d.w_seg_num * U, generator=g, dtype=torch.float64)
+    x = torch.randn(N, d.x_seg_num * U, generator=g, dtype=torch.float64)
+    y = torch.randn(E, d.y_seg_num, generator=g, dtype=torch.float64)
+    r = torch.randn(N, d.out_seg_num * U, generator=g, dtype=torch.float64)
+    spec = make_spec(d.i_list, d.j_list, d.k_list, d.v_list, d.coeff_list, w_segs=d.w_seg_num, x_segs=d.x_seg_num,
+                     y_segs=d.y_seg_num, out_segs=d.out_seg_num, u=d.u_dim, dtype="f64")
+    base = default_tuning(spec, "bwd")
+    tun = dataclasses.replace(base, pipes=u_pipes, go_smem=False, go_tmem=True, stages=2, min_blocks=1)
+    u1d._TUNING_OVERRIDE["bwd"] = tun
+    try:
+        wd, xd, yd = (t.cuda().requires_grad_(True) for t in (w, x, y))
+        out = fast_uniform1d_jit(wd, xd, yd, {1: src.int().cuda()}, {0: dst.int().cuda()}, d.meta(torch.float64, "cuda"))
+        gw, gx, gy = torch.autograd.grad(out, (wd, xd, yd), r.cuda())
+        mod = u1d.get_module(spec, "bwd", (True, True, True), tuning=tun)
+        assert mod.device_status() == 0
+    finally:
+        u1d._TUNING_OVERRIDE.pop("bwd", None)
+    paths = list(zip(d.i_list.tolist(), d.j_list.tolist(), d.k_list.tolist(), d.v_list.tolist()))
+    a = lambda t, s: t.numpy().reshape(t.shape[0], s, -1)
+    kw = dict(src_x=src.numpy(), dst=dst.numpy())
+    rgw, rgx, rgy = uniform1d_ref.uniform1d_backward(a(r, d.out_seg_num), a(w, d.w_seg_num), a(x, d.x_seg_num), a(y, d.y_seg_num), paths,
+                                                     d.coeff_list, **kw)
+    for got, ref, name in ((gw, rgw, "grad_w"), (gx, rgx, "grad_x"), (gy, rgy, "grad_y")):
+        err = np.abs(got.detach().cpu().numpy().reshape(ref.shape) - ref).max() / np.abs(ref).max()
+        assert err <= 1e-12, f"{name}: relative error {err:.3e}"
