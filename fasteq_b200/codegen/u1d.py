@@ -325,8 +325,8 @@ def _check_tuning(spec: U1DSpec, tun: Tuning) -> None:
     if tun.go_tmem:
         if tun.go_smem or tun.groups != 1 or spec.u % tun.ct:
             raise ValueError("the tensor-memory gradient row needs whole channel tiles, one thread group and no shared-memory tile")
-        if tmem_columns(spec, tun) > 512:
-            raise ValueError("the gradient rows of this layout do not fit 512 columns of tensor memory")
+        if tmem_columns(spec, tun) * max(1, tun.min_blocks) > 512:
+            raise ValueError("the gradient rows of this layout (times the resident CTAs asked for) do not fit 512 columns of tensor memory")
         if tun.stages > 13:
             raise ValueError("at most 13 stages beside the tensor-memory slot")
 

@@ -57,3 +57,24 @@ def test_database_entries_decode_and_are_used():
         if spec.y_segs == 16 and not spec.y_vec:
             fused = dataclasses.replace(spec, y_sh=((0, 1, 2, 3), True, "component"))
             assert tuning.lookup(fused, d, needs) == t
+
+
+def test_tensor_memory_layout_limits():
+    """The backward layout that parks the grad_out row in tensor memory: column budget (512 per SM, shared by the resident
+    CTAs), no shared-memory tile beside it, whole channel tiles only."""
+    import dataclasses
+    spec = cwtp_spec("128x0e+128x1o", 3, 3, "f32")
+    base = gen.default_tuning(spec, "bwd")
+    ok = dataclasses.replace(base, go_smem=False, go_tmem=True, stages=5)
+    gen._check_tuning(spec, ok)
+    assert gen.tmem_columns(spec, ok) == 256                      # 8 consumer warps: 2 per lane quarter x 110 columns -> 256
+    assert "scratch_tmem_alloc" in gen.emit_backward(spec, ok, True, True, True)
+    for bad in (dataclasses.replace(ok, go_smem=True), dataclasses.replace(ok, groups=2), dataclasses.replace(ok, min_blocks=3)):
+        with pytest.raises(ValueError):
+            gen._check_tuning(spec, bad)
+    wide = cwtp_spec("128x0e+128x1o+128x2e", 3, 3, "f64")          # 106 segments x 2 columns: 4 pipelines of 2 warps do not fit
+    with pytest.raises(ValueError):
+        gen._check_tuning(wide, dataclasses.replace(gen.default_tuning(wide, "bwd"), pipes=6, go_smem=False, go_tmem=True))
+    tail = cwtp_spec("33x0e+33x1o", 2, 2, "f32")                   # a channel tail would make the warp-collective loads diverge
+    with pytest.raises(ValueError):
+        gen._check_tuning(tail, dataclasses.replace(gen.default_tuning(tail, "bwd"), go_smem=False, go_tmem=True))
