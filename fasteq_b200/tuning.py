@@ -3,11 +3,13 @@
 The reference compiles a handful of candidates per signature, derives warps per block from the registers ptxas reports,
 times them at several sizes and stores the winner on disk (fasteq/ops/uniform1d_jit.py:549-580, :975-1069; sizes in
 fasteq/ops/auto_schedule/multi_size_tuning.py:9-21).  Here the knobs are those of the pipelined kernels -- pipelines
-per CTA, thread groups, ring depth, resident CTAs, one or two passes in the backward -- and the procedure is:
+per CTA, thread groups, ring depth, resident CTAs, one or two passes in the backward, where the backward keeps the
+receiver's grad_out row (shared memory, L1, tensor memory) -- and the procedure is:
 
-* ``candidates(spec, direction)``: the configurations that fit one SM's shared memory;
+* ``candidates(spec, direction)``: the configurations that fit one SM's shared memory and tensor memory;
 * ``sweep(spec, direction, needs)`` (needs a GPU): compile every candidate, time its kernel alone on a synthetic
-  receiver-sorted graph of the benchmark's density, keep the fastest;
+  receiver-sorted graph of the benchmark's density, then time the fastest and the heuristic default again in five
+  alternating bursts; the challenger replaces the default only if it wins that alternation by more than the margin;
 * the winners live in ``tuning_db.json`` beside this file (tracked, so that a fresh checkout starts tuned); the
   operator front-end asks ``lookup`` before it falls back to the heuristic ``codegen.u1d.default_tuning``.
 
@@ -84,8 +86,10 @@ def smem_bytes(spec: U1DSpec, tun: _emit.Tuning, direction: str, need_gy: bool =
 
 
 def candidates(spec: U1DSpec, direction: str, needs=(True, True, True)) -> List[_emit.Tuning]:
-    """Launch configurations worth timing: the heuristic default and its neighbours in (pipelines, thread groups,
-    ring depth, resident CTAs, passes) that fit 227 KB of shared memory and 1024 threads per CTA."""
+    """Launch configurations worth timing: the heuristic default and its neighbours in (two to six pipelines, thread
+    groups, ring depth, resident CTAs, passes; backward: the grad_out row staged in shared memory, read through L1 or
+    parked in tensor memory; L2 prefetch distance) that fit 227 KB of shared memory, 1024 threads per CTA and 512
+    columns of tensor memory."""
     base = _emit.default_tuning(spec, direction)
     out: List[_emit.Tuning] = [base]
     wpg = base.ct // (32 * base.vec)
