@@ -78,3 +78,24 @@ def test_tensor_memory_layout_limits():
     tail = cwtp_spec("33x0e+33x1o", 2, 2, "f32")                   # a channel tail would make the warp-collective loads diverge
     with pytest.raises(ValueError):
         gen._check_tuning(tail, dataclasses.replace(gen.default_tuning(tail, "bwd"), go_smem=False, go_tmem=True))
+
+
+def test_instruction_counts_of_the_standard_signatures():
+    """Multiply / FMA instructions per (edge, channel) in the generated source: the figures the bench line's arithmetic
+    floors rest on.  One-product couplings (l1 = 0 or l2 = 0) cost 2n + 3 instructions for n output components in the
+    backward (sum over the components first, then the shared operand), not 5n."""
+    for in1, fwd, bwd in (("128x0e+128x1o", 220, 490), ("128x0e+128x1o+128x2e", 562, 1244)):
+        spec = cwtp_spec(in1, 3, 3, "f32")
+        f = gen.arith_ops(spec, gen.default_tuning(spec, "fwd"), "fwd", (False, False, False))
+        b = gen.arith_ops(spec, gen.default_tuning(spec, "bwd"), "bwd", (True, True, True))
+        assert (sum(f.values()), sum(b.values())) == (fwd, bwd)
+    # a single l1 = 0 coupling with n = 7 components: 2 * 7 + 3 backward instructions
+    from fasteq_b200.codegen.u1d_common import make_spec
+    n = 7
+    spec = make_spec([0] * n, [0] * n, list(range(n)), list(range(n)), [1.0] * n, w_segs=1, x_segs=1, y_segs=n, out_segs=n, u=64, dtype="f32")
+    b = gen.arith_ops(spec, gen.default_tuning(spec, "bwd"), "bwd", (True, True, True))
+    assert sum(b.values()) == 2 * n + 3
+    # ... and an l2 = 0 coupling (the components differ in x, share y)
+    spec = make_spec([0] * n, list(range(n)), [0] * n, list(range(n)), [1.0] * n, w_segs=1, x_segs=n, y_segs=1, out_segs=n, u=64, dtype="f32")
+    b = gen.arith_ops(spec, gen.default_tuning(spec, "bwd"), "bwd", (True, True, True))
+    assert sum(b.values()) == 2 * n + 3
