@@ -99,3 +99,24 @@ def test_instruction_counts_of_the_standard_signatures():
     spec = make_spec([0] * n, list(range(n)), [0] * n, list(range(n)), [1.0] * n, w_segs=1, x_segs=n, y_segs=1, out_segs=n, u=64, dtype="f32")
     b = gen.arith_ops(spec, gen.default_tuning(spec, "bwd"), "bwd", (True, True, True))
     assert sum(b.values()) == 2 * n + 3
+
+
+def test_tensor_memory_columns_are_returned_on_every_consumer_exit():
+    """Source check (no GPU fault is provoked to test this): in the tensor-memory layout the consumers leave their loop only
+    through ``break`` - also when a bounded wait gave up - and the code after the loop holds the consumers' barrier and the
+    release of the columns; the producers, which never touch tensor memory, are the only warps that return early."""
+    import dataclasses
+    spec = cwtp_spec("128x0e+128x1o", 3, 3, "f32")
+    tun = dataclasses.replace(gen.default_tuning(spec, "bwd"), go_smem=False, go_tmem=True, stages=5)
+    src = gen.emit_backward(spec, tun, True, True, True)
+    kernel = src[src.index("fasteq_u1d_bwd_kernel("):]
+    kernel = kernel[:kernel.index("__device__ int g_status_word")]
+    consumer = kernel[kernel.index("p.run(flush, begin);"):]
+    consumer = consumer[consumer.index("return;") + len("return;"):]          # past the producers' exit
+    import re
+    assert re.search(r"\breturn\b", consumer) is None
+    loop_end = consumer.rindex("if (m.flags & F_DONE) break;")
+    tail = consumer[loop_end:]
+    assert tail.index("bar.sync 1") < tail.index("scratch_tmem_free(")
+    assert kernel.index("scratch_tmem_alloc(") < kernel.index("p.run(flush, begin);")
+    assert consumer.count("if (!mbar_wait(") >= 1 and "break;" in consumer
